@@ -1,0 +1,109 @@
+/* slotscan.h -- C ABI of libslotscan.so: the slot-scan hot path as hand-written CUDA for sm_100a.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless said otherwise, every call is
+ * asynchronous on `stream` (a cudaStream_t passed as void*), allocates nothing and returns a status:
+ *      0   ok
+ *     <0   the arguments were rejected before any launch (SLOTSCAN_E_*)
+ *     >0   a cudaError_t from a launch
+ * The functions replace, one for one, the host side of the reference's runtime-compiled kernels
+ * (gqa25/slotkern_cuda.py: _KVScanC.forward :484-511, _KVScanC.backward :514-533, kernel_attrs :467-479) and the
+ * torch ops around them in gqa25/memlm_sh.py (:362-397 read, :464-475 writer epilogue, :221-234 quantiser).
+ *
+ * Layouts (all contiguous, identical to the reference):
+ *   token streams   k, q (B,T,H,DK)   v (B,T,H,DV)   gate, fr (B,T,H)        token index ix = (b*T + t)*H + h
+ *   snapshots       kbuf (B,NB,H,N,DK)  vbuf (B,NB,H,N,DV),  NB = ceil(T/G): the PRE-write state at t = 0, G, 2G, ...
+ *   per-sequence    (B*H, N, D) finals, (B*H, N) occupancy
+ */
+#ifndef SLOTSCAN_H
+#define SLOTSCAN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SLOTSCAN_ABI_VERSION 1
+
+enum { SLOTSCAN_F32 = 0, SLOTSCAN_BF16 = 1 };
+
+enum {
+    SLOTSCAN_OK = 0,
+    SLOTSCAN_E_NULL = -1,       /* a required pointer is NULL */
+    SLOTSCAN_E_SHAPE = -2,      /* a size is out of the supported range (see slotscan_check) */
+    SLOTSCAN_E_DTYPE = -3,      /* unknown dtype code */
+    SLOTSCAN_E_ALIGN = -4,      /* a pointer is not 16-byte aligned */
+    SLOTSCAN_E_MODE = -5,       /* a mode this entry point does not implement */
+    SLOTSCAN_E_TOO_LARGE = -6   /* beyond the fixed capacity of a no-allocation entry point */
+};
+
+/* Shape and mode of one scan call.  Mirrors the arguments of the reference's kv_scan_c
+ * (gqa25/slotkern_cuda.py:536): N, G, hard_gate, eps, occ_bin; fr_per_token = (fr.dim() == 3) (:491). */
+typedef struct {
+    int32_t B, T, H, N, DK, DV, G;
+    int32_t hard_gate;      /* forward uses [gate > 0.5]; gradient passes straight through */
+    int32_t occ_bin;        /* free-row penalty on [o >= eps] instead of on o */
+    int32_t fr_per_token;   /* fr is (B,T,H); otherwise one element */
+    int32_t in_dtype;       /* SLOTSCAN_F32 / SLOTSCAN_BF16: k, q, v and their gradients */
+    int32_t snap_dtype;     /* SLOTSCAN_F32 / SLOTSCAN_BF16: kbuf, vbuf, dkbuf, dvbuf */
+    float eps;              /* occupancy threshold, 1e-4 in the reference */
+} slotscan_params;
+
+/* Argument check shared by every entry point: 0 or a SLOTSCAN_E_* code.  Supported: B,T,H,N,G >= 1;
+ * DK, DV multiples of 8 in [8,128]; N*(DK+1) floats must fit the 227 KB shared memory of one CTA (N <= 440 at DK=128). */
+int slotscan_check(const slotscan_params* p);
+
+/* Log of one forward call: what the backward (and a caller that streams chunks) needs.  All caller-allocated.
+ *   addr   (B,T,H) int32   the row each token wrote                 [reference: `am`, slotkern_cuda.py:502]
+ *   oold   (B,T,H) f32     that row's occupancy before the write    [`oold` :503]
+ *   kold   (B,T,H,DK) f32, vold (B,T,H,DV) f32   the row before the write   [`kold`, `vold` :503]
+ *   kfin   (B*H,N,DK) f32, vfin (B*H,N,DV) f32, ofin (B*H,N) f32    state after the last token  [:504]
+ *   tfirst (B*H,N) int32   first token at which row n could be addressed (T if never): rows are taken in index
+ *                          order, so everything above the highest row touched so far is exactly zero and is skipped. */
+typedef struct {
+    int32_t* addr;
+    float* oold;
+    float* kold;
+    float* vold;
+    float* kfin;
+    float* vfin;
+    float* ofin;
+    int32_t* tfirst;
+} slotscan_log;
+
+/* Forward: hard (argmax) address, address reads the stored keys as constants.
+ * Replaces _KVScanC.forward (gqa25/slotkern_cuda.py:484-511: addr_fwd :72-174 + val_fwd :178-206).
+ * q may be NULL (search with k).  temp: 1 float on the device (exp(log_wsharp), memlm_sh.py:439).
+ * Writes kbuf, vbuf (snap_dtype) and the log. */
+int slotscan_hard_fwd(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
+                      const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log* log,
+                      void* stream);
+
+/* Bytes of scratch the backward needs (the per-token, per-row table D[t,n] plus per-sequence partial sums). */
+size_t slotscan_hard_bwd_scratch_bytes(const slotscan_params* p);
+
+/* Backward of slotscan_hard_fwd for upstream gradients dkbuf, dvbuf (snap_dtype; either may be NULL = zeros).
+ * Replaces _KVScanC.backward (gqa25/slotkern_cuda.py:514-533: rows_bwd :209-261 + addr_bwd :264-443).
+ * Outputs: dk, dv (in_dtype), dq (in_dtype; NULL iff q is NULL, its gradient is then added into dk),
+ * dgate (B,T,H) f32, dfr (B,T,H) f32 or 1 float, dtemp 1 float.  The scalar sums are reduced in a fixed order:
+ * results are bitwise repeatable (the reference uses float atomics, slotkern_cuda.py:440-441). */
+int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
+                      const float* fr, const float* temp, const slotscan_log* log, const void* dkbuf,
+                      const void* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq, void* dv,
+                      float* dgate, float* dfr, float* dtemp, void* stream);
+
+/* Registers / spilled bytes / static shared memory / max threads of each kernel, the analogue of kernel_attrs
+ * (gqa25/slotkern_cuda.py:467-479).  Fills up to `cap` entries (HOST memory), returns how many kernels exist. */
+typedef struct {
+    char name[48];
+    int32_t regs, local_bytes, static_smem, max_threads;
+} slotscan_kernel_attr;
+int slotscan_query_attrs(slotscan_kernel_attr* out, int cap);
+
+int slotscan_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLOTSCAN_H */

@@ -74,7 +74,10 @@ static void FN(step_address)(const slotscan_cfg* c, const REAL* K, const REAL* o
     w->am = am;
     w->margin = zmax - z2;
     REAL se = 0;
-    for (int n = 0; n < N; n++) { w->asoft[n] = EXP(w->z[n] - zmax); se += w->asoft[n]; }
+    for (int n = 0; n < N; n++) {   /* a masked row is exp(-1e30 - zmax) = 0 exactly; skip the slow libm underflow path */
+        w->asoft[n] = w->ok[n] ? EXP(w->z[n] - zmax) : (REAL)0;
+        se += w->asoft[n];
+    }
     for (int n = 0; n < N; n++) w->asoft[n] /= se;
     if (c->hard) for (int n = 0; n < N; n++) w->afwd[n] = (n == am) ? (REAL)1 : (REAL)0;
     else for (int n = 0; n < N; n++) w->afwd[n] = w->asoft[n];

@@ -1,0 +1,5 @@
+"""slotscan_b200: the slot-scan hot path of smal-memory-llm as hand-written sm_100a CUDA behind the reference's own
+Python call signature.  Importing this package loads nothing; the first op call loads libslotscan.so and fails
+loudly if it is not built."""
+from .scan import kv_scan_c, kv_scan_g, scan_kv, scan_with_log  # noqa: F401
+from ._lib import kernel_attrs  # noqa: F401

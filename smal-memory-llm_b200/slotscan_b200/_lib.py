@@ -1,0 +1,74 @@
+"""Loader of libslotscan.so, the C-ABI CUDA library (include/slotscan.h).  There is no fallback of any kind:
+if the library is missing or an entry point rejects a call, the caller gets an exception."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libslotscan.so")
+
+F32, BF16 = 0, 1
+
+ERRORS = {-1: "a required pointer is NULL", -2: "unsupported shape", -3: "unknown dtype code",
+          -4: "a pointer is not 16-byte aligned", -5: "mode not implemented by this entry point",
+          -6: "beyond the fixed capacity of the no-allocation entry point"}
+
+
+class Params(ctypes.Structure):
+    """slotscan_params of include/slotscan.h."""
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "T", "H", "N", "DK", "DV", "G", "hard_gate", "occ_bin",
+                                              "fr_per_token", "in_dtype", "snap_dtype")] + [("eps", ctypes.c_float)]
+
+
+class Log(ctypes.Structure):
+    """slotscan_log of include/slotscan.h."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst")]
+
+
+class KernelAttr(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 48), ("regs", ctypes.c_int32), ("local_bytes", ctypes.c_int32),
+                ("static_smem", ctypes.c_int32), ("max_threads", ctypes.c_int32)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (run `make` in smal-memory-llm_b200/ or
+    __graft_entry__.build())."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError("libslotscan.so is not built (%s): the slot scan has no other implementation; "
+                               "build it with `make -C smal-memory-llm_b200`" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+        PP, LP = ctypes.POINTER(Params), ctypes.POINTER(Log)
+        L.slotscan_abi_version.restype = ci
+        L.slotscan_check.argtypes = [PP]
+        L.slotscan_hard_fwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, vp, vp, LP, vp]
+        L.slotscan_hard_bwd_scratch_bytes.argtypes = [PP]
+        L.slotscan_hard_bwd_scratch_bytes.restype = sz
+        L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
+        L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
+        for f in ("slotscan_check", "slotscan_hard_fwd", "slotscan_hard_bwd", "slotscan_query_attrs"):
+            getattr(L, f).restype = ci
+        assert L.slotscan_abi_version() == 1, "libslotscan.so / Python host ABI mismatch"
+        _lib = L
+    return _lib
+
+
+def check(rc, what):
+    if rc == 0:
+        return
+    if rc < 0:
+        raise ValueError("%s rejected the call: %s (code %d)" % (what, ERRORS.get(rc, "?"), rc))
+    raise RuntimeError("%s: CUDA error %d" % (what, rc))
+
+
+def kernel_attrs():
+    """{kernel name: (registers, spilled bytes, static shared memory, max threads)} -- the analogue of the
+    reference's kernel_attrs (gqa25/slotkern_cuda.py:467-479).  Needs a CUDA device."""
+    buf = (KernelAttr * 32)()
+    n = lib().slotscan_query_attrs(buf, 32)
+    return {buf[i].name.decode(): (buf[i].regs, buf[i].local_bytes, buf[i].static_smem, buf[i].max_threads)
+            for i in range(min(n, 32))}

@@ -1,0 +1,224 @@
+"""GPU parity of the hard-address scan (through the Python host and the C ABI) against the CPU oracle and the golden
+fixtures.  Criteria: addresses identical wherever the oracle's top-1/top-2 margin exceeds 1e-4 (near-ties counted);
+float32 mode: snapshots within 1e-5, gradients within 1e-4 of their own max against the float64 oracle
+(the reference's own bars are 1e-4 / 1e-3, kvu/test_cuda.py:62); bf16 mode: rtol = atol = 2e-3."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.scan_cases import address_report, allclose_report, make_inputs, rel_to_max
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+DEV = "cuda"
+
+
+def _dev(x, dtype=torch.float32):
+    return None if x is None else torch.as_tensor(np.asarray(x)).to(DEV, dtype)
+
+
+def run_cuda(inp, N, G, hard_gate, occ_bin, wk=None, wv=None, dtype=torch.float32, out_dtype=torch.float32, grad=True):
+    import slotscan_b200 as S
+    k, v, g, fr = (_dev(inp[n], dt) for n, dt in (("k", dtype), ("v", dtype), ("gate", torch.float32), ("fr", torch.float32)))
+    q = _dev(inp["q"], dtype)
+    temp = torch.tensor(float(inp["temp"]), device=DEV)
+    leaves = [k, v, g, fr, temp] + ([q] if q is not None else [])
+    if grad:
+        for t in leaves:
+            t.requires_grad_()
+    kb, vb = S.kv_scan_g(k, v, g, fr, N, temp, G=G, hard=True, hard_gate=hard_gate, detach_addr=True, q=q, occ_bin=occ_bin,
+                         out_dtype=out_dtype)
+    out = dict(kbuf=kb.detach().float().cpu().numpy(), vbuf=vb.detach().float().cpu().numpy())
+    if grad:
+        ((kb.float() * _dev(wk)).sum() + (vb.float() * _dev(wv)).sum()).backward()
+        out.update(dk=k.grad, dv=v.grad, dgate=g.grad, dfr=fr.grad, dtemp=temp.grad)
+        if q is not None:
+            out["dq"] = q.grad
+        out = {n: (x.float().cpu().numpy() if torch.is_tensor(x) else x) for n, x in out.items()}
+    return out
+
+
+def run_log(inp, N, G, hard_gate, occ_bin, dtype=torch.float32):
+    import slotscan_b200 as S
+    lg = S.scan_with_log(_dev(inp["k"], dtype), _dev(inp["v"], dtype), _dev(inp["gate"]), _dev(inp["fr"]), N,
+                         float(inp["temp"]), G=G, hard_gate=hard_gate, q=_dev(inp["q"], dtype), occ_bin=occ_bin)
+    return {n: x.cpu().numpy() for n, x in lg.items()}
+
+
+HARD_DETACHED = sorted(p for p in glob.glob(os.path.join(GOLDEN, "scan_hard_detached*.npz")) +
+                       glob.glob(os.path.join(GOLDEN, "scan_hard_bench*.npz")))
+
+
+@pytest.mark.parametrize("path", HARD_DETACHED, ids=[os.path.basename(p)[5:-4] for p in HARD_DETACHED])
+def test_golden_reference_vectors(path):
+    """The reference's own float64 outputs (tests/golden) reproduced by the CUDA path in float32 mode."""
+    z = np.load(path)
+    B, T, H, N, DK, DV, G, hard, hard_gate, occ_bin, detach, frtok, sepq = (int(x) for x in z["meta"])
+    inp = dict(k=z["k"], v=z["v"], gate=z["gate"], fr=z["fr"], q=z["q"] if sepq else None, temp=float(z["temp"]))
+    lg = run_log(inp, N, G, bool(hard_gate), bool(occ_bin))
+    assert np.array_equal(lg["addr"], z["addr"]), "addresses differ from the reference"
+    out = run_cuda(inp, N, G, bool(hard_gate), bool(occ_bin), wk=z["wk"], wv=z["wv"])
+    assert np.abs(out["kbuf"] - z["kbuf"]).max() < 1e-5 and np.abs(out["vbuf"] - z["vbuf"]).max() < 1e-5
+    for n in ["dk", "dv", "dgate", "dfr", "dtemp"] + (["dq"] if sepq else []):
+        assert rel_to_max(out[n].reshape(z[n].shape), z[n]) < 1e-4, n
+
+
+CASES = [  # name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq        (kvu/test_cuda.py:11-20 + sh25)
+    ("sh25_main", "bench", 1, 1024, 6, 192, 128, 128, 8, False, True, True, True),
+    ("sh25_enc", "bench", 1, 512, 6, 96, 128, 128, 8, False, True, True, True),
+    ("sh25_main_clustered", "clustered", 1, 512, 6, 192, 128, 128, 8, False, True, True, True),
+    ("sh25_main_fill", "fill", 1, 768, 6, 192, 128, 128, 8, False, True, True, True),
+    ("t1000_d64", "gates01", 1, 1000, 4, 192, 64, 64, 8, False, True, True, True),
+    ("n40_g16_scalar_fr", "gates01", 1, 300, 4, 40, 64, 64, 16, False, False, False, False),
+    ("n40_g7_hardgate", "gates01", 1, 300, 4, 40, 64, 64, 7, True, True, False, True),
+    ("n50_d128_no_occbin", "gates01", 1, 300, 3, 50, 128, 128, 8, False, False, False, True),
+    ("g1_short", "clustered", 2, 40, 2, 10, 8, 8, 1, False, True, True, False),
+    ("dk_ne_dv", "bench", 1, 100, 2, 24, 32, 16, 8, False, True, True, True),
+    ("t_lt_g", "bench", 1, 5, 2, 8, 16, 16, 8, False, True, True, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_fp32_mode_vs_float64_oracle(case):
+    name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq = case
+    inp = make_inputs(dist, B, T, H, DK, DV, seed=300 + len(name), frtok=frtok, sepq=sepq)
+    kw = dict(N=N, temp=inp["temp"], G=G, hard=True, hard_gate=hard_gate, q=inp["q"], occ_bin=occ_bin)
+    ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dtype=np.float64, **kw)
+    lg = run_log(inp, N, G, hard_gate, occ_bin)
+    ok, nflip, nbad, keep = address_report(lg["addr"], ref["addr"], ref["margin"])
+    print("%s: sequences with an address flip %d / %d, beyond the 1e-4 margin %d" % (name, nflip, B * H, nbad))
+    assert ok, "an address differs where the oracle's margin exceeds 1e-4"
+    assert keep.mean() >= 0.75, "too many near-tie flips to judge values"
+    gen = torch.Generator().manual_seed(7)
+    wk = torch.randn(ref["kbuf"].shape, generator=gen).numpy()
+    wv = torch.randn(ref["vbuf"].shape, generator=gen).numpy()
+    out = run_cuda(inp, N, G, hard_gate, occ_bin, wk=wk, wv=wv)
+    gr = O.scan_bwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dkbuf=wk, dvbuf=wv, detach_addr=True, dtype=np.float64, **kw)
+    m5 = keep[:, None, :, None, None]                       # (B,NB,H,N,D) mask of sequences without a flip
+    assert (np.abs(out["kbuf"] - ref["kbuf"]) * m5).max() < 1e-5
+    assert (np.abs(out["vbuf"] - ref["vbuf"]) * m5).max() < 1e-5
+    assert np.abs(lg["kfin"].reshape(ref["kfin"].shape) - ref["kfin"])[keep].max() < 1e-5      # final slot state
+    assert np.abs(lg["vfin"].reshape(ref["vfin"].shape) - ref["vfin"])[keep].max() < 1e-5
+    m4 = keep[:, None, :, None]
+    for n in ["dk", "dv"] + (["dq"] if sepq else []):
+        assert rel_to_max(out[n] * m4, gr[n] * m4) < 1e-4, n
+    m3 = keep[:, None, :]
+    assert rel_to_max(out["dgate"] * m3, gr["dgate"] * m3) < 1e-4
+    if frtok:
+        assert rel_to_max(out["dfr"] * m3, gr["dfr"] * m3) < 1e-4
+    if keep.all():
+        assert rel_to_max(out["dtemp"], gr["dtemp"]) < 1e-4
+        if not frtok:
+            assert rel_to_max(out["dfr"], gr["dfr"]) < 1e-4
+
+
+BF16_CASES = [c for c in CASES if c[0] in ("sh25_main", "sh25_enc", "sh25_main_clustered", "t1000_d64", "dk_ne_dv")]
+
+
+@pytest.mark.parametrize("case", BF16_CASES, ids=[c[0] for c in BF16_CASES])
+def test_bf16_storage_mode(case):
+    """bf16 token streams, bf16 snapshots and bf16 upstream gradients, float32 state and accumulation.  The oracle
+    gets the same bf16-rounded inputs, so what is compared is the arithmetic: rtol = atol = 2e-3."""
+    name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq = case
+    inp = make_inputs(dist, B, T, H, DK, DV, seed=300 + len(name), frtok=frtok, sepq=sepq)
+    for n in ("k", "q", "v"):
+        if inp[n] is not None:
+            inp[n] = inp[n].to(torch.bfloat16).float()
+    kw = dict(N=N, temp=inp["temp"], G=G, hard=True, hard_gate=hard_gate, q=inp["q"], occ_bin=occ_bin)
+    ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dtype=np.float64, **kw)
+    lg = run_log(inp, N, G, hard_gate, occ_bin, dtype=torch.bfloat16)
+    ok, nflip, nbad, keep = address_report(lg["addr"], ref["addr"], ref["margin"])
+    print("%s (bf16): sequences with an address flip %d / %d, beyond the margin %d" % (name, nflip, B * H, nbad))
+    assert ok and keep.mean() >= 0.75
+    gen = torch.Generator().manual_seed(7)
+    wk = torch.randn(ref["kbuf"].shape, generator=gen).to(torch.bfloat16).float().numpy()
+    wv = torch.randn(ref["vbuf"].shape, generator=gen).to(torch.bfloat16).float().numpy()
+    out = run_cuda(inp, N, G, hard_gate, occ_bin, wk=wk, wv=wv, dtype=torch.bfloat16, out_dtype=torch.bfloat16)
+    gr = O.scan_bwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dkbuf=wk, dvbuf=wv, detach_addr=True, dtype=np.float64, **kw)
+    m5, m4, m3 = keep[:, None, :, None, None], keep[:, None, :, None], keep[:, None, :]
+    for n, m in (("kbuf", m5), ("vbuf", m5)):
+        okc, worst = allclose_report(out[n] * m, ref[n] * m, 2e-3, 2e-3)
+        assert okc, (n, worst)
+    for n, m in (("dk", m4), ("dv", m4), ("dq", m4), ("dgate", m3), ("dfr", m3)):
+        if n in out and out[n].shape == gr[n].shape:
+            scale = max(np.abs(gr[n]).max(), 1e-30)          # gradients are compared relative to their own max
+            okc, worst = allclose_report(out[n] * m / scale, gr[n] * m / scale, 2e-3, 2e-3)
+            assert okc, (n, worst)
+
+
+def test_edges_and_contract():
+    import slotscan_b200 as S
+    inp = make_inputs("clustered", 2, 128, 4, 16, 16, seed=5, frtok=False, sepq=True)
+    d = lambda x: None if x is None else x.to(DEV)
+    k, q, v, g = d(inp["k"]), d(inp["q"]), d(inp["v"]), d(inp["gate"])
+    t1 = torch.tensor(16.0, device=DEV)
+    # constant per-token fr == scalar fr, bitwise in the forward; sum of per-token dfr == scalar dfr (test_frtok.py:56-70)
+    fr_s = torch.tensor([9.0], device=DEV, requires_grad=True)
+    fr_t = torch.full((2, 128, 4), 9.0, device=DEV, requires_grad=True)
+    a = S.kv_scan_g(k, v, g, fr_s, 32, t1, G=8, hard=True, detach_addr=True, q=q, occ_bin=True)
+    b = S.kv_scan_g(k, v, g, fr_t, 32, t1, G=8, hard=True, detach_addr=True, q=q, occ_bin=True)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    w = [torch.randn_like(x) for x in a]
+    sum((x * wx).sum() for x, wx in zip(a, w)).backward()
+    sum((x * wx).sum() for x, wx in zip(b, w)).backward()
+    assert abs(fr_s.grad.item() - fr_t.grad.sum().item()) <= 1e-4 * max(abs(fr_s.grad.item()), 1e-9)
+    # output contract: float32, (B, ceil(T/G), H, N, D), snapshot 0 all zero (pre-write)
+    assert a[0].dtype == torch.float32 and a[0].shape == (2, 16, 4, 32, 16) and a[1].shape == (2, 16, 4, 32, 16)
+    assert a[0][:, 0].abs().max().item() == 0 and a[1][:, 0].abs().max().item() == 0
+    # G = 1 snapshots sampled every 8 == G = 8 snapshots, bitwise (test_sh.py:68-72 states it for the reference)
+    c = S.kv_scan_g(k, v, g, fr_s.detach(), 32, t1, G=1, hard=True, detach_addr=True, q=q, occ_bin=True)
+    assert torch.equal(c[0][:, ::8], a[0]) and torch.equal(c[1][:, ::8], a[1])
+    # python-float temp and (1,) tensor temp are the same call
+    e = S.kv_scan_g(k, v, g, 9.0, 32, 16.0, G=8, hard=True, detach_addr=True, q=q, occ_bin=True)
+    assert torch.equal(e[0], a[0])
+    # run-to-run bitwise determinism, gradients included
+    def once():
+        kk, vv, gg = (x.clone().requires_grad_() for x in (k, v, g))
+        tt = t1.clone().requires_grad_()
+        kb, vb = S.kv_scan_g(kk, vv, gg, fr_s.detach(), 32, tt, G=8, hard=True, detach_addr=True, q=None, occ_bin=False)
+        ((kb * w[0]).sum() + (vb * w[1]).sum()).backward()
+        return [kb, vb, kk.grad, vv.grad, gg.grad, tt.grad]
+    r1, r2 = once(), once()
+    assert all(torch.equal(x, y) for x, y in zip(r1, r2))
+    # no fallbacks: CPU tensors and the modes that are not built raise
+    with pytest.raises(RuntimeError):
+        S.kv_scan_g(inp["k"], inp["v"], inp["gate"], 9.0, 32, 16.0, G=8, hard=True, detach_addr=True)
+    with pytest.raises(NotImplementedError):
+        S.kv_scan_g(k, v, g, 9.0, 32, t1, G=8, hard=False, detach_addr=True)
+    with pytest.raises(ValueError):
+        S.kv_scan_g(k[..., :12].contiguous(), v, g, 9.0, 32, t1, G=8, hard=True, detach_addr=True)   # DK = 12
+
+
+def test_full_size_properties():
+    """The benchmark configuration itself (B=64, T=1024, H=6, N=192, D=128, G=8, bf16): properties that need no oracle."""
+    import slotscan_b200 as S
+    B, T, H, N, D, G = 64, 1024, 6, 192, 128, 8
+    inp = make_inputs("bench", B, T, H, D, D, seed=0)
+    k, q, v = (inp[n].to(DEV, torch.bfloat16) for n in ("k", "q", "v"))
+    g, fr = inp["gate"].to(DEV), inp["fr"].to(DEV)
+    lg = S.scan_with_log(k, v, g, fr, N, 16.0, G=G, q=q, occ_bin=True, out_dtype=torch.bfloat16)
+    kb, vb, addr = lg["kbuf"], lg["vbuf"], lg["addr"]
+    assert kb.shape == (B, T // G, H, N, D) and kb.dtype == torch.bfloat16
+    assert kb[:, 0].abs().max().item() == 0 and vb[:, 0].abs().max().item() == 0
+    assert int(addr.min()) >= 0 and int(addr.max()) < N
+    # between consecutive snapshots only rows addressed in that block may change
+    changed = (kb[:, 1:] != kb[:, :-1]).any(-1) | (vb[:, 1:] != vb[:, :-1]).any(-1)          # (B,NB-1,H,N)
+    hit = torch.zeros(B, T // G, H, N, dtype=torch.bool, device=DEV)
+    blk = torch.arange(T, device=DEV) // G
+    hit.index_put_((torch.arange(B, device=DEV)[:, None, None].expand(B, T, H), blk[None, :, None].expand(B, T, H),
+                    torch.arange(H, device=DEV)[None, None, :].expand(B, T, H), addr.long()),
+                   torch.ones((), dtype=torch.bool, device=DEV))
+    assert not (changed & ~hit[:, :-1]).any()
+    # batch sharding: a shard of the batch reproduces its slice bitwise (what the multi-GPU split relies on)
+    sub = S.scan_with_log(k[16:24], v[16:24], g[16:24], fr[16:24], N, 16.0, G=G, q=q[16:24], occ_bin=True,
+                          out_dtype=torch.bfloat16)
+    assert torch.equal(sub["kbuf"], kb[16:24]) and torch.equal(sub["vbuf"], vb[16:24]) and torch.equal(sub["addr"], addr[16:24])
+    # the scan is linear in v for fixed addresses (addresses never look at v): vbuf(2 v) == 2 vbuf(v) exactly in bf16
+    lg2 = S.scan_with_log(k[:8], (2 * v[:8]), g[:8], fr[:8], N, 16.0, G=G, q=q[:8], occ_bin=True, out_dtype=torch.bfloat16)
+    assert torch.equal(lg2["vbuf"], 2 * vb[:8]) and torch.equal(lg2["addr"], addr[:8])
+    del lg, lg2, sub, kb, vb, changed, hit
+    torch.cuda.empty_cache()
