@@ -1,0 +1,313 @@
+"""Benchmark of the slot-scan hot path: forward + backward of the hard-address scan at the sh25 training shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            this build's CUDA path
+    python bench.py --impl reference [...]                          the CPU implementation timed on the host cores
+    torchrun ... bench.py --gpus N ...                              one rank per GPU, batch-sharded (weak scaling)
+
+One step = one forward + backward pass of the scan over one batch (B=64 sequences x T=1024 tokens x 6 heads per GPU,
+N=192 slots, dk=dv=128, snapshot stride 8, bf16 token streams and snapshots, float32 state and accumulation), on
+seeded synthetic inputs with the benchmark's distributions.  Prints ONE JSON line:
+  value      tokens/s, whole job, inputs resident in HBM, device-timed (CUDA events, max over ranks)
+  e2e        the same through the public Python API with HOST (pinned) inputs: H2D of k,q,v,gate,fr and D2H of every
+             input gradient inside the timed region
+  roofline   the dominant kernel's algorithmic bytes / its event-timed duration against the measured HBM peak
+  cpu_baseline  the CPU oracle (C, OpenMP) on a bounded sample of the same workload, on this box's host cores
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "smal-memory-llm_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "slot-scan tokens/s per B200 (fwd+bwd, sh25 shape), % HBM roofline, 1/2/4/8 GPU"
+SHAPE = dict(B=64, T=1024, H=6, N=192, DK=128, DV=128, G=8)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes_per_token_head(N, DK, DV, G, e_in, e_s):
+    """Drop-in form, per token and head: forward reads k,q,v + gate,fr and writes the snapshots; backward re-reads the
+    inputs, reads the snapshot gradients and writes dk,dq,dv,dgate,dfr.  Logs and scratch are not counted."""
+    tok = (2 * DK + DV) * e_in + 8
+    snap = N * (DK + DV) * e_s / G
+    return dict(fwd=tok + snap, bwd=tok + snap + tok, total=3 * tok + 2 * snap, tok=tok, snap=snap)
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.thr = threading.Thread(target=self._read, daemon=True)
+            self.thr.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_host_inputs(B, T, H, DK, DV, seed, dist="bench"):
+    from tests.scan_cases import make_inputs
+    return make_inputs(dist, B, T, H, DK, DV, seed=seed)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_leg(steps, warmup, sample_B=2, threads=None, budget_s=90.0):
+    """The CPU implementation of the same path: the C oracle (float32, OpenMP over (sequence, head)), forward + backward,
+    on a bounded sample: `sample_B` sequences of the full T / H / N / D."""
+    import numpy as np
+    from oracle import oracle as O
+    if threads:
+        O.set_threads(threads)
+    s = SHAPE
+    inp = make_host_inputs(sample_B, s["T"], s["H"], s["DK"], s["DV"], seed=0)
+    kw = dict(N=s["N"], temp=16.0, G=s["G"], hard=True, q=inp["q"], occ_bin=True, dtype=np.float32)
+    NB = (s["T"] + s["G"] - 1) // s["G"]
+    rng = np.random.default_rng(7)
+    wk = rng.standard_normal((sample_B, NB, s["H"], s["N"], s["DK"]), dtype=np.float32)
+    wv = rng.standard_normal((sample_B, NB, s["H"], s["N"], s["DV"]), dtype=np.float32)
+
+    def step():
+        O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], **kw)
+        O.scan_bwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dkbuf=wk, dvbuf=wv, detach_addr=True, **kw)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:          # keep the whole run within minutes on a slow host
+            break
+    dt = time.perf_counter() - t0
+    steps = done
+    toks = sample_B * s["T"] * steps
+    return dict(value=toks / dt, ms_per_step=1e3 * dt / steps, cores=O.threads(), steps=steps,
+                sample="%d of %d sequences, full T=%d H=%d N=%d D=%d G=%d, float32, fwd+bwd" %
+                       (sample_B, s["B"], s["T"], s["H"], s["N"], s["DK"], s["G"]))
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    warmup = min(args.warmup, 1)
+    r = cpu_leg(max(1, args.steps), warmup)
+    steps = r["steps"]
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config1: slot-scan fwd+bwd, B=64 T=1024 H=6 N=192 dk=dv=128 G=8 (CPU sample: see cpu_baseline.sample)",
+                       "l2": "n/a (host)"},
+            "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+            "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+def run_gpu(args, rank, local_rank, world):
+    import torch
+    import slotscan_b200 as S
+    from slotscan_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: this build has no CPU path for the scan")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_on = world > 1
+    if dist_on:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    s = dict(SHAPE)
+    if args.B:
+        s["B"] = args.B
+    if args.T:
+        s["T"] = args.T
+    B, T, H, N, DK, DV, G = (s[n] for n in ("B", "T", "H", "N", "DK", "DV", "G"))
+    NB = (T + G - 1) // G
+    inp = make_host_inputs(B, T, H, DK, DV, seed=rank, dist=args.dist)       # each rank its own shard of the batch
+    bf = torch.bfloat16
+    host = {n: inp[n].to(bf).contiguous().pin_memory() for n in ("k", "q", "v")}
+    host.update({n: inp[n].float().contiguous().pin_memory() for n in ("gate", "fr")})
+    devin = {n: t.to(dev) for n, t in host.items()}
+    temp = torch.tensor([16.0], device=dev)
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    dkb = torch.randn(B, NB, H, N, DK, device=dev, dtype=bf, generator=gen)
+    dvb = torch.randn(B, NB, H, N, DV, device=dev, dtype=bf, generator=gen)
+
+    def step(x):
+        k, q, v = (x[n].detach().requires_grad_() for n in ("k", "q", "v"))
+        g, fr = x["gate"].detach().requires_grad_(), x["fr"].detach().requires_grad_()
+        tp = temp.detach().requires_grad_()
+        kb, vb = S.kv_scan_g(k, v, g, fr, N, tp, G=G, hard=True, hard_gate=False, detach_addr=True, q=q, occ_bin=True,
+                             out_dtype=bf)
+        torch.autograd.backward([kb, vb], [dkb, dvb])
+        return k.grad, q.grad, v.grad, g.grad, fr.grad, tp.grad
+
+    def barrier():
+        if dist_on:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(devin)
+    barrier()
+    # ---- device-timed leg: inputs resident in HBM ----
+    _lib.profile_enable(True)
+    _lib.profile_read()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step(devin)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    prof = _lib.profile_read()
+    _lib.profile_enable(False)
+    # ---- end-to-end leg: host inputs in, input gradients out, every step ----
+    hout = None
+    def e2e_step():
+        nonlocal hout
+        x = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
+        grads = step(x)
+        if hout is None:
+            hout = [torch.empty(g_.shape, dtype=g_.dtype).pin_memory() for g_ in grads]
+        for h_, g_ in zip(hout, grads):
+            h_.copy_(g_, non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller holds the gradients on the host
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in hout)
+    if dist_on:
+        tt = torch.tensor([ms, ms_e2e], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    if rank == 0:
+        toks = B * T * world * args.steps
+        ab = algorithmic_bytes_per_token_head(N, DK, DV, G, 2, 2)
+        peak, peak_kind = hbm_peak()
+        # bytes each kernel is responsible for, per token and head (sums to ab["total"])
+        kb_bytes = {"addr_fwd": 2 * DK * 2 + 8, "replay_rows_k": N * DK * 2 / G, "replay_rows_v": DV * 2 + N * DV * 2 / G,
+                    "rows_bwd_k": DK * 2 + N * DK * 2 / G + DK * 2, "rows_bwd_v": DV * 2 + N * DV * 2 / G + DV * 2,
+                    "addr_bwd": DK * 2 + 8 + DK * 2 + 8, "finish": 0}
+        launches = sum(c for c, _ in prof.values())
+        kern = {n: {"launches": c, "ms_per_launch": (t / c if c else None), "share": t / max(sum(x for _, x in prof.values()), 1e-9)}
+                for n, (c, t) in prof.items()}
+        top = max(prof, key=lambda n: prof[n][1])
+        top_ms = prof[top][1] / max(prof[top][0], 1)
+        top_bytes = kb_bytes[top] * B * T * H
+        achieved = top_bytes / (top_ms * 1e-3) / 1e9
+        step_gbs = ab["total"] * H * B * T / (ms / args.steps * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32 state/accumulate, bf16 streams+snapshots", "data": "synthetic",
+                "config": {"workload": "config1: slot-scan fwd+bwd, B=%d/GPU T=%d H=%d N=%d dk=dv=%d G=%d, hard+detached, "
+                                       "occ_bin, per-token fr, separate write query, dist=%s" % (B, T, H, N, DK, G, args.dist),
+                           "global_batch": B * world, "seq_len": T, "sharding": "batch, no collective",
+                           "l2": "working set %.1f GB per step >> 126 MB L2 (no flush needed)" % (ab["total"] * H * B * T / 1e9)},
+                "e2e": {"value": toks / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": launches,
+                "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                             "frac": achieved / peak, "peak_kind": peak_kind, "traffic": TRAFFIC.get(top),
+                             "algorithmic_bytes_per_launch": top_bytes,
+                             "step": {"algorithmic_bytes": ab["total"] * H * B * T, "achieved": step_gbs, "frac": step_gbs / peak}},
+                "kernels": kern,
+                "clocks": clk.summary()}
+        if world == 1 and not args.no_cpu:
+            r = cpu_leg(1, 0)
+            line["cpu_baseline"] = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under profiles/
+TRAFFIC = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--B", type=int, default=0, help="sequences per GPU (default 64)")
+    ap.add_argument("--T", type=int, default=0, help="tokens per sequence (default 1024)")
+    ap.add_argument("--dist", default="bench", help="input distribution: bench (the benchmark's) | fill (every slot used) | clustered")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_gpu(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -85,7 +85,8 @@ size_t slotscan_hard_bwd_scratch_bytes(const slotscan_params* p);
 
 /* Backward of slotscan_hard_fwd for upstream gradients dkbuf, dvbuf (snap_dtype; either may be NULL = zeros).
  * Replaces _KVScanC.backward (gqa25/slotkern_cuda.py:514-533: rows_bwd :209-261 + addr_bwd :264-443).
- * Outputs: dk, dv (in_dtype), dq (in_dtype; NULL iff q is NULL, its gradient is then added into dk),
+ * Outputs: dk, dv, dq (in_dtype; dq is always required: with q NULL it receives the search-path part, which is
+ * then also added into dk),
  * dgate (B,T,H) f32, dfr (B,T,H) f32 or 1 float, dtemp 1 float.  The scalar sums are reduced in a fixed order:
  * results are bitwise repeatable (the reference uses float atomics, slotkern_cuda.py:440-441). */
 int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
@@ -100,6 +101,18 @@ typedef struct {
     int32_t regs, local_bytes, static_smem, max_threads;
 } slotscan_kernel_attr;
 int slotscan_query_attrs(slotscan_kernel_attr* out, int cap);
+
+/* Per-kernel device timing for benchmarks: while enabled, every launch made by this library is bracketed by CUDA
+ * events on the stream it is launched on.  slotscan_profile_read waits for those events, fills per kernel the number
+ * of launches and the summed device time since the last read (HOST memory, up to `cap` entries), clears the record
+ * and returns the number of kernels.  The reference measures the same way from Python (kvu/prof_cuda.py:9-20). */
+typedef struct {
+    char name[48];
+    int32_t launches;
+    float total_ms;
+} slotscan_kernel_time;
+int slotscan_profile_enable(int on);
+int slotscan_profile_read(slotscan_kernel_time* out, int cap);
 
 int slotscan_abi_version(void);
 

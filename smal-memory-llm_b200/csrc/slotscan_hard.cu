@@ -16,6 +16,9 @@
 #include <math.h>
 #include <stdio.h>
 
+#include <mutex>
+#include <vector>
+
 #include "slotscan_common.cuh"
 
 namespace slotscan {
@@ -255,15 +258,16 @@ __global__ void __launch_bounds__(SEQ_THREADS) addr_bwd_kernel(
     float* __restrict__ dfr, float* __restrict__ part /* [2][B*H]: dtemp, scalar dfr */) {
     extern __shared__ __align__(16) float smem[];
     const int N = p.N, DK = p.DK, T = p.T, H = p.H;
+    const int NP = (N + 3) & ~3;                         // keeps rq (read as float4) 16-byte aligned for any N
     float* K = smem;
     float* o = K + (size_t)N * DK;
-    float* kinv = o + N;
-    float* dO = kinv + N;
-    float* sv = dO + N;
-    float* zv = sv + N;
-    float* dwv = zv + N;
-    int* tf = reinterpret_cast<int*>(dwv + N);
-    float* rq = reinterpret_cast<float*>(tf + N);        // [2][SEQ_WARPS][DK]
+    float* kinv = o + NP;
+    float* dO = kinv + NP;
+    float* sv = dO + NP;
+    float* zv = sv + NP;
+    float* dwv = zv + NP;
+    int* tf = reinterpret_cast<int*>(dwv + NP);
+    float* rq = reinterpret_cast<float*>(tf + NP);       // [2][SEQ_WARPS][DK]
     __shared__ float r_m[2][SEQ_WARPS], r_s[2][SEQ_WARPS], r_sd[2][SEQ_WARPS], r_ez[2][SEQ_WARPS], r_ed[2][SEQ_WARPS];
     __shared__ int r_e[2][SEQ_WARPS];
     __shared__ float r_fr[2][SEQ_WARPS], r_dt[SEQ_WARPS];
@@ -419,9 +423,28 @@ __global__ void add_into_kernel(Tin* __restrict__ dst, const Tin* __restrict__ s
 }
 
 // ------------------------------------------------------------------------------------------------------
+// Optional per-kernel timing (slotscan_profile_*): CUDA events recorded on the launching stream around each launch.
+struct ProfRec { int id; cudaEvent_t a, b; };
+static bool g_prof_on = false;
+static std::vector<ProfRec> g_prof;
+static std::mutex g_prof_mu;
+enum { K_ADDR_FWD = 0, K_REPLAY_K, K_REPLAY_V, K_ROWS_BWD_K, K_ROWS_BWD_V, K_ADDR_BWD, K_FINISH, K_NKERN };
+static const char* const K_NAMES[K_NKERN] = {"addr_fwd", "replay_rows_k", "replay_rows_v", "rows_bwd_k", "rows_bwd_v",
+                                             "addr_bwd", "finish"};
+struct ProfScope {
+    int id; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; bool on;
+    ProfScope(int id_, cudaStream_t st_) : id(id_), st(st_), on(g_prof_on) {
+        if (on) { cudaEventCreate(&a); cudaEventCreate(&b); cudaEventRecord(a, st); }
+    }
+    ~ProfScope() {
+        if (on) { cudaEventRecord(b, st); std::lock_guard<std::mutex> l(g_prof_mu); g_prof.push_back({id, a, b}); }
+    }
+};
+
 static size_t addr_fwd_smem(const slotscan_params* p) { return sizeof(float) * ((size_t)p->N * p->DK + 2 * (size_t)p->N); }
 static size_t addr_bwd_smem(const slotscan_params* p) {
-    return sizeof(float) * ((size_t)p->N * p->DK + 8 * (size_t)p->N + 2 * (size_t)SEQ_WARPS * p->DK);
+    const size_t NP = ((size_t)p->N + 3) & ~(size_t)3;
+    return sizeof(float) * ((size_t)p->N * p->DK + 7 * NP + 2 * (size_t)SEQ_WARPS * p->DK);
 }
 constexpr size_t SMEM_CAP = 227 * 1024;
 
@@ -470,12 +493,21 @@ static cudaError_t fwd_typed(const slotscan_params& p, const void* k, const void
     const size_t sm = addr_fwd_smem(&p);
     cudaError_t e = opt_in_smem(addr_fwd_kernel<Tin>, sm);
     if (e != cudaSuccess) return e;
-    addr_fwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), (const Tin*)k, gate, fr, temp,
-                                                             L.addr, L.oold, L.ofin, L.tfirst);
+    {
+        ProfScope ps(K_ADDR_FWD, st);
+        addr_fwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), (const Tin*)k, gate, fr, temp,
+                                                                 L.addr, L.oold, L.ofin, L.tfirst);
+    }
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    DISPATCH_D(p.DK, e = (launch_replay<DD, Tin, Tsn>(p, k, gate, L.addr, kbuf, L.kold, L.kfin, st)));
+    {
+        ProfScope ps(K_REPLAY_K, st);
+        DISPATCH_D(p.DK, e = (launch_replay<DD, Tin, Tsn>(p, k, gate, L.addr, kbuf, L.kold, L.kfin, st)));
+    }
     if (e != cudaSuccess) return e;
-    DISPATCH_D(p.DV, e = (launch_replay<DD, Tin, Tsn>(p, v, gate, L.addr, vbuf, L.vold, L.vfin, st)));
+    {
+        ProfScope ps(K_REPLAY_V, st);
+        DISPATCH_D(p.DV, e = (launch_replay<DD, Tin, Tsn>(p, v, gate, L.addr, vbuf, L.vold, L.vfin, st)));
+    }
     return e;
 }
 
@@ -485,18 +517,28 @@ static cudaError_t bwd_typed(const slotscan_params& p, const void* k, const void
                              const void* dvbuf, float* Dn, float* part, void* dk, void* dq, void* dv, float* dgate,
                              float* dfr, float* dtemp, cudaStream_t st) {
     cudaError_t e;
-    DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, false, k, gate, L.addr, L.kold, L.kfin, L.tfirst, dkbuf, dk, Dn, st)));
+    {
+        ProfScope ps(K_ROWS_BWD_K, st);
+        DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, false, k, gate, L.addr, L.kold, L.kfin, L.tfirst, dkbuf, dk, Dn, st)));
+    }
     if (e != cudaSuccess) return e;
-    DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, true, v, gate, L.addr, L.vold, L.vfin, L.tfirst, dvbuf, dv, Dn, st)));
+    {
+        ProfScope ps(K_ROWS_BWD_V, st);
+        DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, true, v, gate, L.addr, L.vold, L.vfin, L.tfirst, dvbuf, dv, Dn, st)));
+    }
     if (e != cudaSuccess) return e;
     const size_t sm = addr_bwd_smem(&p);
     if ((e = opt_in_smem(addr_bwd_kernel<Tin>, sm)) != cudaSuccess) return e;
-    // q == NULL: the search query is the stored key; its gradient lands in a scratch-free way by writing dq into
-    // dk's own buffer is impossible (dk is already final), so the caller gives a dq buffer in that case too.
-    addr_bwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), gate, fr, temp, L.addr, L.kold,
-                                                             L.oold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq, dgate, dfr,
-                                                             part);
+    // q == NULL: the search query is the stored key.  dq is still a separate buffer (dk is written by another
+    // kernel); the two are summed into dk at the end.
+    {
+        ProfScope ps(K_ADDR_BWD, st);
+        addr_bwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), gate, fr, temp, L.addr,
+                                                                 L.kold, L.oold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq,
+                                                                 dgate, dfr, part);
+    }
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    ProfScope ps(K_FINISH, st);
     finish_scalars_kernel<<<1, 32, 0, st>>>(part, p.B * p.H, p.fr_per_token, dtemp, dfr);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (q == nullptr) {
@@ -617,4 +659,32 @@ extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     fill_attr(out, cap, n, "addr_bwd<f32>", addr_bwd_kernel<float>);
     fill_attr(out, cap, n, "addr_bwd<bf16>", addr_bwd_kernel<__nv_bfloat16>);
     return n;
+}
+
+extern "C" int slotscan_profile_enable(int on) {
+    std::lock_guard<std::mutex> l(g_prof_mu);
+    g_prof_on = on != 0;
+    return 0;
+}
+
+extern "C" int slotscan_profile_read(slotscan_kernel_time* out, int cap) {
+    std::lock_guard<std::mutex> l(g_prof_mu);
+    float ms[K_NKERN] = {0};
+    int cnt[K_NKERN] = {0};
+    for (auto& r : g_prof) {
+        float t = 0.f;
+        if (cudaEventSynchronize(r.b) == cudaSuccess && cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) {
+            ms[r.id] += t;
+            cnt[r.id]++;
+        }
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
+    g_prof.clear();
+    for (int i = 0; i < K_NKERN && i < cap; i++) {
+        snprintf(out[i].name, sizeof(out[i].name), "%s", K_NAMES[i]);
+        out[i].launches = cnt[i];
+        out[i].total_ms = ms[i];
+    }
+    return K_NKERN;
 }

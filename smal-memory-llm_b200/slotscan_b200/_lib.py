@@ -29,6 +29,10 @@ class KernelAttr(ctypes.Structure):
                 ("static_smem", ctypes.c_int32), ("max_threads", ctypes.c_int32)]
 
 
+class KernelTime(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 48), ("launches", ctypes.c_int32), ("total_ms", ctypes.c_float)]
+
+
 _lib = None
 
 
@@ -50,7 +54,9 @@ def lib():
         L.slotscan_hard_bwd_scratch_bytes.restype = sz
         L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
-        for f in ("slotscan_check", "slotscan_hard_fwd", "slotscan_hard_bwd", "slotscan_query_attrs"):
+        L.slotscan_profile_enable.argtypes = [ci]
+        L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]
+        for f in ("slotscan_profile_enable", "slotscan_profile_read", "slotscan_check", "slotscan_hard_fwd", "slotscan_hard_bwd", "slotscan_query_attrs"):
             getattr(L, f).restype = ci
         assert L.slotscan_abi_version() == 1, "libslotscan.so / Python host ABI mismatch"
         _lib = L
@@ -72,3 +78,15 @@ def kernel_attrs():
     n = lib().slotscan_query_attrs(buf, 32)
     return {buf[i].name.decode(): (buf[i].regs, buf[i].local_bytes, buf[i].static_smem, buf[i].max_threads)
             for i in range(min(n, 32))}
+
+
+def profile_enable(on=True):
+    """Bracket every kernel launch of the library with CUDA events (on the launching stream) until switched off."""
+    lib().slotscan_profile_enable(int(bool(on)))
+
+
+def profile_read():
+    """{kernel: (launches, total device ms)} since the last read; waits for the recorded events."""
+    buf = (KernelTime * 16)()
+    n = lib().slotscan_profile_read(buf, 16)
+    return {buf[i].name.decode(): (buf[i].launches, buf[i].total_ms) for i in range(min(n, 16))}
