@@ -119,10 +119,27 @@ def test_fp32_mode_vs_float64_oracle(case):
 BF16_CASES = [c for c in CASES if c[0] in ("sh25_main", "sh25_enc", "sh25_main_clustered", "t1000_d64", "dk_ne_dv")]
 
 
+def _bf16(x):
+    return torch.as_tensor(np.asarray(x, np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+def _bf16_storage_close(out, ref, scale=1.0):
+    """A bf16-typed output against the oracle: bf16 keeps 8 significant bits (unit round-off 2^-8 = 3.9e-3), so the
+    stored number cannot sit within rtol 2e-3 of the exact one.  What can be asked is that it is the oracle's value
+    in the same storage format: equal to the bf16-rounded oracle value up to one bf16 ulp (float32 round-off can
+    tip a value across a rounding boundary), plus the absolute 2e-3 (of the tensor's scale)."""
+    r = _bf16(ref)
+    ulp = np.abs(r) * 2.0 ** -7
+    err = np.abs(np.asarray(out, np.float64) - r) - (ulp + 2e-3 * scale)
+    return bool((err <= 0).all()), float(err.max())
+
+
 @pytest.mark.parametrize("case", BF16_CASES, ids=[c[0] for c in BF16_CASES])
 def test_bf16_storage_mode(case):
     """bf16 token streams, bf16 snapshots and bf16 upstream gradients, float32 state and accumulation.  The oracle
-    gets the same bf16-rounded inputs, so what is compared is the arithmetic: rtol = atol = 2e-3."""
+    gets the same bf16-rounded inputs, so what is compared is the arithmetic.  float32-typed results (final slot
+    state, dgate, dfr, dtemp) at rtol = atol = 2e-3; bf16-typed results (snapshots, dk, dq, dv) against the oracle
+    value in the same storage format (see _bf16_storage_close)."""
     name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq = case
     inp = make_inputs(dist, B, T, H, DK, DV, seed=300 + len(name), frtok=frtok, sepq=sepq)
     for n in ("k", "q", "v"):
@@ -140,14 +157,25 @@ def test_bf16_storage_mode(case):
     out = run_cuda(inp, N, G, hard_gate, occ_bin, wk=wk, wv=wv, dtype=torch.bfloat16, out_dtype=torch.bfloat16)
     gr = O.scan_bwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dkbuf=wk, dvbuf=wv, detach_addr=True, dtype=np.float64, **kw)
     m5, m4, m3 = keep[:, None, :, None, None], keep[:, None, :, None], keep[:, None, :]
-    for n, m in (("kbuf", m5), ("vbuf", m5)):
-        okc, worst = allclose_report(out[n] * m, ref[n] * m, 2e-3, 2e-3)
+    # the final slot state is float32 in every mode: the tolerance asked of the bf16 configuration, with room to spare
+    for n in ("kfin", "vfin"):
+        okc, worst = allclose_report(lg[n].reshape(ref[n].shape)[keep], ref[n][keep], 2e-3, 2e-3)
         assert okc, (n, worst)
-    for n, m in (("dk", m4), ("dv", m4), ("dq", m4), ("dgate", m3), ("dfr", m3)):
-        if n in out and out[n].shape == gr[n].shape:
+    for n, m in (("kbuf", m5), ("vbuf", m5)):
+        okc, worst = _bf16_storage_close(out[n] * m, ref[n] * m)
+        assert okc, (n, worst)
+    for n, m in (("dk", m4), ("dv", m4), ("dq", m4)):
+        if n in out:
+            scale = max(np.abs(gr[n]).max(), 1e-30)
+            okc, worst = _bf16_storage_close(out[n] * m, gr[n] * m, scale)
+            assert okc, (n, worst / scale)
+    for n in ("dgate", "dfr"):
+        if out[n].shape == gr[n].shape:
             scale = max(np.abs(gr[n]).max(), 1e-30)          # gradients are compared relative to their own max
-            okc, worst = allclose_report(out[n] * m / scale, gr[n] * m / scale, 2e-3, 2e-3)
+            okc, worst = allclose_report(out[n] * m3 / scale, gr[n] * m3 / scale, 2e-3, 2e-3)
             assert okc, (n, worst)
+    if keep.all():
+        assert rel_to_max(out["dtemp"], gr["dtemp"]) < 2e-3
 
 
 def test_edges_and_contract():
