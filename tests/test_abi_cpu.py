@@ -1,0 +1,86 @@
+"""CPU-side checks of the boundary: the C-ABI library loads and exports every function include/slotscan.h declares,
+argument validation rejects bad shapes without touching a GPU, the Python host mirrors the reference signatures, and
+the product refuses to run without CUDA (no fallback)."""
+import ctypes
+import inspect
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    src = open(os.path.join(ROOT, "include", "slotscan.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(slotscan_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    from slotscan_b200 import _lib
+    L = _lib.lib()
+    names = declared_functions()
+    assert len(names) >= 10, names
+    for n in names:
+        assert hasattr(L, n), "libslotscan.so does not export %s" % n
+    assert L.slotscan_abi_version() == 1
+
+
+def test_argument_validation_needs_no_gpu():
+    from slotscan_b200 import _lib
+    L = _lib.lib()
+    ok = _lib.Params(2, 16, 3, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
+    assert L.slotscan_check(ctypes.byref(ok)) == 0
+    for field, val in (("DK", 12), ("DV", 256), ("N", 0), ("G", 0), ("in_dtype", 7), ("N", 20000)):
+        p = _lib.Params(2, 16, 3, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
+        setattr(p, field, val)
+        assert L.slotscan_check(ctypes.byref(p)) < 0, field
+    assert L.slotscan_check(None) == -1
+    assert L.slotscan_hard_bwd_scratch_bytes(ctypes.byref(ok)) >= 4 * 2 * 3 * 16 * 12
+    # NULL pointers are refused before any launch
+    assert L.slotscan_hard_fwd(ctypes.byref(ok), None, None, None, None, None, None, None, None, None, None) == -1
+
+
+def test_python_host_mirrors_reference_signatures():
+    import slotscan_b200 as S
+    import slotkern_cuda, slotkern_kvg                                   # the drop-in module names
+    want = ["k", "v", "gate", "fr", "N", "temp", "G", "hard", "hard_gate", "eps", "detach_addr", "q", "nw", "nwb", "occ_bin"]
+    for fn in (S.kv_scan_g, S.kv_scan_c, slotkern_cuda.kv_scan_c, slotkern_kvg.kv_scan_g):
+        ps = list(inspect.signature(fn).parameters)
+        assert ps[:len(want)] == want, ps                               # gqa25/slotkern_kvg.py:257, slotkern_cuda.py:536
+        d = {n: p.default for n, p in inspect.signature(fn).parameters.items()}
+        assert d["G"] == 16 and d["hard"] is False and d["eps"] == 1e-4 and d["q"] is None and d["occ_bin"] is False
+    ps = list(inspect.signature(S.scan_kv).parameters)                  # gqa25/slotkern_kv.py:29
+    assert ps == ["k", "v", "gate", "fr", "N", "temp", "G", "hard", "hard_gate", "eps", "detach_addr", "q"]
+    assert inspect.signature(S.scan_kv).parameters["G"].default == 1
+
+
+def test_no_cpu_fallback():
+    import slotscan_b200 as S
+    k = torch.randn(1, 8, 2, 16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        S.kv_scan_g(k, k, torch.rand(1, 8, 2), 1.0, 4, 16.0, G=4, hard=True, detach_addr=True)
+
+
+def test_product_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "smal-memory-llm_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("the CPU oracle lives in the test tree", ""), os.path.join(dirpath, f)
+
+
+def test_custom_op_has_fake_kernel_for_compiled_callers():
+    """The reference calls its scan from torch.compile'd blocks (gqa25/train_sh.py:783-793): the op must trace on
+    meta tensors without a graph break."""
+    from slotscan_b200 import ops
+    k = torch.empty(2, 16, 3, 32, device="meta")
+    g = torch.empty(2, 16, 3, device="meta")
+    t1 = torch.empty(1, device="meta")
+    out = torch.ops.slotscan.hard_fwd(k, k, k, g, g, t1, 24, 8, False, 1e-4, True, True)
+    assert out[0].shape == (2, 2, 3, 24, 32) and out[0].dtype == torch.bfloat16 and out[2].dtype == torch.int32
+    gr = torch.ops.slotscan.hard_bwd(k, k, k, g, g, t1, *out[2:], out[0], out[1], 24, 8, False, 1e-4, True, True)
+    assert gr[0].shape == k.shape and gr[5].shape == (1,)
