@@ -94,6 +94,27 @@ int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, co
                       const void* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq, void* dv,
                       float* dgate, float* dfr, float* dtemp, void* stream);
 
+/* The same backward for callers that cannot supply scratch memory.  [No counterpart in the reference: its host side
+ * always allocates through torch.]  Meant for hosts whose device memory is already fully assigned (a server that
+ * handed everything to its own arena, a binding with no device allocator) or that must not make a synchronising
+ * allocation on this path.  The table D[t,n] and the partial sums live in ONE fixed array of
+ * SLOTSCAN_NOALLOC_SCRATCH_BYTES inside the library (each GPU that loads the library holds that much until the process
+ * exits).  Arguments and results are those of slotscan_hard_bwd without `scratch`; results are bit-identical to it.
+ *   - Limit: slotscan_hard_bwd_scratch_bytes(p) must not exceed the capacity, i.e. roughly B*H*T*N <= 2 M table
+ *     entries; beyond that the call returns SLOTSCAN_E_TOO_LARGE and launches nothing.
+ *   - The call itself allocates no device memory and frees none.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside any stream capture.
+ *   - Every call on a device shares the one array, which still holds the previous call's table: nothing in it needs
+ *     clearing, but two calls whose kernels overlap on the GPU (different streams, or threads) would overwrite each
+ *     other's table.  Keep calls to this entry point ordered on one stream per device. */
+#define SLOTSCAN_NOALLOC_SCRATCH_BYTES (8u << 20)
+size_t slotscan_hard_bwd_noalloc_capacity(void);
+int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
+                              const float* fr, const float* temp, const slotscan_log* log, const void* dkbuf,
+                              const void* dvbuf, void* dk, void* dq, void* dv, float* dgate, float* dfr, float* dtemp,
+                              void* stream);
+
 /* Registers / spilled bytes / static shared memory / max threads of each kernel, the analogue of kernel_attrs
  * (gqa25/slotkern_cuda.py:467-479).  Fills up to `cap` entries (HOST memory), returns how many kernels exist. */
 typedef struct {

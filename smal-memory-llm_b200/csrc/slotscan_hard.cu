@@ -688,3 +688,47 @@ extern "C" int slotscan_profile_read(slotscan_kernel_time* out, int cap) {
     }
     return K_NKERN;
 }
+
+// ------------------------------------------------------------------------------------------------------
+// Backward without caller scratch.  Some hosts cannot hand this library a scratch buffer: a serving process that
+// gave every byte of device memory to its own arena at start-up, a thin foreign-language binding that has no device
+// allocator to call, a code path in which a synchronising cudaMalloc / cudaFree is not acceptable.  For them the
+// table D[t,n] and the per-sequence partial sums live in a fixed array inside the library image.
+//
+// The array's name is only a host-side handle for the symbol; the device address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static __device__ __align__(256) unsigned char g_fixed_scratch[SLOTSCAN_NOALLOC_SCRATCH_BYTES];
+constexpr int MAX_DEVICES = 64;
+static void* g_fixed_scratch_addr[MAX_DEVICES] = {nullptr};
+static std::mutex g_fixed_scratch_mu;
+
+extern "C" size_t slotscan_hard_bwd_noalloc_capacity(void) { return (size_t)SLOTSCAN_NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k, const void* q, const void* v,
+                                         const float* gate, const float* fr, const float* temp, const slotscan_log* log,
+                                         const void* dkbuf, const void* dvbuf, void* dk, void* dq, void* dv, float* dgate,
+                                         float* dfr, float* dtemp, void* stream) {
+    int rc = slotscan_check(p);
+    if (rc) return rc;
+    if (slotscan_hard_bwd_scratch_bytes(p) > (size_t)SLOTSCAN_NOALLOC_SCRATCH_BYTES) return SLOTSCAN_E_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return SLOTSCAN_E_SHAPE;
+    void* scratch;
+    {
+        std::lock_guard<std::mutex> l(g_fixed_scratch_mu);
+        if (g_fixed_scratch_addr[dev] == nullptr) {          // first call on this device: resolve the symbol
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
+            if (e != cudaSuccess) return (int)e;
+            if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+            g_fixed_scratch_addr[dev] = ptr;
+        }
+        scratch = g_fixed_scratch_addr[dev];
+    }
+    // Nothing in the scratch has to start at zero: every D[t,n] and every partial sum that is read was written earlier
+    // in the same call (the key pass stores D, the value pass adds to it, the address pass reads it).
+    return slotscan_hard_bwd(p, k, q, v, gate, fr, temp, log, dkbuf, dvbuf, scratch, (size_t)SLOTSCAN_NOALLOC_SCRATCH_BYTES,
+                             dk, dq, dv, dgate, dfr, dtemp, stream);
+}

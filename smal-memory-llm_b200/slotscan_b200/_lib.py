@@ -53,6 +53,9 @@ def lib():
         L.slotscan_hard_bwd_scratch_bytes.argtypes = [PP]
         L.slotscan_hard_bwd_scratch_bytes.restype = sz
         L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
+        L.slotscan_hard_bwd_noalloc.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.slotscan_hard_bwd_noalloc.restype = ci
+        L.slotscan_hard_bwd_noalloc_capacity.restype = sz
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
         L.slotscan_profile_enable.argtypes = [ci]
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]
