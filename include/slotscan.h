@@ -57,6 +57,7 @@ int slotscan_check(const slotscan_params* p);
 /* Log of one forward call: what the backward (and a caller that streams chunks) needs.  All caller-allocated.
  *   addr   (B,T,H) int32   the row each token wrote                 [reference: `am`, slotkern_cuda.py:502]
  *   oold   (B,T,H) f32     that row's occupancy before the write    [`oold` :503]
+ *   kiold  (B,T,H) f32     1 / max(|key row|, 1e-6) of that row before the write
  *   kold   (B,T,H,DK) f32, vold (B,T,H,DV) f32   the row before the write   [`kold`, `vold` :503]
  *   kfin   (B*H,N,DK) f32, vfin (B*H,N,DV) f32, ofin (B*H,N) f32    state after the last token  [:504]
  *   tfirst (B*H,N) int32   first token at which row n could be addressed (T if never): rows are taken in index
@@ -70,6 +71,7 @@ typedef struct {
     float* vfin;
     float* ofin;
     int32_t* tfirst;
+    float* kiold;
 } slotscan_log;
 
 /* Forward: hard (argmax) address, address reads the stored keys as constants.

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "slotscan_common.cuh"
+#include "slotscan_addr_fwd.cuh"
 
 namespace slotscan {
 
@@ -453,6 +454,25 @@ static cudaError_t opt_in_smem(F f, size_t bytes) {
     return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
+template <int DK, typename Tin>
+static cudaError_t launch_addr_fwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
+                                   const float* fr, const float* temp, const slotscan_log& L, cudaStream_t st) {
+    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK).total;
+    cudaError_t e;
+    if (p.N <= 192) {
+        auto kern = addr_fwd_chunked_kernel<DK, 6, Tin>;
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
+                                                L.ofin, L.tfirst);
+    } else {
+        auto kern = addr_fwd_chunked_kernel<DK, 14, Tin>;
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
+                                                L.ofin, L.tfirst);
+    }
+    return cudaGetLastError();
+}
+
 template <int D, typename Tin, typename Tsn>
 static cudaError_t launch_replay(const slotscan_params& p, const void* x, const float* gate, const int* am, void* xbuf,
                                  float* xold, float* xfin, cudaStream_t st) {
@@ -490,14 +510,12 @@ template <typename Tin, typename Tsn>
 static cudaError_t fwd_typed(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
                              const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
                              cudaStream_t st) {
-    const size_t sm = addr_fwd_smem(&p);
-    cudaError_t e = opt_in_smem(addr_fwd_kernel<Tin>, sm);
-    if (e != cudaSuccess) return e;
+    cudaError_t e;
     {
         ProfScope ps(K_ADDR_FWD, st);
-        addr_fwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), (const Tin*)k, gate, fr, temp,
-                                                                 L.addr, L.oold, L.ofin, L.tfirst);
+        DISPATCH_D(p.DK, e = (launch_addr_fwd<DD, Tin>(p, q ? q : k, k, gate, fr, temp, L, st)));
     }
+    if (e != cudaSuccess) return e;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     {
         ProfScope ps(K_REPLAY_K, st);
@@ -563,6 +581,7 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (p->DK < 8 || p->DK > 128 || (p->DK & (p->DK - 1))) return SLOTSCAN_E_SHAPE;
     if (p->DV < 8 || p->DV > 128 || (p->DV & (p->DV - 1))) return SLOTSCAN_E_SHAPE;
     if (addr_bwd_smem(p) + 1024 > SMEM_CAP) return SLOTSCAN_E_SHAPE;
+    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK).total + 1024 > SMEM_CAP || p->N > 448) return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
     if (p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
     if (p->snap_dtype != SLOTSCAN_F32 && p->snap_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
@@ -575,7 +594,8 @@ extern "C" int slotscan_hard_fwd(const slotscan_params* p, const void* k, const 
     int rc = slotscan_check(p);
     if (rc) return rc;
     if (!k || !v || !gate || !fr || !temp || !kbuf || !vbuf || !log) return SLOTSCAN_E_NULL;
-    if (!log->addr || !log->oold || !log->kold || !log->vold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst)
+    if (!log->addr || !log->oold || !log->kold || !log->vold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst ||
+        !log->kiold)
         return SLOTSCAN_E_NULL;
     if (misaligned(k) || misaligned(q) || misaligned(v) || misaligned(kbuf) || misaligned(vbuf) || misaligned(log->kold) ||
         misaligned(log->vold) || misaligned(log->kfin) || misaligned(log->vfin))
@@ -608,7 +628,8 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
     if (rc) return rc;
     if (!k || !v || !gate || !fr || !temp || !log || !scratch || !dk || !dq || !dv || !dgate || !dfr || !dtemp)
         return SLOTSCAN_E_NULL;
-    if (!log->addr || !log->oold || !log->kold || !log->vold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst)
+    if (!log->addr || !log->oold || !log->kold || !log->vold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst ||
+        !log->kiold)
         return SLOTSCAN_E_NULL;
     if (scratch_bytes < slotscan_hard_bwd_scratch_bytes(p)) return SLOTSCAN_E_SHAPE;
     if (misaligned(k) || misaligned(q) || misaligned(v) || misaligned(dkbuf) || misaligned(dvbuf) || misaligned(dk) ||
@@ -650,8 +671,8 @@ static void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* na
 
 extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     int n = 0;
-    fill_attr(out, cap, n, "addr_fwd<f32>", addr_fwd_kernel<float>);
-    fill_attr(out, cap, n, "addr_fwd<bf16>", addr_fwd_kernel<__nv_bfloat16>);
+    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_chunked_kernel<128, 6, float>);
+    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_chunked_kernel<128, 6, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float>);
     fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);

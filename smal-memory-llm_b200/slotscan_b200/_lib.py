@@ -21,7 +21,7 @@ class Params(ctypes.Structure):
 
 class Log(ctypes.Structure):
     """slotscan_log of include/slotscan.h."""
-    _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst")]
+    _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")]
 
 
 class KernelAttr(ctypes.Structure):

@@ -39,9 +39,10 @@ def _require_cuda(*ts):
 def hard_fwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
              temp: torch.Tensor, N: int, G: int, hard_gate: bool, eps: float, occ_bin: bool,
              snap_bf16: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
-                                       torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+                                       torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                                       torch.Tensor]:
     """k, q, v: contiguous f32 or bf16 (same dtype); gate, fr, temp: contiguous f32.
-    Returns kbuf, vbuf, then the log: addr, oold, kold, vold, kfin, vfin, ofin, tfirst (include/slotscan.h)."""
+    Returns kbuf, vbuf, then the log: addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold (include/slotscan.h)."""
     _require_cuda(k, q, v, gate, fr, temp)
     B, T, H, DK = k.shape
     DV = v.shape[-1]
@@ -54,13 +55,14 @@ def hard_fwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: 
     kold, vold = e(B, T, H, DK), e(B, T, H, DV)
     kfin, vfin, ofin = e(B * H, N, DK), e(B * H, N, DV), e(B * H, N)
     tfirst = e(B * H, N, dt=torch.int32)
+    kiold = e(B, T, H)
     p = _params(k, v, gate, fr, N, G, hard_gate, eps, occ_bin, sdt)
-    log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst)))
+    log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold)))
     with torch.cuda.device(dev):
         rc = _lib.lib().slotscan_hard_fwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
                                           _ptr(kbuf), _ptr(vbuf), ctypes.byref(log), _stream(dev))
     _lib.check(rc, "slotscan_hard_fwd")
-    return kbuf, vbuf, addr, oold, kold, vold, kfin, vfin, ofin, tfirst
+    return kbuf, vbuf, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold
 
 
 @hard_fwd.register_fake
@@ -71,13 +73,14 @@ def _(k, q, v, gate, fr, temp, N, G, hard_gate, eps, occ_bin, snap_bf16):
     sdt = torch.bfloat16 if snap_bf16 else torch.float32
     e = lambda *s, dt=torch.float32: k.new_empty(s, dtype=dt)
     return (e(B, NB, H, N, DK, dt=sdt), e(B, NB, H, N, DV, dt=sdt), e(B, T, H, dt=torch.int32), e(B, T, H),
-            e(B, T, H, DK), e(B, T, H, DV), e(B * H, N, DK), e(B * H, N, DV), e(B * H, N), e(B * H, N, dt=torch.int32))
+            e(B, T, H, DK), e(B, T, H, DV), e(B * H, N, DK), e(B * H, N, DV), e(B * H, N), e(B * H, N, dt=torch.int32),
+            e(B, T, H))
 
 
 @torch.library.custom_op("slotscan::hard_bwd", mutates_args=())
 def hard_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
              temp: torch.Tensor, addr: torch.Tensor, oold: torch.Tensor, kold: torch.Tensor, vold: torch.Tensor,
-             kfin: torch.Tensor, vfin: torch.Tensor, ofin: torch.Tensor, tfirst: torch.Tensor,
+             kfin: torch.Tensor, vfin: torch.Tensor, ofin: torch.Tensor, tfirst: torch.Tensor, kiold: torch.Tensor,
              dkbuf: Optional[torch.Tensor], dvbuf: Optional[torch.Tensor], N: int, G: int, hard_gate: bool,
              eps: float, occ_bin: bool, snap_bf16: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor,
                                                                    torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -94,7 +97,7 @@ def hard_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: 
     dgate = torch.empty(gate.shape, device=dev, dtype=torch.float32)
     dfr = torch.empty(fr.shape, device=dev, dtype=torch.float32)
     dtemp = torch.empty(1, device=dev, dtype=torch.float32)
-    log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst)))
+    log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold)))
     with torch.cuda.device(dev):
         rc = L.slotscan_hard_bwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
                                  ctypes.byref(log), _ptr(dkbuf), _ptr(dvbuf), _ptr(scratch), nbytes, _ptr(dk), _ptr(dq),
@@ -104,8 +107,8 @@ def hard_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: 
 
 
 @hard_bwd.register_fake
-def _(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, dkbuf, dvbuf, N, G, hard_gate, eps,
-      occ_bin, snap_bf16):
+def _(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold, dkbuf, dvbuf, N, G, hard_gate,
+      eps, occ_bin, snap_bf16):
     f = lambda t: t.new_empty(t.shape, dtype=torch.float32)
     return torch.empty_like(k), torch.empty_like(k), torch.empty_like(v), f(gate), f(fr), gate.new_empty(1)
 
@@ -118,12 +121,12 @@ def _setup(ctx, inputs, output):
 
 
 def _backward(ctx, dkbuf, dvbuf, *unused):
-    k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst = ctx.saved_tensors
+    k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold = ctx.saved_tensors
     N, G, hard_gate, eps, occ_bin, snap_bf16 = ctx.meta
     sdt = torch.bfloat16 if snap_bf16 else torch.float32
     c = lambda g: None if g is None else g.contiguous().to(sdt)
     dk, dq, dv, dgate, dfr, dtemp = hard_bwd(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst,
-                                             c(dkbuf), c(dvbuf), N, G, hard_gate, eps, occ_bin, snap_bf16)
+                                             kiold, c(dkbuf), c(dvbuf), N, G, hard_gate, eps, occ_bin, snap_bf16)
     return dk, (None if q is None else dq), dv, dgate, dfr, dtemp, None, None, None, None, None, None
 
 

@@ -76,5 +76,5 @@ def scan_with_log(k, v, gate, fr, N, temp, G=16, hard_gate=False, eps=1e-4, q=No
     with torch.no_grad():
         out = ops.hard_fwd(conv(k), None if q is None else conv(q), conv(v), _as_f32(gate), fr_, temp_, int(N), int(G),
                            bool(hard_gate), float(eps), bool(occ_bin), out_dtype == torch.bfloat16)
-    names = ("kbuf", "vbuf", "addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst")
+    names = ("kbuf", "vbuf", "addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")
     return dict(zip(names, out))

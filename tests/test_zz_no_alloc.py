@@ -36,7 +36,7 @@ def _both_backwards(tensors, lg, N, G, seed):
     B, T, H, DK = k.shape
     temp = torch.tensor([16.0], device=DEV)
     p = _lib.Params(B, T, H, N, DK, v.shape[-1], G, 0, 1, 1, _lib.F32, _lib.F32, 1e-4)
-    log = _lib.Log(*(lg[n].data_ptr() for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst")))
+    log = _lib.Log(*(lg[n].data_ptr() for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")))
     gen = torch.Generator(device=DEV).manual_seed(seed)
     dkb = torch.randn(lg["kbuf"].shape, device=DEV, generator=gen)
     dvb = torch.randn(lg["vbuf"].shape, device=DEV, generator=gen)
@@ -81,7 +81,7 @@ def test_noalloc_backward_refuses_what_does_not_fit():
     p = _lib.Params(64, 1024, 6, 192, 128, 128, 8, 0, 1, 1, _lib.F32, _lib.F32, 1e-4)      # table of 75 M entries
     assert L.slotscan_hard_bwd_scratch_bytes(ctypes.byref(p)) > L.slotscan_hard_bwd_noalloc_capacity()
     one = torch.zeros(64, device=DEV)
-    log = _lib.Log(*([one.data_ptr()] * 8))
+    log = _lib.Log(*([one.data_ptr()] * 9))
     rc = L.slotscan_hard_bwd_noalloc(ctypes.byref(p), *([_ptr(one)] * 6), ctypes.byref(log), None, None,
                                      *([_ptr(one)] * 6), None)
     assert rc == -6                                                                         # SLOTSCAN_E_TOO_LARGE
