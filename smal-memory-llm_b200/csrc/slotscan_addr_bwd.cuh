@@ -1,0 +1,363 @@
+// Backward of the address: dgate, dfr, dtemp, dq.  [reference addr_bwd, slotkern_cuda.py:264-443]
+//
+// With every address known from the log, nothing here is sequential inside a chunk of CH = 8 tokens: one CTA per
+// (sequence, head) walks the chunks from last to first, keeps the key rows in shared memory as f32 and per chunk
+//   0. restores the rows the chunk wrote (undo log) -> K is the state BEFORE the chunk's first token, and forms
+//      delta_i = g_i (k_i - kold_i), the change token i made to its row;
+//   1. score phase (all warps): St[n][j] = <K_n, q_j> for every candidate row and the 8 queries, plus the 8x8 table
+//      PD[i][j] = <delta_i, q_j>; the score of token j against a row rewritten earlier in the chunk is
+//      St[n][j] + sum_{i<j, a_i = n} PD[i][j] by linearity;
+//   2. softmax adjoint (warp j = token j): z over the candidate rows, softmax statistics by warp reductions,
+//      dw = D[t,n] (+ (1-o) dO when the penalty is on o itself), dz_n = asoft_n (g dw_n - sum_m asoft_m g dw_m),
+//      dgate = dw[a_t], dfr = -sum occ dz, dtemp += sum dz s / temp; C[n][j] = dz temp kinv_n overwrites St;
+//   3. query gradient (warp w = 16 output columns): dqn_j = sum_n C[n][j] K_n + sum_{i<j} C[a_i][j] delta_i, then
+//      dq_j = qinv (dqn_j - qn_j <qn_j, dqn_j>).
+// Norms and occupancies before each write come from the forward log (kiold, oold), so the scores rebuilt here are the
+// numbers the forward decided on.
+#pragma once
+#include "slotscan_addr_fwd.cuh"
+
+namespace slotscan {
+
+struct AddrBwdSmem {
+    int K, kinv, o, Qc, Dl, St, PD, misc, total;
+    int qstride;
+};
+__host__ __device__ inline AddrBwdSmem addr_bwd_layout(int N, int DK) {
+    AddrBwdSmem L;
+    const int NP = (N + 3) & ~3;
+    L.qstride = DK + 4;
+    L.K = 0;
+    L.kinv = L.K + N * DK;
+    L.o = L.kinv + NP;
+    L.Qc = L.o + NP;
+    L.Dl = L.Qc + CH * L.qstride;
+    L.St = L.Dl + CH * DK;
+    L.PD = L.St + CH * N;
+    L.misc = L.PD + CH * CH;     // qinv g fr oold kiold (8 each) | am (8) | pr[8 warps][8] | red[8]
+    L.total = L.misc + 6 * CH + CH * AF_WARPS + 8;
+    return L;
+}
+
+template <int DK, int RPL, bool OCCB, typename Tin>
+__global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
+    const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
+    const float* __restrict__ fr, const float* __restrict__ temp_p, const int* __restrict__ am_in,
+    const float* __restrict__ kold, const float* __restrict__ oold_in, const float* __restrict__ kiold_in,
+    const float* __restrict__ kfin, const float* __restrict__ ofin, const int* __restrict__ tfirst,
+    const float* __restrict__ Din, Tin* __restrict__ dq, float* __restrict__ dg, float* __restrict__ dfr,
+    float* __restrict__ part /* [2][B*H]: dtemp, scalar dfr */) {
+    extern __shared__ __align__(16) float smem[];
+    constexpr int NI = (DK + 15) / 16;
+    constexpr int IPS = CH * DK / 8;                    // 8-element items per stream and chunk
+    constexpr int NITEM = (3 * IPS + AF_THREADS - 1) / AF_THREADS;   // q, k, kold items per thread
+    const int N = p.N, T = p.T, H = p.H;
+    const AddrBwdSmem L = addr_bwd_layout(N, DK);
+    float* K = smem + L.K;
+    float* s_kinv = smem + L.kinv;
+    float* s_o = smem + L.o;
+    float* Qc = smem + L.Qc;
+    float* Dl = smem + L.Dl;
+    float* St = smem + L.St;
+    float* PD = smem + L.PD;
+    float* s_qinv = smem + L.misc;
+    float* s_g = s_qinv + CH;
+    float* s_fr = s_g + CH;
+    float* s_oold = s_fr + CH;
+    float* s_kiold = s_oold + CH;
+    int* s_am = reinterpret_cast<int*>(s_kiold + CH);
+    float* s_pr = reinterpret_cast<float*>(s_am + CH);  // [AF_WARPS][CH] partial <qn, dqn>
+    float* s_red = s_pr + CH * AF_WARPS;
+
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pj = lane & 7, pp = lane >> 3;
+    const float temp = temp_p[0], eps = p.eps;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int i = tid; i < N * DK; i += AF_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
+    for (int i = tid; i < N; i += AF_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
+    __syncthreads();
+    for (int n = warp; n < N; n += AF_WARPS) {          // norms of the final state
+        const int col = lane * 4;
+        const float4 Kn = (col < DK) ? ld4(K + (size_t)n * DK + col) : zero4;
+        const float nsq = warp_sum(dot4(Kn, Kn));
+        if (lane == 0) s_kinv[n] = fminf(rsqrtf(nsq), 1e6f);
+    }
+    // candidates at token t: rows n with tfirst[n] <= t; uniform, walked down as t decreases
+    int lim = N - 1;
+    float dtemp_acc = 0.f, dfr_acc = 0.f;
+    float dO_r[RPL];                                      // only used when the penalty is on o itself (!OCCB)
+#pragma unroll
+    for (int i = 0; i < RPL; i++) dO_r[i] = 0.f;
+
+    // ---- chunk loader: items 0..IPS-1 = q, IPS..2IPS-1 = k, 2IPS..3IPS-1 = kold (always f32) ----
+    Pre8<Tin> pre_q[NITEM];
+    Pre8<float> pre_o[NITEM];
+    float pre_s = 0.f;
+    int pre_i = 0;
+#define AB_ITEM(R, S_, J_, C_)                                   \
+    const int id_ = tid + (R) * AF_THREADS;                      \
+    const int S_ = id_ / IPS, rr_ = id_ % IPS, J_ = rr_ / (DK / 8), C_ = (rr_ % (DK / 8)) * 8;
+#define AB_ISSUE_LOADS(T0)                                                                                   \
+    {                                                                                                        \
+        _Pragma("unroll") for (int r = 0; r < NITEM; r++) {                                                  \
+            AB_ITEM(r, s_, j_, c_)                                                                           \
+            const int t_ = (T0) + j_;                                                                        \
+            const size_t ix_ = ((size_t)b * T + t_) * H + h;                                                 \
+            if (s_ < 2) { if (t_ < T && t_ >= 0) pre_q[r].load((s_ ? k : q) + ix_ * DK + c_); else pre_q[r].zero(); } \
+            else if (s_ == 2) { if (t_ < T && t_ >= 0) pre_o[r].load(kold + ix_ * DK + c_); else pre_o[r].zero(); }   \
+        }                                                                                                    \
+        if (tid < 4 * CH) {                                                                                  \
+            const int tt_ = (T0) + (tid & (CH - 1)), w_ = tid / CH;                                          \
+            const size_t ix_ = ((size_t)b * T + tt_) * H + h;                                                \
+            const bool in_ = tt_ < T && tt_ >= 0;                                                            \
+            if (w_ == 0) pre_s = in_ ? gate_eff(gate[ix_], p.hard_gate) : 0.f;                               \
+            else if (w_ == 1) pre_s = in_ ? (p.fr_per_token ? fr[ix_] : fr[0]) : 0.f;                        \
+            else if (w_ == 2) pre_s = in_ ? oold_in[ix_] : 0.f;                                              \
+            else pre_s = in_ ? kiold_in[ix_] : 0.f;                                                          \
+        }                                                                                                    \
+        if (tid >= 4 * CH && tid < 5 * CH) {                                                                 \
+            const int tt_ = (T0) + (tid & (CH - 1));                                                         \
+            pre_i = (tt_ < T && tt_ >= 0) ? am_in[((size_t)b * T + tt_) * H + h] : -1;                       \
+        }                                                                                                    \
+    }
+
+    // first chunk = the last tokens
+    const int nchunk = (T + CH - 1) / CH;
+    AB_ISSUE_LOADS((nchunk - 1) * CH);
+    __syncthreads();
+
+    for (int ck = nchunk - 1; ck >= 0; ck--) {
+        const int t0 = ck * CH, cn = min(CH, T - t0);
+        // ---- land the chunk's scalars, then its rows ----
+        if (tid < CH) s_g[tid] = pre_s;
+        else if (tid < 2 * CH) s_fr[tid - CH] = pre_s;
+        else if (tid < 3 * CH) s_oold[tid - 2 * CH] = pre_s;
+        else if (tid < 4 * CH) s_kiold[tid - 3 * CH] = pre_s;
+        else if (tid < 5 * CH) s_am[tid - 4 * CH] = pre_i;
+        // q -> Qc; k is parked in Dl until kold arrives
+#pragma unroll
+        for (int r = 0; r < NITEM; r++) {
+            AB_ITEM(r, s_, j_, c_)
+            if (s_ == 0) pre_q[r].store(Qc + j_ * L.qstride + c_);
+            else if (s_ == 1) pre_q[r].store(Dl + j_ * DK + c_);
+        }
+        __syncthreads();
+        // kold: delta_j = g_j (k_j - kold_j) into Dl, and the row restore for the EARLIEST hit of each row
+#pragma unroll
+        for (int r = 0; r < NITEM; r++) {
+            AB_ITEM(r, s_, j_, c_)
+            if (s_ == 2 && j_ < cn) {
+                const int a = s_am[j_];
+                const float g = s_g[j_];
+                bool first = true;
+                for (int j2 = 0; j2 < j_; j2++) first = first && (s_am[j2] != a);
+                float* dl = Dl + j_ * DK + c_;
+                const float4 k0 = ld4(dl), k1 = ld4(dl + 4);
+                const float4 o0 = pre_o[r].a, o1 = pre_o[r].b;
+                st4(dl, make_float4(g * (k0.x - o0.x), g * (k0.y - o0.y), g * (k0.z - o0.z), g * (k0.w - o0.w)));
+                st4(dl + 4, make_float4(g * (k1.x - o1.x), g * (k1.y - o1.y), g * (k1.z - o1.z), g * (k1.w - o1.w)));
+                if (first) pre_o[r].store(K + (size_t)a * DK + c_);
+            }
+        }
+        if (ck > 0) AB_ISSUE_LOADS((ck - 1) * CH);       // the next (earlier) chunk's loads fly from here on
+        // candidate limit at the chunk's last token
+        {
+            const int tl = t0 + cn - 1;
+            while (lim > 0 && tfirst[(size_t)bh * N + lim] > tl) lim--;
+        }
+        __syncthreads();
+        // ---------------- score phase ----------------
+        {
+            float4 Qr[NI];
+#pragma unroll
+            for (int i = 0; i < NI; i++) {
+                const int d0 = i * 16 + pp * 4;
+                Qr[i] = (d0 < DK) ? ld4(Qc + pj * L.qstride + d0) : zero4;
+            }
+            if (warp == 0) {
+                float qq = 0.f;
+#pragma unroll
+                for (int i = 0; i < NI; i++) qq += dot4(Qr[i], Qr[i]);
+                qq += __shfl_xor_sync(FULL, qq, 8);
+                qq += __shfl_xor_sync(FULL, qq, 16);
+                if (pp == 0) s_qinv[pj] = fminf(rsqrtf(qq), 1e6f);
+            }
+            const int rows = lim + 1;
+            for (int n = warp; n < rows + CH; n += AF_WARPS) {
+                const bool is_d = n >= rows;
+                const float* row = is_d ? (Dl + (n - rows) * DK) : (K + (size_t)n * DK);
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < NI; i++) {
+                    const int d0 = i * 16 + pp * 4;
+                    if (d0 < DK) {
+                        const float4 r4 = ld4(row + d0);
+                        if (i & 1) a1 += dot4(r4, Qr[i]); else a0 += dot4(r4, Qr[i]);
+                    }
+                }
+                float a = a0 + a1;
+                a += __shfl_xor_sync(FULL, a, 8);
+                a += __shfl_xor_sync(FULL, a, 16);
+                if (pp == 0) { if (is_d) PD[(n - rows) * CH + pj] = a; else St[n * CH + pj] = a; }
+            }
+        }
+        __syncthreads();
+        // ---------------- softmax adjoint: warp j handles token j (all tokens at once when OCCB) ----------------
+        {
+            int am_c[CH];
+            float oo_c[CH], ki_c[CH];
+#pragma unroll
+            for (int i = 0; i < CH; i++) { am_c[i] = (i < cn) ? s_am[i] : -1; oo_c[i] = s_oold[i]; ki_c[i] = s_kiold[i]; }
+            const int jlo = OCCB ? warp : 0, jhi = OCCB ? warp + 1 : cn;       // !OCCB: warp 0 walks the tokens in reverse
+            if (OCCB ? (warp < cn) : (warp == 0)) {
+                for (int jj = jhi - 1; jj >= jlo; jj--) {
+                    const int j = jj, t = t0 + j;
+                    int limj = lim;
+                    while (limj > 0 && tfirst[(size_t)bh * N + limj] > t) limj--;
+                    const float g = s_g[j], frv = s_fr[j], tq = temp * s_qinv[j];
+                    const int a = am_c[j];
+                    float sv[RPL], zv[RPL], dwv[RPL], kiv[RPL], occv[RPL];
+                    bool okv[RPL];
+                    int ei = BIGI;
+#pragma unroll
+                    for (int i = 0; i < RPL; i++) {
+                        const int n = lane + 32 * i;
+                        sv[i] = 0.f; zv[i] = -INFINITY; dwv[i] = 0.f; kiv[i] = 0.f; occv[i] = 0.f; okv[i] = false;
+                        if (32 * i <= limj && n <= limj) {
+                            float S = St[n * CH + j], ki = s_kinv[n], oc = s_o[n];
+                            bool got = false;
+#pragma unroll
+                            for (int i2 = 0; i2 < CH; i2++) {
+                                if (am_c[i2] == n) {
+                                    if (i2 < j) S += PD[i2 * CH + j];                       // rewritten earlier in the chunk
+                                    else if (!got) { ki = ki_c[i2]; oc = oo_c[i2]; got = true; }   // next write of this row
+                                }
+                            }
+                            const float s = tq * (ki * S);
+                            const float occ = OCCB ? (oc >= eps ? 1.f : 0.f) : oc;
+                            sv[i] = s; kiv[i] = ki; occv[i] = occ;
+                            zv[i] = s - frv * occ;
+                            okv[i] = oc >= eps;
+                            if (oc < eps && n < ei) ei = n;
+                            dwv[i] = Din[((size_t)bh * T + t) * N + n] + (OCCB ? 0.f : (1.f - oc) * dO_r[i]);
+                        }
+                    }
+                    ei = (int)__reduce_min_sync(FULL, (unsigned)ei);     // the lowest free row competes too
+                    float zmax;
+                    {
+                        unsigned kk = 0u;
+#pragma unroll
+                        for (int i = 0; i < RPL; i++) {
+                            if (lane + 32 * i == ei) okv[i] = true;
+                            if (okv[i]) kk = max(kk, ord_key(zv[i]));
+                        }
+                        kk = __reduce_max_sync(FULL, kk);
+                        zmax = __uint_as_float((kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk);   // inverse of ord_key
+                    }
+                    float se = 0.f, sd = 0.f, ev[RPL];
+#pragma unroll
+                    for (int i = 0; i < RPL; i++) {
+                        ev[i] = okv[i] ? __expf(zv[i] - zmax) : 0.f;
+                        se += ev[i]; sd += ev[i] * dwv[i];
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) {
+                        se += __shfl_xor_sync(FULL, se, off);
+                        sd += __shfl_xor_sync(FULL, sd, off);
+                    }
+                    const float sa = g * sd / se;                                  // sum_n asoft_n (g dw_n)
+                    float f1 = 0.f, f2 = 0.f;
+#pragma unroll
+                    for (int i = 0; i < RPL; i++) {
+                        const int n = lane + 32 * i;
+                        const float dz = okv[i] ? (ev[i] / se) * (g * dwv[i] - sa) : 0.f;
+                        f1 += -occv[i] * dz;
+                        f2 += dz * sv[i];
+                        if (32 * i <= limj && n <= limj) {
+                            St[n * CH + j] = dz * temp * kiv[i];                   // C[n][j]
+                            if (n == a) dg[((size_t)b * T + t) * H + h] = dwv[i];
+                            if (!OCCB) dO_r[i] = ((n == a) ? 1.f - g : 1.f) * dO_r[i] - frv * dz;
+                        } else if (32 * i <= lim && n <= lim) {
+                            St[n * CH + j] = 0.f;                                  // a row that was no candidate yet
+                        }
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) {
+                        f1 += __shfl_xor_sync(FULL, f1, off);
+                        f2 += __shfl_xor_sync(FULL, f2, off);
+                    }
+                    if (lane == 0) {
+                        if (p.fr_per_token) dfr[((size_t)b * T + t) * H + h] = f1; else dfr_acc += f1;
+                        dtemp_acc += f2 / temp;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // ---------------- query gradient: warp w owns 16 output columns, lane = (token j, 4 columns) ----------------
+        {
+            const int j = lane & 7, cc = (warp * 16) + (lane >> 3) * 4;           // column base of this lane
+            const bool act = cc < DK && j < cn;
+            float4 acc = zero4;
+            if (cc < DK) {
+                const int rows = lim + 1;
+                for (int n = 0; n < rows; n++) {
+                    const float c = St[n * CH + j];
+                    const float4 r4 = ld4(K + (size_t)n * DK + cc);
+                    acc.x += c * r4.x; acc.y += c * r4.y; acc.z += c * r4.z; acc.w += c * r4.w;
+                }
+#pragma unroll
+                for (int i = 0; i < CH; i++) {            // rows rewritten earlier in the chunk: K_n(t_j) = K_n + sum delta
+                    if (i < j && i < cn) {
+                        const float c = St[s_am[i] * CH + j];
+                        const float4 r4 = ld4(Dl + i * DK + cc);
+                        acc.x += c * r4.x; acc.y += c * r4.y; acc.z += c * r4.z; acc.w += c * r4.w;
+                    }
+                }
+            }
+            const float qi = s_qinv[j];
+            float4 qn = zero4;
+            if (cc < DK) { const float4 q4 = ld4(Qc + j * L.qstride + cc); qn = make_float4(q4.x * qi, q4.y * qi, q4.z * qi, q4.w * qi); }
+            float pr = dot4(acc, qn);
+            pr += __shfl_xor_sync(FULL, pr, 8);
+            pr += __shfl_xor_sync(FULL, pr, 16);                                   // over this warp's 16 columns
+            if ((lane >> 3) == 0) s_pr[warp * CH + j] = pr;
+            __syncthreads();
+            float prj = 0.f;
+#pragma unroll
+            for (int w = 0; w < AF_WARPS; w++) prj += s_pr[w * CH + j];            // fixed order: repeatable
+            if (act) {
+                const size_t ix = ((size_t)b * T + t0 + j) * H + h;
+                // qinv = 1e6 means |q| was under the 1e-6 clamp: no projection term (slotkern_cuda.py:422)
+                const bool clamped = qi >= 1e6f;
+                float4 out;
+                if (clamped) out = make_float4(qi * acc.x, qi * acc.y, qi * acc.z, qi * acc.w);
+                else out = make_float4(qi * (acc.x - qn.x * prj), qi * (acc.y - qn.y * prj), qi * (acc.z - qn.z * prj),
+                                       qi * (acc.w - qn.w * prj));
+                st4(dq + ix * DK + cc, out);
+            }
+        }
+        // ---- the norm / occupancy arrays go back to the state before the chunk ----
+        if (tid < cn) {
+            const int a = s_am[tid];
+            bool first = true;
+            for (int j2 = 0; j2 < tid; j2++) first = first && (s_am[j2] != a);
+            if (first) { s_kinv[a] = s_kiold[tid]; s_o[a] = s_oold[tid]; }
+        }
+        __syncthreads();
+    }
+#undef AB_ITEM
+#undef AB_ISSUE_LOADS
+    if (lane == 0) { s_pr[warp] = dtemp_acc; s_pr[AF_WARPS + warp] = dfr_acc; }
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.f, c = 0.f;
+        for (int w = 0; w < AF_WARPS; w++) { a += s_pr[w]; c += s_pr[AF_WARPS + w]; }
+        part[bh] = a;
+        part[(size_t)p.B * H + bh] = c;
+    }
+}
+
+}  // namespace slotscan

@@ -21,6 +21,7 @@
 
 #include "slotscan_common.cuh"
 #include "slotscan_addr_fwd.cuh"
+#include "slotscan_addr_bwd.cuh"
 
 namespace slotscan {
 
@@ -457,19 +458,44 @@ static cudaError_t opt_in_smem(F f, size_t bytes) {
 template <int DK, typename Tin>
 static cudaError_t launch_addr_fwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
                                    const float* fr, const float* temp, const slotscan_log& L, cudaStream_t st) {
-    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK).total;
+    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK, (int)sizeof(Tin)).total;
     cudaError_t e;
-    if (p.N <= 192) {
-        auto kern = addr_fwd_chunked_kernel<DK, 6, Tin>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
-                                                L.ofin, L.tfirst);
-    } else {
-        auto kern = addr_fwd_chunked_kernel<DK, 14, Tin>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
-                                                L.ofin, L.tfirst);
+#define AF_LAUNCH(RPL_, OCCB_)                                                                                     \
+    {                                                                                                              \
+        auto kern = addr_fwd_chunked_kernel<DK, RPL_, OCCB_, Tin>;                                                 \
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                  \
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold,   \
+                                                L.kiold, L.ofin, L.tfirst);                                        \
     }
+    if (p.N <= 192) {
+        if (p.occ_bin) AF_LAUNCH(6, true) else AF_LAUNCH(6, false)
+    } else {
+        if (p.occ_bin) AF_LAUNCH(14, true) else AF_LAUNCH(14, false)
+    }
+#undef AF_LAUNCH
+    return cudaGetLastError();
+}
+
+template <int DK, typename Tin>
+static cudaError_t launch_addr_bwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
+                                   const float* fr, const float* temp, const slotscan_log& L, const float* Dn, void* dq,
+                                   float* dgate, float* dfr, float* part, cudaStream_t st) {
+    const size_t sm = sizeof(float) * (size_t)addr_bwd_layout(p.N, DK).total;
+    cudaError_t e;
+#define AB_LAUNCH(RPL_, OCCB_)                                                                                      \
+    {                                                                                                               \
+        auto kern = addr_bwd_chunked_kernel<DK, RPL_, OCCB_, Tin>;                                                  \
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                   \
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.kold,    \
+                                                L.oold, L.kiold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq, dgate, dfr, \
+                                                part);                                                              \
+    }
+    if (p.N <= 192) {
+        if (p.occ_bin) AB_LAUNCH(6, true) else AB_LAUNCH(6, false)
+    } else {
+        if (p.occ_bin) AB_LAUNCH(14, true) else AB_LAUNCH(14, false)
+    }
+#undef AB_LAUNCH
     return cudaGetLastError();
 }
 
@@ -545,16 +571,11 @@ static cudaError_t bwd_typed(const slotscan_params& p, const void* k, const void
         DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, true, v, gate, L.addr, L.vold, L.vfin, L.tfirst, dvbuf, dv, Dn, st)));
     }
     if (e != cudaSuccess) return e;
-    const size_t sm = addr_bwd_smem(&p);
-    if ((e = opt_in_smem(addr_bwd_kernel<Tin>, sm)) != cudaSuccess) return e;
-    // q == NULL: the search query is the stored key.  dq is still a separate buffer (dk is written by another
-    // kernel); the two are summed into dk at the end.
     {
         ProfScope ps(K_ADDR_BWD, st);
-        addr_bwd_kernel<Tin><<<p.B * p.H, SEQ_THREADS, sm, st>>>(p, (const Tin*)(q ? q : k), gate, fr, temp, L.addr,
-                                                                 L.kold, L.oold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq,
-                                                                 dgate, dfr, part);
+        DISPATCH_D(p.DK, e = (launch_addr_bwd<DD, Tin>(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st)));
     }
+    if (e != cudaSuccess) return e;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     ProfScope ps(K_FINISH, st);
     finish_scalars_kernel<<<1, 32, 0, st>>>(part, p.B * p.H, p.fr_per_token, dtemp, dfr);
@@ -581,7 +602,8 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (p->DK < 8 || p->DK > 128 || (p->DK & (p->DK - 1))) return SLOTSCAN_E_SHAPE;
     if (p->DV < 8 || p->DV > 128 || (p->DV & (p->DV - 1))) return SLOTSCAN_E_SHAPE;
     if (addr_bwd_smem(p) + 1024 > SMEM_CAP) return SLOTSCAN_E_SHAPE;
-    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK).total + 1024 > SMEM_CAP || p->N > 448) return SLOTSCAN_E_SHAPE;
+    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK, 4).total + 1024 > SMEM_CAP || p->N > 448) return SLOTSCAN_E_SHAPE;
+    if (sizeof(float) * (size_t)addr_bwd_layout(p->N, p->DK).total + 1024 > SMEM_CAP) return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
     if (p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
     if (p->snap_dtype != SLOTSCAN_F32 && p->snap_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
@@ -671,14 +693,14 @@ static void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* na
 
 extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     int n = 0;
-    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_chunked_kernel<128, 6, float>);
-    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_chunked_kernel<128, 6, __nv_bfloat16>);
+    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_chunked_kernel<128, 6, true, float>);
+    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_chunked_kernel<128, 6, true, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float>);
     fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);
     fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float, false>);
-    fill_attr(out, cap, n, "addr_bwd<f32>", addr_bwd_kernel<float>);
-    fill_attr(out, cap, n, "addr_bwd<bf16>", addr_bwd_kernel<__nv_bfloat16>);
+    fill_attr(out, cap, n, "addr_bwd<128,f32>", addr_bwd_chunked_kernel<128, 6, true, float>);
+    fill_attr(out, cap, n, "addr_bwd<128,bf16>", addr_bwd_chunked_kernel<128, 6, true, __nv_bfloat16>);
     return n;
 }
 
@@ -753,3 +775,15 @@ extern "C" int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k
     return slotscan_hard_bwd(p, k, q, v, gate, fr, temp, log, dkbuf, dvbuf, scratch, (size_t)SLOTSCAN_NOALLOC_SCRATCH_BYTES,
                              dk, dq, dv, dgate, dfr, dtemp, stream);
 }
+
+#ifdef SLOTSCAN_PHASE_TIMING
+// development aid (not part of the ABI header): per-phase clock totals of the chunked kernels, summed over CTAs
+extern "C" int slotscan_debug_phase_cycles(unsigned long long* out8, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out8, slotscan::g_phase_cycles, 16 * sizeof(unsigned long long));
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[16] = {0};
+        e = cudaMemcpyToSymbol(slotscan::g_phase_cycles, z, sizeof(z));
+    }
+    return (int)e;
+}
+#endif
