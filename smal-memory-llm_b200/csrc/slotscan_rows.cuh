@@ -1,0 +1,221 @@
+// Row-parallel kernels of the hard-address scan: once the address log exists, every key row and every value row
+// evolves on its own (a row changes only at the tokens that addressed it).
+//
+//   replay_rows_kernel   forward: replays rows from the log, emits the stride-G snapshots, the undo log (the row
+//                        before each write) and the final state.                 [reference val_fwd, slotkern_cuda.py:178-206]
+//   rows_bwd_kernel      reverse: undoes rows from the undo log, carries dX <- (1-g) dX + dxbuf, emits dx_t = g dX_a and
+//                        the table D[t,n] = <x_t - X_n, dX_n>.                    [reference rows_bwd, :209-261]
+//
+// Layout: one group of LPR = D/8 lanes per row, 8 elements per lane in registers, RPB = 256 / LPR rows per CTA;
+// grid (B*H, row tiles).  Tokens are taken in chunks of RC = 64: the chunk's gates, a per-row bit mask of the tokens
+// that hit the row, and the chunk's token vectors are staged in shared memory once per CTA, so the walk over a chunk
+// is a walk over EVENTS (next hit, next snapshot) and never waits on a global load.  A tile whose rows are never
+// addressed (tfirst == T for all of them) only writes zeros (forward) or does nothing (reverse).
+#pragma once
+#include "slotscan_common.cuh"
+
+namespace slotscan {
+
+constexpr int ROW_THREADS = 256;
+constexpr int RC = 64;                        // tokens per staged chunk (one 64-bit hit mask per row)
+
+template <typename T>
+__device__ __forceinline__ void copy8(T* dst, const T* src);
+template <>
+__device__ __forceinline__ void copy8<float>(float* dst, const float* src) {
+    const float4 a = ld4(src), b = ld4(src + 4);
+    st4(dst, a); st4(dst + 4, b);
+}
+template <>
+__device__ __forceinline__ void copy8<__nv_bfloat16>(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+}
+
+// true if any row of this CTA's tile is ever a candidate (row 0 always is)
+__device__ __forceinline__ bool tile_active(const int* tfirst_bh, int n, bool live, int T, int* s_flag) {
+    if (threadIdx.x == 0) *s_flag = 0;
+    __syncthreads();
+    if (live && tfirst_bh[n] < T) *s_flag = 1;
+    __syncthreads();
+    return *s_flag != 0;
+}
+
+// stage one chunk: gates, per-row hit masks and (optionally) token vectors; the caller syncs afterwards
+template <int D, typename Tin>
+__device__ __forceinline__ void stage_chunk(const slotscan_params& p, int b, int h, int t0, int tc, int row0,
+                                            const float* __restrict__ gate, const int* __restrict__ am,
+                                            const Tin* __restrict__ x, float* s_g, unsigned long long* s_mask, Tin* s_x) {
+    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
+    const int tid = threadIdx.x, T = p.T, H = p.H;
+    for (int i = tid; i < RPB; i += ROW_THREADS) s_mask[i] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < tc; i += ROW_THREADS) {
+        const size_t ix = ((size_t)b * T + t0 + i) * H + h;
+        s_g[i] = gate_eff(gate[ix], p.hard_gate);
+        const int a = am[ix] - row0;
+        if (a >= 0 && a < RPB) atomicOr(&s_mask[a], 1ull << i);
+    }
+    for (int it = tid; it < tc * LPR; it += ROW_THREADS) {
+        const int j = it / LPR, cc = (it % LPR) * 8;
+        copy8<Tin>(s_x + j * D + cc, x + (((size_t)b * T + t0 + j) * H + h) * D + cc);
+    }
+}
+
+// ======================================================================================================
+template <int D, typename Tin, typename Tsn>
+__global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
+    const slotscan_params p, const Tin* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ am,
+    const int* __restrict__ tfirst, Tsn* __restrict__ xbuf, float* __restrict__ xold, float* __restrict__ xfin) {
+    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
+    __shared__ float s_g[RC];
+    __shared__ unsigned long long s_mask[RPB];
+    __shared__ __align__(16) Tin s_x[RC * D];
+    __shared__ int s_flag;
+    const int N = p.N, T = p.T, H = p.H, G = p.G;
+    const int NB = (T + G - 1) / G;
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int tid = threadIdx.x, r = tid / LPR, c = tid % LPR, row0 = blockIdx.y * RPB, n = row0 + r;
+    const bool live = n < N;
+    float X[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) X[j] = 0.f;
+    const size_t snap_stride = (size_t)H * N * D;                   // between consecutive snapshots of one sequence
+    Tsn* snap = xbuf + (((size_t)b * NB) * H + h) * N * D + (size_t)n * D + c * 8;
+
+    if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) {
+        if (live) {                                                  // never addressed: every snapshot is zero
+            for (int j = 0; j < NB; j++) st8(snap + j * snap_stride, X);
+            st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+        }
+        return;
+    }
+    int tsnap = 0;                                                   // next snapshot time (multiple of G)
+    for (int t0 = 0; t0 < T; t0 += RC) {
+        const int tc = min(RC, T - t0);
+        __syncthreads();
+        stage_chunk<D, Tin>(p, b, h, t0, tc, row0, gate, am, x, s_g, s_mask, s_x);
+        __syncthreads();
+        if (!live) continue;
+        const unsigned long long m = s_mask[r];
+        int i = 0;
+        while (true) {
+            const unsigned long long mm = m >> i;                    // i < tc <= 64 here
+            const int ih = mm ? i + __ffsll((long long)mm) - 1 : tc; // next token that writes this row
+            const int tlast = t0 + min(ih, tc - 1);
+            for (; tsnap <= tlast; tsnap += G) { st8(snap, X); snap += snap_stride; }   // pre-write copies
+            if (ih >= tc) break;
+            const size_t ix = ((size_t)b * T + t0 + ih) * H + h;
+            const float g = s_g[ih], omw = 1.f - g;
+            float xv[8];
+            ld8(xv, s_x + ih * D + c * 8);
+            st8(xold + ix * D + c * 8, X);
+#pragma unroll
+            for (int j = 0; j < 8; j++) X[j] = blend(X[j], xv[j], g, omw);
+            i = ih + 1;
+            if (i >= tc) break;
+        }
+    }
+    if (live) st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+}
+
+// ======================================================================================================
+// rows_bwd: reverse scan per row.  dX_n <- (1-w) dX_n + dxbuf;  dx_t = g dX_am;  D[t,n] (+)= <x_t - X_n, dX_n>.
+// A row stops at tfirst[n]: before that token it is neither written nor a candidate, so nothing reads its D.
+// Dynamic shared memory: the chunk's token vectors (Tin), the undo rows of the tokens that hit this tile (f32),
+// gates and hit masks.
+template <int D, typename Tin>
+__host__ __device__ constexpr size_t rows_bwd_smem_bytes() {
+    return (size_t)RC * D * sizeof(Tin) + (size_t)RC * D * sizeof(float) + RC * sizeof(float) +
+           (ROW_THREADS / (D / 8)) * sizeof(unsigned long long) + 16;
+}
+
+template <int D, typename Tin, typename Tsn, bool ACCUM>
+__global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
+    const slotscan_params p, const Tin* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ am,
+    const float* __restrict__ xold, const float* __restrict__ xfin, const int* __restrict__ tfirst,
+    const Tsn* __restrict__ dxbuf, Tin* __restrict__ dx, float* __restrict__ Dn) {
+    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
+    extern __shared__ __align__(16) unsigned char dsm[];
+    float* s_xo = reinterpret_cast<float*>(dsm);                                   // [RC][D] undo rows
+    Tin* s_x = reinterpret_cast<Tin*>(dsm + (size_t)RC * D * sizeof(float));       // [RC][D] token vectors
+    unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(dsm + (size_t)RC * D * (sizeof(float) + sizeof(Tin)));
+    float* s_g = reinterpret_cast<float*>(s_mask + RPB);
+    __shared__ int s_flag, s_stop;
+    const int N = p.N, T = p.T, H = p.H, G = p.G;
+    const int NB = (T + G - 1) / G;
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int tid = threadIdx.x, r = tid / LPR, c = tid % LPR, row0 = blockIdx.y * RPB, n0 = row0 + r;
+    const bool live = n0 < N;
+    const int n = live ? n0 : 0;          // dead rows still run the shuffles; they read row 0 and write nothing
+    if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) return;
+    const int tstop = live ? tfirst[(size_t)bh * N + n] : T;
+    const int wstop = __reduce_min_sync(FULL, tstop);      // every lane of a warp runs the same shuffle steps
+    if (tid == 0) s_stop = T;
+    __syncthreads();
+    if ((tid & 31) == 0) atomicMin(&s_stop, wstop);
+    __syncthreads();
+    const int cstop = s_stop;                               // the whole tile is done below this token
+    float X[8], dX[8];
+    ld8(X, xfin + ((size_t)bh * N + n) * D + c * 8);
+#pragma unroll
+    for (int j = 0; j < 8; j++) dX[j] = 0.f;
+    const size_t snap_stride = (size_t)H * N * D;
+    const Tsn* dsnap0 = (dxbuf == nullptr) ? nullptr : dxbuf + (((size_t)b * NB) * H + h) * N * D + (size_t)n * D + c * 8;
+    // the snapshot gradient of block jb is added when the walk passes t = jb * G; it is fetched one block ahead
+    int jb = NB - 1;
+    float nxt[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) nxt[j] = 0.f;
+    if (dsnap0 != nullptr && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+
+    const int nchunk = (T + RC - 1) / RC;
+    for (int ck = nchunk - 1; ck >= 0; ck--) {
+        const int t0 = ck * RC, tc = min(RC, T - t0);
+        if (t0 + tc <= cstop) break;                                               // uniform over the CTA
+        __syncthreads();
+        stage_chunk<D, Tin>(p, b, h, t0, tc, row0, gate, am, x, s_g, s_mask, s_x);
+        __syncthreads();
+        // undo rows of the tokens that hit this tile
+        for (int it = tid; it < tc * LPR; it += ROW_THREADS) {
+            const int j = it / LPR, cc = (it % LPR) * 8;
+            const int a = am[((size_t)b * T + t0 + j) * H + h] - row0;
+            if (a >= 0 && a < RPB) copy8<float>(s_xo + j * D + cc, xold + (((size_t)b * T + t0 + j) * H + h) * D + cc);
+        }
+        __syncthreads();
+        const unsigned long long m = live ? s_mask[r] : 0ull;
+        for (int i = tc - 1; i >= 0; i--) {
+            const int t = t0 + i;
+            if (t < wstop) break;
+            const bool on = t >= tstop;
+            const bool hit = on && ((m >> i) & 1ull);
+            float xv[8];
+            ld8(xv, s_x + i * D + c * 8);
+            if (hit) ld8(X, s_xo + i * D + c * 8);
+            float pacc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) pacc += (xv[j] - X[j]) * dX[j];
+            pacc = group_sum<LPR>(pacc);
+            if (on && c == 0) {
+                float* dst = Dn + ((size_t)bh * T + t) * N + n;
+                if (ACCUM) *dst += pacc; else *dst = pacc;
+            }
+            if (hit) {
+                const float g = s_g[i], omw = 1.f - g;
+                float a[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) { a[j] = g * dX[j]; dX[j] = omw * dX[j]; }
+                st8(dx + (((size_t)b * T + t) * H + h) * D + c * 8, a);
+            }
+            if (t == jb * G) {                                                     // pre-write state of block jb
+                if (on) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) dX[j] += nxt[j];
+                }
+                jb--;
+                if (dsnap0 != nullptr && jb >= 0 && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+            }
+        }
+    }
+}
+
+}  // namespace slotscan
