@@ -102,7 +102,7 @@ int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, co
  * allocation on this path.  The table D[t,n] and the partial sums live in ONE fixed array of
  * SLOTSCAN_NOALLOC_SCRATCH_BYTES inside the library (each GPU that loads the library holds that much until the process
  * exits).  Arguments and results are those of slotscan_hard_bwd without `scratch`; results are bit-identical to it.
- *   - Limit: slotscan_hard_bwd_scratch_bytes(p) must not exceed the capacity, i.e. roughly B*H*T*N <= 2 M table
+ *   - Limit: slotscan_hard_bwd_scratch_bytes(p) must not exceed the capacity, i.e. roughly B*H*T*N <= 1 M table
  *     entries; beyond that the call returns SLOTSCAN_E_TOO_LARGE and launches nothing.
  *   - The call itself allocates no device memory and frees none.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device

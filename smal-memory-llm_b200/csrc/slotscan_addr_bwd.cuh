@@ -19,6 +19,9 @@
 
 namespace slotscan {
 
+constexpr int AB_THREADS = 256;
+constexpr int AB_WARPS = AB_THREADS / 32;
+
 struct AddrBwdSmem {
     int K, kinv, o, Qc, Dl, St, PD, misc, total;
     int qstride;
@@ -35,12 +38,12 @@ __host__ __device__ inline AddrBwdSmem addr_bwd_layout(int N, int DK) {
     L.St = L.Dl + CH * DK;
     L.PD = L.St + CH * N;
     L.misc = L.PD + CH * CH;     // qinv g fr oold kiold (8 each) | am (8) | pr[8 warps][8] | red[8]
-    L.total = L.misc + 6 * CH + CH * AF_WARPS + 8;
+    L.total = L.misc + 6 * CH + CH * AB_WARPS + 8;
     return L;
 }
 
 template <int DK, int RPL, bool OCCB, typename Tin>
-__global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
+__global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, const int* __restrict__ am_in,
     const float* __restrict__ kold, const float* __restrict__ oold_in, const float* __restrict__ kiold_in,
@@ -50,7 +53,7 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
     extern __shared__ __align__(16) float smem[];
     constexpr int NI = (DK + 15) / 16;
     constexpr int IPS = CH * DK / 8;                    // 8-element items per stream and chunk
-    constexpr int NITEM = (3 * IPS + AF_THREADS - 1) / AF_THREADS;   // q, k, kold items per thread
+    constexpr int NITEM = (3 * IPS + AB_THREADS - 1) / AB_THREADS;   // q, k, kold items per thread
     const int N = p.N, T = p.T, H = p.H;
     const AddrBwdSmem L = addr_bwd_layout(N, DK);
     float* K = smem + L.K;
@@ -66,8 +69,8 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
     float* s_oold = s_fr + CH;
     float* s_kiold = s_oold + CH;
     int* s_am = reinterpret_cast<int*>(s_kiold + CH);
-    float* s_pr = reinterpret_cast<float*>(s_am + CH);  // [AF_WARPS][CH] partial <qn, dqn>
-    float* s_red = s_pr + CH * AF_WARPS;
+    float* s_pr = reinterpret_cast<float*>(s_am + CH);  // [AB_WARPS][CH] partial <qn, dqn>
+    float* s_red = s_pr + CH * AB_WARPS;
 
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -75,10 +78,10 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
     const float temp = temp_p[0], eps = p.eps;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    for (int i = tid; i < N * DK; i += AF_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
-    for (int i = tid; i < N; i += AF_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
+    for (int i = tid; i < N * DK; i += AB_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
+    for (int i = tid; i < N; i += AB_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
     __syncthreads();
-    for (int n = warp; n < N; n += AF_WARPS) {          // norms of the final state
+    for (int n = warp; n < N; n += AB_WARPS) {          // norms of the final state
         const int col = lane * 4;
         const float4 Kn = (col < DK) ? ld4(K + (size_t)n * DK + col) : zero4;
         const float nsq = warp_sum(dot4(Kn, Kn));
@@ -97,7 +100,7 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
     float pre_s = 0.f;
     int pre_i = 0;
 #define AB_ITEM(R, S_, J_, C_)                                   \
-    const int id_ = tid + (R) * AF_THREADS;                      \
+    const int id_ = tid + (R) * AB_THREADS;                      \
     const int S_ = id_ / IPS, rr_ = id_ % IPS, J_ = rr_ / (DK / 8), C_ = (rr_ % (DK / 8)) * 8;
 #define AB_ISSUE_LOADS(T0)                                                                                   \
     {                                                                                                        \
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
                 if (pp == 0) s_qinv[pj] = fminf(rsqrtf(qq), 1e6f);
             }
             const int rows = lim + 1;
-            for (int n = warp; n < rows + CH; n += AF_WARPS) {
+            for (int n = warp; n < rows + CH; n += AB_WARPS) {
                 const bool is_d = n >= rows;
                 const float* row = is_d ? (Dl + (n - rows) * DK) : (K + (size_t)n * DK);
                 float a0 = 0.f, a1 = 0.f;
@@ -218,71 +221,85 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
                     while (limj > 0 && tfirst[(size_t)bh * N + limj] > t) limj--;
                     const float g = s_g[j], frv = s_fr[j], tq = temp * s_qinv[j];
                     const int a = am_c[j];
-                    float sv[RPL], zv[RPL], dwv[RPL], kiv[RPL], occv[RPL];
-                    bool okv[RPL];
-                    int ei = BIGI;
-#pragma unroll
-                    for (int i = 0; i < RPL; i++) {
-                        const int n = lane + 32 * i;
-                        sv[i] = 0.f; zv[i] = -INFINITY; dwv[i] = 0.f; kiv[i] = 0.f; occv[i] = 0.f; okv[i] = false;
-                        if (32 * i <= limj && n <= limj) {
-                            float S = St[n * CH + j], ki = s_kinv[n], oc = s_o[n];
-                            bool got = false;
-#pragma unroll
-                            for (int i2 = 0; i2 < CH; i2++) {
-                                if (am_c[i2] == n) {
-                                    if (i2 < j) S += PD[i2 * CH + j];                       // rewritten earlier in the chunk
-                                    else if (!got) { ki = ki_c[i2]; oc = oo_c[i2]; got = true; }   // next write of this row
-                                }
-                            }
-                            const float s = tq * (ki * S);
-                            const float occ = OCCB ? (oc >= eps ? 1.f : 0.f) : oc;
-                            sv[i] = s; kiv[i] = ki; occv[i] = occ;
-                            zv[i] = s - frv * occ;
-                            okv[i] = oc >= eps;
-                            if (oc < eps && n < ei) ei = n;
-                            dwv[i] = Din[((size_t)bh * T + t) * N + n] + (OCCB ? 0.f : (1.f - oc) * dO_r[i]);
-                        }
-                    }
-                    ei = (int)__reduce_min_sync(FULL, (unsigned)ei);     // the lowest free row competes too
-                    float zmax;
-                    {
-                        unsigned kk = 0u;
-#pragma unroll
-                        for (int i = 0; i < RPL; i++) {
-                            if (lane + 32 * i == ei) okv[i] = true;
-                            if (okv[i]) kk = max(kk, ord_key(zv[i]));
-                        }
-                        kk = __reduce_max_sync(FULL, kk);
-                        zmax = __uint_as_float((kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk);   // inverse of ord_key
-                    }
-                    float se = 0.f, sd = 0.f, ev[RPL];
-#pragma unroll
-                    for (int i = 0; i < RPL; i++) {
-                        ev[i] = okv[i] ? __expf(zv[i] - zmax) : 0.f;
-                        se += ev[i]; sd += ev[i] * dwv[i];
-                    }
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) {
-                        se += __shfl_xor_sync(FULL, se, off);
-                        sd += __shfl_xor_sync(FULL, sd, off);
-                    }
-                    const float sa = g * sd / se;                                  // sum_n asoft_n (g dw_n)
                     float f1 = 0.f, f2 = 0.f;
-#pragma unroll
-                    for (int i = 0; i < RPL; i++) {
-                        const int n = lane + 32 * i;
-                        const float dz = okv[i] ? (ev[i] / se) * (g * dwv[i] - sa) : 0.f;
-                        f1 += -occv[i] * dz;
-                        f2 += dz * sv[i];
-                        if (32 * i <= limj && n <= limj) {
-                            St[n * CH + j] = dz * temp * kiv[i];                   // C[n][j]
-                            if (n == a) dg[((size_t)b * T + t) * H + h] = dwv[i];
-                            if (!OCCB) dO_r[i] = ((n == a) ? 1.f - g : 1.f) * dO_r[i] - frv * dz;
-                        } else if (32 * i <= lim && n <= lim) {
-                            St[n * CH + j] = 0.f;                                  // a row that was no candidate yet
-                        }
-                    }
+                    // compiled once per number of live row slots (rows above the chunk's candidate limit are never visited)
+#define AB_ADJ(NS) \
+    { \
+                    float sv[(NS)], zv[(NS)], dwv[(NS)], kiv[(NS)], occv[(NS)]; \
+                    bool okv[(NS)]; \
+                    int ei = BIGI; \
+_Pragma("unroll") \
+                    for (int i = 0; i < (NS); i++) { \
+                        const int n = lane + 32 * i; \
+                        sv[i] = 0.f; zv[i] = -INFINITY; dwv[i] = 0.f; kiv[i] = 0.f; occv[i] = 0.f; okv[i] = false; \
+                        if (32 * i <= limj && n <= limj) { \
+                            float S = St[n * CH + j], ki = s_kinv[n], oc = s_o[n]; \
+                            bool got = false; \
+_Pragma("unroll") \
+                            for (int i2 = 0; i2 < CH; i2++) { \
+                                if (am_c[i2] == n) { \
+                                    if (i2 < j) S += PD[i2 * CH + j]; \
+                                    else if (!got) { ki = ki_c[i2]; oc = oo_c[i2]; got = true; } \
+                                } \
+                            } \
+                            const float s = tq * (ki * S); \
+                            const float occ = OCCB ? (oc >= eps ? 1.f : 0.f) : oc; \
+                            sv[i] = s; kiv[i] = ki; occv[i] = occ; \
+                            zv[i] = s - frv * occ; \
+                            okv[i] = oc >= eps; \
+                            if (oc < eps && n < ei) ei = n; \
+                            { \
+                                const size_t di = ((size_t)bh * T + t) * N + n; \
+                                dwv[i] = (Din[di] + Din[(size_t)p.B * H * T * N + di]) + (OCCB ? 0.f : (1.f - oc) * dO_r[i]); \
+                            } \
+                        } \
+                    } \
+                    ei = (int)__reduce_min_sync(FULL, (unsigned)ei); \
+                    float zmax; \
+                    { \
+                        unsigned kk = 0u; \
+_Pragma("unroll") \
+                        for (int i = 0; i < (NS); i++) { \
+                            if (lane + 32 * i == ei) okv[i] = true; \
+                            if (okv[i]) kk = max(kk, ord_key(zv[i])); \
+                        } \
+                        kk = __reduce_max_sync(FULL, kk); \
+                        zmax = __uint_as_float((kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk); \
+                    } \
+                    float se = 0.f, sd = 0.f, ev[(NS)]; \
+_Pragma("unroll") \
+                    for (int i = 0; i < (NS); i++) { \
+                        ev[i] = okv[i] ? __expf(zv[i] - zmax) : 0.f; \
+                        se += ev[i]; sd += ev[i] * dwv[i]; \
+                    } \
+_Pragma("unroll") \
+                    for (int off = 16; off > 0; off >>= 1) { \
+                        se += __shfl_xor_sync(FULL, se, off); \
+                        sd += __shfl_xor_sync(FULL, sd, off); \
+                    } \
+                    const float sa = g * sd / se; \
+_Pragma("unroll") \
+                    for (int i = 0; i < (NS); i++) { \
+                        const int n = lane + 32 * i; \
+                        const float dz = okv[i] ? (ev[i] / se) * (g * dwv[i] - sa) : 0.f; \
+                        f1 += -occv[i] * dz; \
+                        f2 += dz * sv[i]; \
+                        if (32 * i <= limj && n <= limj) { \
+                            St[n * CH + j] = dz * temp * kiv[i]; \
+                            if (n == a) dg[((size_t)b * T + t) * H + h] = dwv[i]; \
+                            if (!OCCB) dO_r[i] = ((n == a) ? 1.f - g : 1.f) * dO_r[i] - frv * dz; \
+                        } else if (32 * i <= lim && n <= lim) { \
+                            St[n * CH + j] = 0.f; \
+                        } \
+                    } \
+    }
+                    if (lim < 32) AB_ADJ(1)
+                    else if (lim < 64) AB_ADJ((RPL < 2 ? RPL : 2))
+                    else if (lim < 96) AB_ADJ((RPL < 3 ? RPL : 3))
+                    else if (lim < 128) AB_ADJ((RPL < 4 ? RPL : 4))
+                    else if (lim < 192) AB_ADJ((RPL < 6 ? RPL : 6))
+                    else AB_ADJ(RPL)
+#undef AB_ADJ
 #pragma unroll
                     for (int off = 16; off > 0; off >>= 1) {
                         f1 += __shfl_xor_sync(FULL, f1, off);
@@ -327,7 +344,7 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
             __syncthreads();
             float prj = 0.f;
 #pragma unroll
-            for (int w = 0; w < AF_WARPS; w++) prj += s_pr[w * CH + j];            // fixed order: repeatable
+            for (int w = 0; w < AB_WARPS; w++) prj += s_pr[w * CH + j];            // fixed order: repeatable
             if (act) {
                 const size_t ix = ((size_t)b * T + t0 + j) * H + h;
                 // qinv = 1e6 means |q| was under the 1e-6 clamp: no projection term (slotkern_cuda.py:422)
@@ -350,11 +367,11 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_bwd_chunked_kernel(
     }
 #undef AB_ITEM
 #undef AB_ISSUE_LOADS
-    if (lane == 0) { s_pr[warp] = dtemp_acc; s_pr[AF_WARPS + warp] = dfr_acc; }
+    if (lane == 0) { s_pr[warp] = dtemp_acc; s_pr[AB_WARPS + warp] = dfr_acc; }
     __syncthreads();
     if (tid == 0) {
         float a = 0.f, c = 0.f;
-        for (int w = 0; w < AF_WARPS; w++) { a += s_pr[w]; c += s_pr[AF_WARPS + w]; }
+        for (int w = 0; w < AB_WARPS; w++) { a += s_pr[w]; c += s_pr[AB_WARPS + w]; }
         part[bh] = a;
         part[(size_t)p.B * H + bh] = c;
     }

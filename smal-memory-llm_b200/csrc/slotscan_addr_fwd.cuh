@@ -1,21 +1,18 @@
-// Forward address scan, chunked: the sequential decision (which row does token t write?) is the only thing left in
-// a token-by-token loop, and that loop runs in ONE warp on lane-local numbers prepared for it in bulk.
+// Forward address scan: which row does token t write?  [reference addr_fwd, slotkern_cuda.py:72-174]
 //
-// Per chunk of CH = 8 tokens and per (sequence, head), one CTA of 8 warps does
-//   1. score phase (all warps): St[j][n] = <K_n, q_j> and Rt[j][n] = <K_n, k_j> for every row touched so far against
-//      the chunk's 8 write queries and 8 keys (key rows resident in shared memory as f32, each lane keeps its token
-//      slice in registers, rows are broadcast reads), plus the 8x8 Gram tables Pm = <k_i, q_j>, Gm = <k_i, k_j>;
-//   2. resolve phase (warp 0): each lane owns the rows lane, lane + 32, ... and holds their 8 scores of the chunk in
-//      registers.  Per token  z_n = temp * qinv * kinv_n * S[n][j] - fr * occ_n  over the candidate rows, argmax by
-//      a warp max-reduction and a ballot.  The write itself is NOT executed here: what the next token needs from it
-//      follows from linearity of  K_a' = (1-g) K_a + g k_i  and stays inside the owner lane:
-//          <K_a', q_j> = (1-g) S[a][j] + g Pm[i][j]          <K_a', k_j> = (1-g) R[a][j] + g Gm[i][j]
-//          |K_a'|^2    = (1-g)^2 |K_a|^2 + 2 g (1-g) R[a][i] + g^2 Gm[i][i]       (accumulated in double)
-//      so a step has no shared-memory row traffic and no cross-lane hand-off besides the reduction;
-//   3. apply phase (all warps): the chunk's writes are executed on the key rows, one warp per written row.
-// Against the reference (slotkern_cuda.py:72-174) this changes the order of operations (dot first, scale after;
-// the reference normalises first), which moves a score by float32 round-off only; addresses are checked against
-// the float64 oracle with a 1e-4 margin rule.
+// One CTA of 4 warps per (sequence, head), key rows resident in shared memory as f32 for the whole scan.
+// Work split per token: LANE = ROW (row n = lane + 32 s for slot s), WARP = COLUMN QUARTER.  Each lane reads its own
+// row slice (row stride DK + 4 floats: the 8 lanes of a quarter-warp fall into 8 different bank groups) against the
+// token's query and key slices (broadcast reads) and produces two partial dots, <K_n, q_t> and <K_n, k_t>.  After one
+// barrier warp 0 adds the four partials, forms  z_n = temp * qinv * kinv_n * <K_n, q_t> - fr * occ_n  over the
+// candidate rows and takes the argmax with two warp reductions (max of an order-preserving key, then min index).
+// The row norm is never reduced again: |K_a'|^2 = (1-g)^2 |K_a|^2 + 2 g (1-g) <K_a, k_t> + g^2 |k_t|^2, accumulated in
+// double.  After a second barrier every warp blends its column quarter of the chosen row.  Only rows up to the
+// highest row touched so far (+1) are visited: everything above is exactly zero.
+//
+// Against the reference this changes the order of operations (dot first, scale after; the reference normalises
+// first), which moves a score by float32 round-off only; addresses are checked against the float64 oracle with a
+// 1e-4 margin rule.
 #pragma once
 #include "slotscan_common.cuh"
 
@@ -23,45 +20,20 @@ namespace slotscan {
 
 #ifdef SLOTSCAN_PHASE_TIMING
 __device__ unsigned long long g_phase_cycles[16];
-#define PHASE_T0() long long _pt = clock64()
-#define PHASE_MARK(I) do { if (tid == 0) { long long _n = clock64(); _acc[I] += _n - _pt; _pt = _n; } } while (0)
+#define STEP_T0() long long _st = clock64()
 #define STEP_MARK(I) do { long long _n = clock64(); _acc[I] += _n - _st; _st = _n; } while (0)
 #else
-#define PHASE_T0()
-#define PHASE_MARK(I)
+#define STEP_T0()
 #define STEP_MARK(I)
 #endif
 
-constexpr int CH = 8;                       // tokens per chunk
-constexpr int AF_THREADS = 256;
+constexpr int CH = 8;                       // tokens staged per chunk
+constexpr int AF_THREADS = 128;
 constexpr int AF_WARPS = AF_THREADS / 32;
 
 __device__ __forceinline__ unsigned ord_key(float f) {    // monotone float -> unsigned
     const unsigned u = __float_as_uint(f);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-struct AddrFwdSmem {       // offsets in floats into dynamic shared memory
-    int K, St, U, Pm, Gm, nsq, misc, Kc, total;    // Kc: the chunk's keys kept in their input dtype (last region)
-    int qstride, sstride;
-};
-// U holds the chunk's queries while they are being copied into registers, then the table Rt for the rest of the chunk.
-// St / Rt are token-major ([j][n]): the lanes of the resolver read consecutive rows of one token without conflicts.
-__host__ __device__ inline AddrFwdSmem addr_fwd_layout(int N, int DK, int in_bytes) {
-    AddrFwdSmem L;
-    L.qstride = DK + 4;                     // padded: the 8 tokens of a quarter-warp hit 8 different bank groups
-    L.sstride = (N + 3) & ~3;
-    const int usz = (CH * L.qstride > CH * L.sstride) ? CH * L.qstride : CH * L.sstride;
-    L.K = 0;
-    L.St = L.K + N * DK;
-    L.U = L.St + CH * L.sstride;
-    L.Pm = L.U + usz;
-    L.Gm = L.Pm + CH * CH;
-    L.nsq = L.Gm + CH * CH;                 // per row: |K|^2 as double (2 floats)
-    L.misc = L.nsq + 2 * L.sstride;         // qinv g fr (8 each) | am oold kiold (8 each) | tok[8][4] | hw
-    L.Kc = L.misc + 6 * CH + 4 * CH + 8;
-    L.total = L.Kc + CH * DK * in_bytes / 4;
-    return L;
 }
 
 // 8 elements of a token stream held in registers between the global load and the shared-memory store
@@ -91,80 +63,100 @@ template <> struct Pre8<__nv_bfloat16> {
     }
 };
 
-// RPL = rows per lane of the resolver warp (N <= 32 * RPL)
+struct AddrFwdSmem {       // offsets in floats into dynamic shared memory
+    int K, part, tok, tokd, log, cur, Qs, Ks, total;
+    int kstride;
+};
+__host__ __device__ inline AddrFwdSmem addr_fwd_layout(int N, int DK, int RPL, int in_bytes) {
+    AddrFwdSmem L;
+    L.kstride = DK + 4;
+    L.K = 0;
+    L.part = L.K + N * L.kstride;                 // [RPL][4 warps][32 lanes] float2 partial dots
+    L.tok = L.part + RPL * AF_WARPS * 32 * 2;     // [CH] float4: temp*qinv, fr, g, |k|^2
+    L.tokd = L.tok + 4 * CH;                      // [CH][4] double: (1-g)^2, 2 g (1-g), g^2 |k|^2, pad
+    L.log = L.tokd + 8 * CH;                      // am, oold, kiold [CH each]
+    L.cur = L.log + 3 * CH;                       // am, lim of the current token
+    L.Qs = L.cur + 4;                             // the chunk's queries and keys in their input dtype
+    L.Ks = L.Qs + CH * DK * in_bytes / 4;
+    L.total = L.Ks + CH * DK * in_bytes / 4;
+    return L;
+}
+
+// RPL = row slots per lane (N <= 32 * RPL)
 template <int DK, int RPL, bool OCCB, typename Tin>
-__global__ void __launch_bounds__(AF_THREADS, 2) addr_fwd_chunked_kernel(
+__global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, int* __restrict__ am_out,
     float* __restrict__ oold_out, float* __restrict__ kiold_out, float* __restrict__ ofin, int* __restrict__ tfirst) {
     extern __shared__ __align__(16) float smem[];
-    constexpr int NI = (DK + 15) / 16;                  // float4 slices per lane in the score phase
-    constexpr int IPS = CH * DK / 8;                    // 8-element items per stream and chunk
+    constexpr int CW = (DK >= 16) ? DK / 4 : 4;           // columns per warp
+    constexpr int NF = CW / 4;                            // float4 per lane and row slice
+    constexpr int IPS = CH * DK / 8;                      // 8-element items per stream and chunk
+    constexpr int NIT = (2 * IPS + AF_THREADS - 1) / AF_THREADS;
     const int N = p.N, T = p.T, H = p.H;
-    const AddrFwdSmem L = addr_fwd_layout(N, DK, (int)sizeof(Tin));
+    const AddrFwdSmem L = addr_fwd_layout(N, DK, RPL, (int)sizeof(Tin));
+    const int KS = L.kstride;
     float* K = smem + L.K;
-    Tin* Kc = reinterpret_cast<Tin*>(smem + L.Kc);
-    float* St = smem + L.St;
-    float* Qc = smem + L.U;
-    float* Rt = smem + L.U;
-    float* Pm = smem + L.Pm;
-    float* Gm = smem + L.Gm;
-    double* s_nsq = reinterpret_cast<double*>(smem + L.nsq);       // |K_n|^2 (double: the recurrence must not drift)
-    float* s_qinv = smem + L.misc;
-    float* s_g = s_qinv + CH;
-    float* s_fr = s_g + CH;
-    int* s_am = reinterpret_cast<int*>(s_fr + CH);
-    float* s_oold = reinterpret_cast<float*>(s_am + CH);
-    float* s_kiold = s_oold + CH;
-    float* s_tok = s_kiold + CH;
-    int* s_hw = reinterpret_cast<int*>(s_tok + 4 * CH);
+    float2* part = reinterpret_cast<float2*>(smem + L.part);
+    float* s_tok = smem + L.tok;
+    double* s_tokd = reinterpret_cast<double*>(smem + L.tokd);
+    int* s_am = reinterpret_cast<int*>(smem + L.log);
+    float* s_oold = smem + L.log + CH;
+    float* s_kiold = smem + L.log + 2 * CH;
+    int* s_cur = reinterpret_cast<int*>(smem + L.cur);
+    Tin* Qs = reinterpret_cast<Tin*>(smem + L.Qs);
+    Tin* Ks = reinterpret_cast<Tin*>(smem + L.Ks);
 
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int pj = lane & 7, pp = lane >> 3;            // score phase: token and column part of this lane
+    const int c0 = warp * CW;                             // first column of this warp
+    const bool wact = c0 < DK;
     const float temp = temp_p[0], eps = p.eps;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    for (int i = tid; i < N * DK; i += AF_THREADS) K[i] = 0.f;
-    for (int i = tid; i < N; i += AF_THREADS) {
-        tfirst[(size_t)bh * N + i] = (i == 0) ? 0 : T;
-        s_nsq[i] = 0.0;
-    }
-    if (tid == 0) *s_hw = -1;
+    for (int i = tid; i < N * KS; i += AF_THREADS) K[i] = 0.f;
+    for (int i = tid; i < N; i += AF_THREADS) tfirst[(size_t)bh * N + i] = (i == 0) ? 0 : T;
 
-    // ---- chunk loader: each thread carries at most one 8-element item of q or k, plus gate / fr on 16 threads ----
-    Pre8<Tin> pre;
+    // ---- chunk loader: 8-element items of q (first IPS) and k (next IPS), gate / fr on 16 threads ----
+    Pre8<Tin> pre[NIT];
     float pre_s = 0.f;
-    const bool has_item = tid < 2 * IPS;
-    const int it_s = has_item ? tid / IPS : 0, it_r = tid % IPS, it_j = it_r / (DK / 8), it_c = (it_r % (DK / 8)) * 8;
 #define AF_ISSUE_LOADS(T0)                                                                                 \
     {                                                                                                      \
-        const int t_ = (T0) + it_j;                                                                        \
-        if (has_item) {                                                                                    \
-            if (t_ < T) pre.load((it_s ? k : q) + (((size_t)b * T + t_) * H + h) * DK + it_c);             \
-            else pre.zero();                                                                               \
+        _Pragma("unroll") for (int r_ = 0; r_ < NIT; r_++) {                                               \
+            const int id_ = tid + r_ * AF_THREADS;                                                         \
+            if (id_ < 2 * IPS) {                                                                           \
+                const int s_ = id_ / IPS, rr_ = id_ % IPS, j_ = rr_ / (DK / 8), c_ = (rr_ % (DK / 8)) * 8; \
+                if ((T0) + j_ < T) pre[r_].load((s_ ? k : q) + (((size_t)b * T + (T0) + j_) * H + h) * DK + c_); \
+                else pre[r_].zero();                                                                       \
+            }                                                                                              \
         }                                                                                                  \
         if (tid < 2 * CH) {                                                                                \
             const int tt_ = (T0) + (tid & (CH - 1));                                                       \
             const size_t ix_ = ((size_t)b * T + tt_) * H + h;                                              \
-            if (tid < CH) pre_s = (tt_ < T) ? gate[ix_] : 0.f;   /* no arithmetic here: the load must stay in flight */ \
+            if (tid < CH) pre_s = (tt_ < T) ? gate[ix_] : 0.f;   /* no arithmetic: the load stays in flight */ \
             else pre_s = (tt_ < T) ? (p.fr_per_token ? fr[ix_] : fr[0]) : 0.f;                             \
         }                                                                                                  \
     }
 #define AF_COMMIT_LOADS()                                                                                  \
     {                                                                                                      \
-        if (has_item) {                                                                                    \
-            if (it_s) pre.store_raw(Kc + it_j * DK + it_c); else pre.store(Qc + it_j * L.qstride + it_c);  \
+        _Pragma("unroll") for (int r_ = 0; r_ < NIT; r_++) {                                               \
+            const int id_ = tid + r_ * AF_THREADS;                                                         \
+            if (id_ < 2 * IPS) {                                                                           \
+                const int s_ = id_ / IPS, rr_ = id_ % IPS;                                                 \
+                pre[r_].store_raw((s_ ? Ks : Qs) + rr_ * 8);                                               \
+            }                                                                                              \
         }                                                                                                  \
-        if (tid < CH) s_g[tid] = gate_eff(pre_s, p.hard_gate);                                             \
-        else if (tid < 2 * CH) s_fr[tid - CH] = pre_s;                                                     \
+        if (tid < CH) s_tok[4 * tid + 2] = gate_eff(pre_s, p.hard_gate);                                   \
+        else if (tid < 2 * CH) s_tok[4 * (tid - CH) + 1] = pre_s;                                          \
     }
 
-    // resolver state (warp 0), per owned row lane + 32 i: 1 / max(|K|, 1e-6) and the occupancy
+    // resolver state (warp 0), per owned row lane + 32 s: |K|^2 (double: the recurrence must not drift),
+    // 1 / max(|K|, 1e-6) and the occupancy
+    double nsq_r[RPL];
     float kinv_r[RPL], o_r[RPL];
 #pragma unroll
-    for (int i = 0; i < RPL; i++) { kinv_r[i] = 1e6f; o_r[i] = 0.f; }
-    int hw = -1, fe = 0;                                  // highest row touched; lowest free row (N if none)
+    for (int s = 0; s < RPL; s++) { nsq_r[s] = 0.0; kinv_r[s] = 1e6f; o_r[s] = 0.f; }
+    int hw = -1, fe = 0, lim = 0;                         // highest row touched; lowest free row (N if none)
 
     AF_ISSUE_LOADS(0);
     AF_COMMIT_LOADS();
@@ -172,191 +164,174 @@ __global__ void __launch_bounds__(AF_THREADS, 2) addr_fwd_chunked_kernel(
 
 #ifdef SLOTSCAN_PHASE_TIMING
     long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    long long _st = 0;
 #endif
-    PHASE_T0();
+    STEP_T0();
     for (int t0 = 0; t0 < T; t0 += CH) {
         const int cn = min(CH, T - t0);
-        if (t0 + CH < T) AF_ISSUE_LOADS(t0 + CH);         // next chunk's global loads fly through every phase
-        // ---------------- score phase ----------------
-        float4 Qr[NI], Kr[NI];
-#pragma unroll
-        for (int i = 0; i < NI; i++) {
-            const int d0 = i * 16 + pp * 4;
-            Qr[i] = (d0 < DK) ? ld4(Qc + pj * L.qstride + d0) : zero4;
-            Kr[i] = (d0 < DK) ? ld4(Kc + pj * DK + d0) : zero4;
-        }
-        if (warp == 0) {
-            float qq = 0.f;
-#pragma unroll
-            for (int i = 0; i < NI; i++) qq += dot4(Qr[i], Qr[i]);
-            qq += __shfl_xor_sync(FULL, qq, 8);
-            qq += __shfl_xor_sync(FULL, qq, 16);
-            if (pp == 0) s_qinv[pj] = fminf(rsqrtf(qq), 1e6f);          // 1 / max(|q|, 1e-6)
-        }
-        __syncthreads();                                  // the queries are in registers: U becomes Rt
-        PHASE_MARK(0);
-        const int hw0 = *s_hw;
-        const int rows = min(hw0 + CH, N - 1) + 1;        // rows that can be candidates before this chunk ends
-        for (int n0 = warp; n0 < rows + CH; n0 += 2 * AF_WARPS) {      // two rows per pass: independent FMA chains
-            const int n1 = n0 + AF_WARPS;
-            const bool key0 = n0 >= rows, key1 = n1 >= rows, has1 = n1 < rows + CH;
-            const int m0 = key0 ? n0 - rows : n0, m1 = has1 ? (key1 ? n1 - rows : n1) : m0;
-            const bool k1 = has1 ? key1 : key0;
-            float aq0 = 0.f, ak0 = 0.f, aq1 = 0.f, ak1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < NI; i++) {
-                const int d0 = i * 16 + pp * 4;
-                if (d0 < DK) {
-                    const float4 r0 = key0 ? ld4(Kc + m0 * DK + d0) : ld4(K + (size_t)m0 * DK + d0);
-                    const float4 r1 = k1 ? ld4(Kc + m1 * DK + d0) : ld4(K + (size_t)m1 * DK + d0);
-                    aq0 += dot4(r0, Qr[i]); ak0 += dot4(r0, Kr[i]);
-                    aq1 += dot4(r1, Qr[i]); ak1 += dot4(r1, Kr[i]);
-                }
+        if (t0 + CH < T) AF_ISSUE_LOADS(t0 + CH);         // next chunk's global loads fly through the whole chunk
+        // per-token constants: warp w handles tokens w and w + 4
+        for (int j = warp; j < CH; j += AF_WARPS) {
+            float qq = 0.f, kk = 0.f;
+            for (int cc = lane * 4; cc < DK; cc += 128) {
+                const float4 q4 = ld4(Qs + j * DK + cc), k4 = ld4(Ks + j * DK + cc);
+                qq += dot4(q4, q4); kk += dot4(k4, k4);
             }
-            aq0 += __shfl_xor_sync(FULL, aq0, 8);  ak0 += __shfl_xor_sync(FULL, ak0, 8);
-            aq1 += __shfl_xor_sync(FULL, aq1, 8);  ak1 += __shfl_xor_sync(FULL, ak1, 8);
-            aq0 += __shfl_xor_sync(FULL, aq0, 16); ak0 += __shfl_xor_sync(FULL, ak0, 16);
-            aq1 += __shfl_xor_sync(FULL, aq1, 16); ak1 += __shfl_xor_sync(FULL, ak1, 16);
-            if (pp == 0) {
-                if (key0) { Pm[(n0 - rows) * CH + pj] = aq0; Gm[(n0 - rows) * CH + pj] = ak0; }
-                else { St[pj * L.sstride + n0] = aq0; Rt[pj * L.sstride + n0] = ak0; }
-                if (has1) {
-                    if (key1) { Pm[(n1 - rows) * CH + pj] = aq1; Gm[(n1 - rows) * CH + pj] = ak1; }
-                    else { St[pj * L.sstride + n1] = aq1; Rt[pj * L.sstride + n1] = ak1; }
-                }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                qq += __shfl_xor_sync(FULL, qq, off);
+                kk += __shfl_xor_sync(FULL, kk, off);
+            }
+            if (lane == 0) {
+                s_tok[4 * j] = temp * fminf(rsqrtf(qq), 1e6f);                                        // 1 / max(|q|, 1e-6)
+                const double gd = (double)s_tok[4 * j + 2], od = 1.0 - gd;     // |K'|^2 = od^2 |K|^2 + 2 gd od <K,k> + gd^2 |k|^2
+                s_tokd[4 * j] = od * od; s_tokd[4 * j + 1] = 2.0 * gd * od; s_tokd[4 * j + 2] = gd * gd * (double)kk;
             }
         }
         __syncthreads();
-        PHASE_MARK(1);
-        // ---------------- resolve phase (warp 0) ----------------
-        if (warp == 0) {
-            if (lane < CH)         // per-token constants in one 16-byte word: temp * qinv, fr, g, |k|^2
-                st4(s_tok + 4 * lane, make_float4(temp * s_qinv[lane], s_fr[lane], s_g[lane], Gm[lane * CH + lane]));
-            __syncwarp();
-            PHASE_MARK(2);
-#ifdef SLOTSCAN_PHASE_TIMING
-            _st = clock64();
-#endif
-            for (int j = 0; j < cn; j++) {
-                const int t = t0 + j;
+        STEP_MARK(0);
+        for (int j = 0; j < cn; j++) {
+            const int t = t0 + j;
+            // The step is compiled once per number of live row slots (rows above the highest touched one are exactly
+            // zero and are not visited): the common case of few occupied rows runs a short instruction stream.
+#define AF_DOTS(NS)                                                                                            \
+    {                                                                                                          \
+      if (wact) {                                                                                              \
+        float4 q4[NF], k4[NF];                                                                                 \
+        _Pragma("unroll") for (int i = 0; i < NF; i++) {                                                       \
+            q4[i] = ld4(Qs + j * DK + c0 + 4 * i);                                                             \
+            k4[i] = ld4(Ks + j * DK + c0 + 4 * i);                                                             \
+        }                                                                                                      \
+        _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
+            const int n = min(lane + 32 * s, N - 1);                                                           \
+            const float* Kr = K + (size_t)n * KS + c0;                                                         \
+            float a0 = 0.f, a1 = 0.f, r0 = 0.f, r1 = 0.f;                                                      \
+            _Pragma("unroll") for (int i = 0; i < NF; i++) {                                                   \
+                const float4 K4 = ld4(Kr + 4 * i);                                                             \
+                if (i & 1) { a1 += dot4(K4, q4[i]); r1 += dot4(K4, k4[i]); }                                   \
+                else { a0 += dot4(K4, q4[i]); r0 += dot4(K4, k4[i]); }                                         \
+            }                                                                                                  \
+            part[(s * AF_WARPS + warp) * 32 + lane] = make_float2(a0 + a1, r0 + r1);                           \
+        }                                                                                                      \
+      }                                                                                                        \
+    }
+            // lane = row, warp = column quarter
+            if (lim < 32) AF_DOTS(1)
+            else if (lim < 64) AF_DOTS(RPL < 2 ? RPL : 2)
+            else if (lim < 96) AF_DOTS(RPL < 3 ? RPL : 3)
+            else if (lim < 128) AF_DOTS(RPL < 4 ? RPL : 4)
+            else if (lim < 192) AF_DOTS(RPL < 6 ? RPL : 6)
+            else AF_DOTS(RPL)
+#undef AF_DOTS
+            STEP_MARK(1);
+            __syncthreads();
+            STEP_MARK(2);
+            // ---------------- resolve (warp 0) ----------------
+#define AF_RESOLVE(NS)                                                                                         \
+    {                                                                                                          \
+        float bz = -INFINITY, Rb = 0.f;                                                                        \
+        int bi = BIGI;                                                                                         \
+        _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
+            const int n = lane + 32 * s;                                                                       \
+            float S = 0.f, R = 0.f;                                                                            \
+            _Pragma("unroll") for (int w = 0; w < AF_WARPS; w++) {                                             \
+                if (w * CW < DK) { const float2 pr = part[(s * AF_WARPS + w) * 32 + lane]; S += pr.x; R += pr.y; } \
+            }                                                                                                  \
+            const float oc = o_r[s];                                                                           \
+            const float sc = tq * (kinv_r[s] * S);                                                             \
+            const float z = (OCCB ? (sc - frv * (oc >= eps ? 1.f : 0.f)) : (sc - frv * oc)) + 0.f;             \
+            if (n <= lim && (oc >= eps || n == fe) && z > bz) { bz = z; bi = n; Rb = R; }   /* ascending n */  \
+        }                                                                                                      \
+        const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);                                                  \
+        const unsigned kmax = __reduce_max_sync(FULL, key);                                                    \
+        am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));                \
+        /* the owner lane's best row IS am (it holds the maximum), so Rb is <K_am, k_t> there */               \
+        const bool owner = (am & 31) == lane;                                                                  \
+        const int ai = am >> 5;                                                                                \
+        _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
+            if (owner && s == ai) {                                                                            \
+                const double nn = fmax(fma(s_tokd[4 * j], nsq_r[s], fma(s_tokd[4 * j + 1], (double)Rb, s_tokd[4 * j + 2])), 0.0); \
+                s_am[j] = am; s_oold[j] = o_r[s]; s_kiold[j] = kinv_r[s];                                      \
+                nsq_r[s] = nn;                                                                                 \
+                kinv_r[s] = fminf(rsqrtf((float)nn), 1e6f);                                                    \
+                o_r[s] = __fmaf_rn(omw, o_r[s], g);                                                            \
+                o_new = o_r[s];                                                                                \
+            }                                                                                                  \
+        }                                                                                                      \
+    }
+            if (warp == 0) {
                 const float4 c4 = ld4(s_tok + 4 * j);
                 const float tq = c4.x, frv = c4.y, g = c4.z, omw = 1.f - g;
-                const int lim = min(hw + 1, N - 1);
-                const float* Sj = St + j * L.sstride;
-                float bz = -INFINITY;
-                int bi = BIGI;
-#pragma unroll
-                for (int i = 0; i < RPL; i++) {
-                    if (32 * i <= lim) {                   // uniform: rows above the highest touched one are zero
-                        const int n = lane + 32 * i;
-                        const float oc = o_r[i];
-                        const float s = tq * (kinv_r[i] * Sj[min(n, N - 1)]);
-                        const float z = (OCCB ? (s - frv * (oc >= eps ? 1.f : 0.f)) : (s - frv * oc)) + 0.f;
-                        if (n <= lim && (oc >= eps || n == fe) && z > bz) { bz = z; bi = n; }   // ascending n
-                    }
+                int am = 0;
+                float o_new = 0.f;
+                if (lim < 32) AF_RESOLVE(1)
+                else if (lim < 64) AF_RESOLVE(RPL < 2 ? RPL : 2)
+                else if (lim < 96) AF_RESOLVE(RPL < 3 ? RPL : 3)
+                else if (lim < 128) AF_RESOLVE(RPL < 4 ? RPL : 4)
+                else if (lim < 192) AF_RESOLVE(RPL < 6 ? RPL : 6)
+                else AF_RESOLVE(RPL)
+#undef AF_RESOLVE
+                o_new = __shfl_sync(FULL, o_new, am & 31);
+                if (am > hw) {
+                    hw = am;
+                    if (lane == 0 && am + 1 < N) tfirst[(size_t)bh * N + am + 1] = t + 1;
                 }
-                STEP_MARK(8);
-                const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);
-                const unsigned kmax = __reduce_max_sync(FULL, key);
-                int am;
-                if (lim < 32) am = __ffs(__ballot_sync(FULL, key == kmax && bi != BIGI)) - 1;   // one row per lane
-                else am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));
-                STEP_MARK(9);
-                // the write, booked by every lane alike from broadcast reads (no divergence, no hand-off):
-                // |K_a'|^2 = (1-g)^2 |K_a|^2 + 2 g (1-g) <K_a, k_t> + g^2 |k_t|^2
-                const double gd = (double)g, od = (double)omw;
-                const double nn = fmax(od * od * s_nsq[am] + 2.0 * gd * od * (double)Rt[j * L.sstride + am] +
-                                       gd * gd * (double)c4.w, 0.0);
-                const bool owner = (am & 31) == lane;
-                const int ai = am >> 5;
-                float o_old = o_r[0], k_old = kinv_r[0];
-#pragma unroll
-                for (int i = 1; i < RPL; i++)
-                    if (i == ai) { o_old = o_r[i]; k_old = kinv_r[i]; }
-                o_old = __shfl_sync(FULL, o_old, am & 31);
-                k_old = __shfl_sync(FULL, k_old, am & 31);
-                const float k_new = fminf(rsqrtf((float)nn), 1e6f), o_new = __fmaf_rn(omw, o_old, g);
-#pragma unroll
-                for (int i = 0; i < RPL; i++)
-                    if (owner && i == ai) { kinv_r[i] = k_new; o_r[i] = o_new; }
-                STEP_MARK(10);
-                // scores of the chunk's remaining tokens against the rewritten row, by linearity (one lane per token)
-                if (lane > j && lane < cn) {
-                    float* sp = St + lane * L.sstride + am;
-                    float* rp = Rt + lane * L.sstride + am;
-                    *sp = blend(*sp, Pm[j * CH + lane], g, omw);
-                    *rp = blend(*rp, Gm[j * CH + lane], g, omw);
-                }
-                if (lane == 0) {
-                    s_nsq[am] = nn;
-                    s_am[j] = am; s_oold[j] = o_old; s_kiold[j] = k_old;
-                    if (am > hw && am + 1 < N) tfirst[(size_t)bh * N + am + 1] = t + 1;
-                }
-                STEP_MARK(11);
-                hw = max(hw, am);
                 if (am == fe && o_new >= eps) {            // the free row got taken: find the next one
                     int m = BIGI;
 #pragma unroll
-                    for (int i = RPL - 1; i >= 0; i--) {
-                        const int n = lane + 32 * i;
-                        if (n < N && o_r[i] < eps) m = n;
+                    for (int s = RPL - 1; s >= 0; s--) {
+                        const int n = lane + 32 * s;
+                        if (n < N && o_r[s] < eps) m = n;
                     }
                     m = (int)__reduce_min_sync(FULL, (unsigned)m);
                     fe = (m == BIGI) ? N : m;
                 } else if (o_new < eps && am < fe) {
                     fe = am;
                 }
-                __syncwarp();
-                STEP_MARK(12);
+                if (lane == 0) { s_cur[0] = am; s_cur[1] = min(hw + 1, N - 1); }
             }
-            if (lane == 0) *s_hw = hw;
-            PHASE_MARK(3);
-        }
-        __syncthreads();
-        PHASE_MARK(4);
-        // ---------------- apply phase: warp j executes token j's write unless a later token rewrites the same row;
-        // the warp of the LAST hit replays every hit of its row in order ----------------
-        if (warp < cn) {
-            const int a = s_am[warp];
-            bool last = true;
-            for (int j2 = warp + 1; j2 < cn; j2++) last = last && (s_am[j2] != a);
-            const int col = lane * 4;
-            if (last && col < DK) {
-                float4 Kn = ld4(K + (size_t)a * DK + col);
-                for (int j = 0; j <= warp; j++) {
-                    if (s_am[j] != a) continue;
-                    const float g = s_g[j], omw = 1.f - g;
-                    const float4 kt = ld4(Kc + j * DK + col);
+            STEP_MARK(3);
+            __syncthreads();
+            STEP_MARK(4);
+            // ---------------- the write: every warp blends its column quarter of the chosen row ----------------
+            {
+                const int am = s_cur[0];
+                lim = s_cur[1];
+                if (wact && lane < NF) {
+                    const float g = s_tok[4 * j + 2], omw = 1.f - g;
+                    float* Kr = K + (size_t)am * KS + c0 + 4 * lane;
+                    float4 Kn = ld4(Kr);
+                    const float4 kt = ld4(Ks + j * DK + c0 + 4 * lane);
                     Kn.x = blend(Kn.x, kt.x, g, omw); Kn.y = blend(Kn.y, kt.y, g, omw);
                     Kn.z = blend(Kn.z, kt.z, g, omw); Kn.w = blend(Kn.w, kt.w, g, omw);
+                    st4(Kr, Kn);
                 }
-                st4(K + (size_t)a * DK + col, Kn);
+                __syncwarp();                              // a warp only ever reads the columns it writes
             }
+            STEP_MARK(5);
         }
+        // ---------------- flush the chunk's log, land the next chunk ----------------
+        __syncthreads();
         if (tid < cn) {
             const size_t ix = ((size_t)b * T + t0 + tid) * H + h;
             am_out[ix] = s_am[tid];
             oold_out[ix] = s_oold[tid];
             kiold_out[ix] = s_kiold[tid];
         }
-        __syncthreads();
-        PHASE_MARK(5);
         if (t0 + CH < T) AF_COMMIT_LOADS();
         __syncthreads();
-        PHASE_MARK(6);
+        STEP_MARK(6);
     }
-#undef AF_ISSUE_LOADS
-#undef AF_COMMIT_LOADS
 #ifdef SLOTSCAN_PHASE_TIMING
     if (tid == 0)
         for (int i = 0; i < 16; i++) atomicAdd(&g_phase_cycles[i], (unsigned long long)_acc[i]);
 #endif
+#undef AF_ISSUE_LOADS
+#undef AF_COMMIT_LOADS
     if (warp == 0) {
 #pragma unroll
-        for (int i = 0; i < RPL; i++) {
-            const int n = lane + 32 * i;
-            if (n < N) ofin[(size_t)bh * N + n] = o_r[i];
+        for (int s = 0; s < RPL; s++) {
+            const int n = lane + 32 * s;
+            if (n < N) ofin[(size_t)bh * N + n] = o_r[s];
         }
     }
 }

@@ -2,7 +2,7 @@
 // (hard argmax address, address gradient detached from the stored keys).
 //
 // Decomposition (the row a token writes is the only sequential decision):
-//   addr_fwd_chunked_kernel (slotscan_addr_fwd.cuh)  one CTA per (sequence, head): keys resident in shared memory,
+//   addr_fwd_direct_kernel (slotscan_addr_fwd.cuh)  one CTA per (sequence, head): keys resident in shared memory,
 //                      scores per chunk of 8 tokens in bulk, one warp resolves the addresses.   [addr_fwd, slotkern_cuda.py:72-174]
 //   replay_rows_kernel (slotscan_rows.cuh)  row-parallel: replays key / value rows from the log, emits the stride-G
 //                      snapshots, the undo log and the final state.                              [val_fwd :178-206]
@@ -69,11 +69,12 @@ static cudaError_t opt_in_smem(F f, size_t bytes) {
 template <int DK, typename Tin>
 static cudaError_t launch_addr_fwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
                                    const float* fr, const float* temp, const slotscan_log& L, cudaStream_t st) {
-    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK, (int)sizeof(Tin)).total;
+    const int rpl = p.N <= 192 ? 6 : 14;
+    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK, rpl, (int)sizeof(Tin)).total;
     cudaError_t e;
 #define AF_LAUNCH(RPL_, OCCB_)                                                                                     \
     {                                                                                                              \
-        auto kern = addr_fwd_chunked_kernel<DK, RPL_, OCCB_, Tin>;                                                 \
+        auto kern = addr_fwd_direct_kernel<DK, RPL_, OCCB_, Tin>;                                                 \
         if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                  \
         kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold,   \
                                                 L.kiold, L.ofin, L.tfirst);                                        \
@@ -97,7 +98,7 @@ static cudaError_t launch_addr_bwd(const slotscan_params& p, const void* q, cons
     {                                                                                                               \
         auto kern = addr_bwd_chunked_kernel<DK, RPL_, OCCB_, Tin>;                                                  \
         if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                   \
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.kold,    \
+        kern<<<p.B * p.H, AB_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.kold,    \
                                                 L.oold, L.kiold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq, dgate, dfr, \
                                                 part);                                                              \
     }
@@ -119,22 +120,16 @@ static cudaError_t launch_replay(const slotscan_params& p, const void* x, const 
     return cudaGetLastError();
 }
 template <int D, typename Tin, typename Tsn>
-static cudaError_t launch_rows_bwd(const slotscan_params& p, bool accum, const void* x, const float* gate, const int* am,
-                                   const float* xold, const float* xfin, const int* tfirst, const void* dxbuf, void* dx,
-                                   float* Dn, cudaStream_t st) {
+static cudaError_t launch_rows_bwd(const slotscan_params& p, int ntensors, const RowsBwdArgs<Tin, Tsn>& a0,
+                                   const RowsBwdArgs<Tin, Tsn>& a1, const float* gate, const int* am, const int* tfirst,
+                                   cudaStream_t st) {
     constexpr int RPB = ROW_THREADS / (D / 8);
-    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB);
+    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB, ntensors);
     constexpr size_t sm = rows_bwd_smem_bytes<D, Tin>();
-    cudaError_t e;
-    if (accum) {
-        auto kern = rows_bwd_kernel<D, Tin, Tsn, true>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<grid, ROW_THREADS, sm, st>>>(p, (const Tin*)x, gate, am, xold, xfin, tfirst, (const Tsn*)dxbuf, (Tin*)dx, Dn);
-    } else {
-        auto kern = rows_bwd_kernel<D, Tin, Tsn, false>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<grid, ROW_THREADS, sm, st>>>(p, (const Tin*)x, gate, am, xold, xfin, tfirst, (const Tsn*)dxbuf, (Tin*)dx, Dn);
-    }
+    auto kern = rows_bwd_kernel<D, Tin, Tsn>;
+    cudaError_t e = opt_in_smem(kern, sm);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, ROW_THREADS, sm, st>>>(p, a0, a1, gate, am, tfirst);
     return cudaGetLastError();
 }
 
@@ -177,14 +172,21 @@ static cudaError_t bwd_typed(const slotscan_params& p, const void* k, const void
                              const void* dvbuf, float* Dn, float* part, void* dk, void* dq, void* dv, float* dgate,
                              float* dfr, float* dtemp, cudaStream_t st) {
     cudaError_t e;
-    {
+    // keys and values are independent given the log: one launch (blockIdx.z) when dk == dv, each into its own D table
+    float* DnV = Dn + (size_t)p.B * p.H * p.T * p.N;
+    const RowsBwdArgs<Tin, Tsn> ak{(const Tin*)k, L.kold, L.kfin, (const Tsn*)dkbuf, (Tin*)dk, Dn};
+    const RowsBwdArgs<Tin, Tsn> av{(const Tin*)v, L.vold, L.vfin, (const Tsn*)dvbuf, (Tin*)dv, DnV};
+    if (p.DK == p.DV) {
         ProfScope ps(K_ROWS_BWD_K, st);
-        DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, false, k, gate, L.addr, L.kold, L.kfin, L.tfirst, dkbuf, dk, Dn, st)));
-    }
-    if (e != cudaSuccess) return e;
-    {
+        DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 2, ak, av, gate, L.addr, L.tfirst, st)));
+    } else {
+        {
+            ProfScope ps(K_ROWS_BWD_K, st);
+            DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 1, ak, ak, gate, L.addr, L.tfirst, st)));
+        }
+        if (e != cudaSuccess) return e;
         ProfScope ps(K_ROWS_BWD_V, st);
-        DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, true, v, gate, L.addr, L.vold, L.vfin, L.tfirst, dvbuf, dv, Dn, st)));
+        DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 1, av, av, gate, L.addr, L.tfirst, st)));
     }
     if (e != cudaSuccess) return e;
     {
@@ -217,7 +219,8 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (p->B < 1 || p->T < 1 || p->H < 1 || p->N < 1 || p->G < 1) return SLOTSCAN_E_SHAPE;
     if (p->DK < 8 || p->DK > 128 || (p->DK & (p->DK - 1))) return SLOTSCAN_E_SHAPE;
     if (p->DV < 8 || p->DV > 128 || (p->DV & (p->DV - 1))) return SLOTSCAN_E_SHAPE;
-    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK, 4).total + 1024 > SMEM_CAP || p->N > 448) return SLOTSCAN_E_SHAPE;
+    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK, p->N <= 192 ? 6 : 14, 4).total + 1024 > SMEM_CAP || p->N > 448)
+        return SLOTSCAN_E_SHAPE;
     if (sizeof(float) * (size_t)addr_bwd_layout(p->N, p->DK).total + 1024 > SMEM_CAP) return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
     if (p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
@@ -252,7 +255,7 @@ extern "C" int slotscan_hard_fwd(const slotscan_params* p, const void* k, const 
 extern "C" size_t slotscan_hard_bwd_scratch_bytes(const slotscan_params* p) {
     if (slotscan_check(p)) return 0;
     const size_t BH = (size_t)p->B * p->H;
-    size_t dn = sizeof(float) * BH * p->T * p->N;
+    size_t dn = 2 * sizeof(float) * BH * p->T * p->N;      // one D table for the keys, one for the values
     dn = (dn + 255) & ~(size_t)255;
     return dn + sizeof(float) * 2 * BH;
 }
@@ -274,7 +277,7 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
         misaligned(log->kfin) || misaligned(log->vfin))
         return SLOTSCAN_E_ALIGN;
     const size_t BH = (size_t)p->B * p->H;
-    size_t dn = sizeof(float) * BH * p->T * p->N;
+    size_t dn = 2 * sizeof(float) * BH * p->T * p->N;
     dn = (dn + 255) & ~(size_t)255;
     float* Dn = (float*)scratch;
     float* part = (float*)((char*)scratch + dn);
@@ -308,12 +311,12 @@ static void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* na
 
 extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     int n = 0;
-    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_chunked_kernel<128, 6, true, float>);
-    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_chunked_kernel<128, 6, true, __nv_bfloat16>);
+    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_direct_kernel<128, 6, true, float>);
+    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_direct_kernel<128, 6, true, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16>);
     fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float>);
-    fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);
-    fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float, false>);
+    fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16>);
+    fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float>);
     fill_attr(out, cap, n, "addr_bwd<128,f32>", addr_bwd_chunked_kernel<128, 6, true, float>);
     fill_attr(out, cap, n, "addr_bwd<128,bf16>", addr_bwd_chunked_kernel<128, 6, true, __nv_bfloat16>);
     return n;

@@ -7,7 +7,7 @@
 //                        the table D[t,n] = <x_t - X_n, dX_n>.                    [reference rows_bwd, :209-261]
 //
 // Layout: one group of LPR = D/8 lanes per row, 8 elements per lane in registers, RPB = 256 / LPR rows per CTA;
-// grid (B*H, row tiles).  Tokens are taken in chunks of RC = 64: the chunk's gates, a per-row bit mask of the tokens
+// grid (B*H, row tiles).  Tokens are taken in chunks of RC = 32: the chunk's gates, a per-row bit mask of the tokens
 // that hit the row, and the chunk's token vectors are staged in shared memory once per CTA, so the walk over a chunk
 // is a walk over EVENTS (next hit, next snapshot) and never waits on a global load.  A tile whose rows are never
 // addressed (tfirst == T for all of them) only writes zeros (forward) or does nothing (reverse).
@@ -17,7 +17,7 @@
 namespace slotscan {
 
 constexpr int ROW_THREADS = 256;
-constexpr int RC = 64;                        // tokens per staged chunk (one 64-bit hit mask per row)
+constexpr int RC = 32;                        // tokens per staged chunk (hit mask per row: one bit per token)
 
 template <typename T>
 __device__ __forceinline__ void copy8(T* dst, const T* src);
@@ -129,11 +129,29 @@ __host__ __device__ constexpr size_t rows_bwd_smem_bytes() {
            (ROW_THREADS / (D / 8)) * sizeof(unsigned long long) + 16;
 }
 
-template <int D, typename Tin, typename Tsn, bool ACCUM>
+// one tensor's worth of arguments: blockIdx.z picks the keys (0) or the values (1) when both run in one launch
+template <typename Tin, typename Tsn>
+struct RowsBwdArgs {
+    const Tin* x;
+    const float* xold;
+    const float* xfin;
+    const Tsn* dxbuf;
+    Tin* dx;
+    float* Dn;       // this tensor's own D table: the address backward adds the two
+};
+
+template <int D, typename Tin, typename Tsn>
 __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
-    const slotscan_params p, const Tin* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ am,
-    const float* __restrict__ xold, const float* __restrict__ xfin, const int* __restrict__ tfirst,
-    const Tsn* __restrict__ dxbuf, Tin* __restrict__ dx, float* __restrict__ Dn) {
+    const slotscan_params p, const RowsBwdArgs<Tin, Tsn> a0, const RowsBwdArgs<Tin, Tsn> a1,
+    const float* __restrict__ gate, const int* __restrict__ am, const int* __restrict__ tfirst) {
+    constexpr bool ACCUM = false;
+    const RowsBwdArgs<Tin, Tsn>& A = blockIdx.z ? a1 : a0;
+    const Tin* __restrict__ x = A.x;
+    const float* __restrict__ xold = A.xold;
+    const float* __restrict__ xfin = A.xfin;
+    const Tsn* __restrict__ dxbuf = A.dxbuf;
+    Tin* __restrict__ dx = A.dx;
+    float* __restrict__ Dn = A.Dn;
     constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
     extern __shared__ __align__(16) unsigned char dsm[];
     float* s_xo = reinterpret_cast<float*>(dsm);                                   // [RC][D] undo rows
@@ -183,9 +201,57 @@ __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
         }
         __syncthreads();
         const unsigned long long m = live ? s_mask[r] : 0ull;
+        // hit masks of the rows sharing this warp decide together whether the 4-token fast path may run
+        unsigned long long mw = m;
+#pragma unroll
+        for (int off = 16; off >= LPR && off > 0; off >>= 1) mw |= __shfl_xor_sync(FULL, mw, off);
         for (int i = tc - 1; i >= 0; i--) {
-            const int t = t0 + i;
+            int t = t0 + i;
             if (t < wstop) break;
+            if (LPR >= 4) {
+                // Four consecutive tokens t, t-1, t-2, t-3 see the same (X, dX) when none of them writes a row of this
+                // warp and no snapshot gradient lands after the first three: then the four dot products are reduced
+                // together (5 shuffles instead of 16).
+                while (i >= 3 && t - 3 >= wstop && ((mw >> (i - 3)) & 0xfull) == 0ull &&
+                       (jb < 0 || jb * G <= t - 3 || jb * G > t)) {
+                    float ps[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        float xv[8];
+                        ld8(xv, s_x + (i - u) * D + c * 8);
+                        float a = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) a += (xv[j] - X[j]) * dX[j];
+                        ps[u] = a;
+                    }
+                    constexpr int O1 = LPR / 2, O2 = LPR / 4;
+                    const bool up1 = (c & O1) != 0, up2 = (c & O2) != 0;
+                    const float s0 = up1 ? ps[0] : ps[2], s1 = up1 ? ps[1] : ps[3];
+                    const float r0 = __shfl_xor_sync(FULL, s0, O1), r1 = __shfl_xor_sync(FULL, s1, O1);
+                    const float q0 = (up1 ? ps[2] : ps[0]) + r0, q1 = (up1 ? ps[3] : ps[1]) + r1;   // tokens 2u1, 2u1+1
+                    const float r2 = __shfl_xor_sync(FULL, up2 ? q0 : q1, O2);
+                    float w = (up2 ? q1 : q0) + r2;                                                // token 2 u1 + u2
+#pragma unroll
+                    for (int off = O2 / 2; off > 0; off >>= 1) w += __shfl_xor_sync(FULL, w, off);
+                    const int u = (up1 ? 2 : 0) + (up2 ? 1 : 0);
+                    const int tu = t - u;
+                    if (live && tu >= tstop && (c & (O2 - 1)) == 0) {
+                        float* dst = Dn + ((size_t)bh * T + tu) * N + n;
+                        if (ACCUM) *dst += w; else *dst = w;
+                    }
+                    if (jb >= 0 && jb * G == t - 3) {                              // the group ended on a snapshot time
+                        if (t - 3 >= tstop) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) dX[j] += nxt[j];
+                        }
+                        jb--;
+                        if (dsnap0 != nullptr && jb >= 0 && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+                    }
+                    i -= 4;
+                    t -= 4;
+                }
+                if (i < 0 || t < wstop) break;
+            }
             const bool on = t >= tstop;
             const bool hit = on && ((m >> i) & 1ull);
             float xv[8];
