@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
             const int tt_ = (T0) + (tid & (CH - 1)), w_ = tid / CH;                                          \
             const size_t ix_ = ((size_t)b * T + tt_) * H + h;                                                \
             const bool in_ = tt_ < T && tt_ >= 0;                                                            \
-            if (w_ == 0) pre_s = in_ ? gate_eff(gate[ix_], p.hard_gate) : 0.f;                               \
+            if (w_ == 0) pre_s = in_ ? gate[ix_] : 0.f;   /* no arithmetic here: the load stays in flight */                               \
             else if (w_ == 1) pre_s = in_ ? (p.fr_per_token ? fr[ix_] : fr[0]) : 0.f;                        \
             else if (w_ == 2) pre_s = in_ ? oold_in[ix_] : 0.f;                                              \
             else pre_s = in_ ? kiold_in[ix_] : 0.f;                                                          \
@@ -131,10 +131,14 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
     AB_ISSUE_LOADS((nchunk - 1) * CH);
     __syncthreads();
 
+#ifdef SLOTSCAN_PHASE_TIMING
+    long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+    STEP_T0();
     for (int ck = nchunk - 1; ck >= 0; ck--) {
         const int t0 = ck * CH, cn = min(CH, T - t0);
         // ---- land the chunk's scalars, then its rows ----
-        if (tid < CH) s_g[tid] = pre_s;
+        if (tid < CH) s_g[tid] = gate_eff(pre_s, p.hard_gate);
         else if (tid < 2 * CH) s_fr[tid - CH] = pre_s;
         else if (tid < 3 * CH) s_oold[tid - 2 * CH] = pre_s;
         else if (tid < 4 * CH) s_kiold[tid - 3 * CH] = pre_s;
@@ -147,6 +151,7 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
             else if (s_ == 1) pre_q[r].store(Dl + j_ * DK + c_);
         }
         __syncthreads();
+        STEP_MARK(0);
         // kold: delta_j = g_j (k_j - kold_j) into Dl, and the row restore for the EARLIEST hit of each row
 #pragma unroll
         for (int r = 0; r < NITEM; r++) {
@@ -170,7 +175,19 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
             const int tl = t0 + cn - 1;
             while (lim > 0 && tfirst[(size_t)bh * N + lim] > tl) lim--;
         }
+        // D[t, n] of this warp's token (key part + value part), fetched now so the loads fly through the score phase
+        float dpre[RPL];
+#pragma unroll
+        for (int i = 0; i < RPL; i++) {
+            const int n = lane + 32 * i;
+            dpre[i] = 0.f;
+            if (OCCB && warp < cn && 32 * i <= lim && n <= lim) {
+                const size_t di = ((size_t)bh * T + t0 + warp) * N + n;
+                dpre[i] = Din[di] + Din[(size_t)p.B * H * T * N + di];
+            }
+        }
         __syncthreads();
+        STEP_MARK(1);
         // ---------------- score phase ----------------
         {
             float4 Qr[NI];
@@ -207,6 +224,7 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
             }
         }
         __syncthreads();
+        STEP_MARK(2);
         // ---------------- softmax adjoint: warp j handles token j (all tokens at once when OCCB) ----------------
         {
             int am_c[CH];
@@ -250,7 +268,7 @@ _Pragma("unroll") \
                             if (oc < eps && n < ei) ei = n; \
                             { \
                                 const size_t di = ((size_t)bh * T + t) * N + n; \
-                                dwv[i] = (Din[di] + Din[(size_t)p.B * H * T * N + di]) + (OCCB ? 0.f : (1.f - oc) * dO_r[i]); \
+                                dwv[i] = OCCB ? dpre[i] : (Din[di] + Din[(size_t)p.B * H * T * N + di]) + (1.f - oc) * dO_r[i]; \
                             } \
                         } \
                     } \
@@ -313,6 +331,7 @@ _Pragma("unroll") \
             }
         }
         __syncthreads();
+        STEP_MARK(3);
         // ---------------- query gradient: warp w owns 16 output columns, lane = (token j, 4 columns) ----------------
         {
             const int j = lane & 7, cc = (warp * 16) + (lane >> 3) * 4;           // column base of this lane
@@ -342,6 +361,7 @@ _Pragma("unroll") \
             pr += __shfl_xor_sync(FULL, pr, 16);                                   // over this warp's 16 columns
             if ((lane >> 3) == 0) s_pr[warp * CH + j] = pr;
             __syncthreads();
+        STEP_MARK(4);
             float prj = 0.f;
 #pragma unroll
             for (int w = 0; w < AB_WARPS; w++) prj += s_pr[w * CH + j];            // fixed order: repeatable
@@ -364,7 +384,12 @@ _Pragma("unroll") \
             if (first) { s_kinv[a] = s_kiold[tid]; s_o[a] = s_oold[tid]; }
         }
         __syncthreads();
+        STEP_MARK(5);
     }
+#ifdef SLOTSCAN_PHASE_TIMING
+    if (tid == 0)
+        for (int i = 0; i < 8; i++) atomicAdd(&g_phase_cycles[8 + i], (unsigned long long)_acc[i]);
+#endif
 #undef AB_ITEM
 #undef AB_ISSUE_LOADS
     if (lane == 0) { s_pr[warp] = dtemp_acc; s_pr[AB_WARPS + warp] = dfr_acc; }

@@ -67,6 +67,7 @@ struct AddrFwdSmem {       // offsets in floats into dynamic shared memory
     int K, part, tok, tokd, log, cur, Qs, Ks, total;
     int kstride;
 };
+// N here is the number of key rows held in shared memory (the kernel's `ncap`)
 __host__ __device__ inline AddrFwdSmem addr_fwd_layout(int N, int DK, int RPL, int in_bytes) {
     AddrFwdSmem L;
     L.kstride = DK + 4;
@@ -87,14 +88,19 @@ template <int DK, int RPL, bool OCCB, typename Tin>
 __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, int* __restrict__ am_out,
-    float* __restrict__ oold_out, float* __restrict__ kiold_out, float* __restrict__ ofin, int* __restrict__ tfirst) {
+    float* __restrict__ oold_out, float* __restrict__ kiold_out, float* __restrict__ ofin, int* __restrict__ tfirst,
+    const int ncap, const int second_pass) {
+    // Two-pass protocol.  Most sequences touch few rows, and a CTA that holds only `ncap` rows is small enough for every
+    // (sequence, head) of a large batch to be resident at once.  Pass 1 (ncap < N) runs every sequence; one that
+    // needs row ncap gives up, marks itself by tfirst[bh][0] = -1 and leaves.  Pass 2 (ncap = N, second_pass = 1)
+    // redoes exactly the marked sequences from the start and returns at once for the others.
     extern __shared__ __align__(16) float smem[];
     constexpr int CW = (DK >= 16) ? DK / 4 : 4;           // columns per warp
     constexpr int NF = CW / 4;                            // float4 per lane and row slice
     constexpr int IPS = CH * DK / 8;                      // 8-element items per stream and chunk
     constexpr int NIT = (2 * IPS + AF_THREADS - 1) / AF_THREADS;
     const int N = p.N, T = p.T, H = p.H;
-    const AddrFwdSmem L = addr_fwd_layout(N, DK, RPL, (int)sizeof(Tin));
+    const AddrFwdSmem L = addr_fwd_layout(ncap, DK, RPL, (int)sizeof(Tin));
     const int KS = L.kstride;
     float* K = smem + L.K;
     float2* part = reinterpret_cast<float2*>(smem + L.part);
@@ -114,7 +120,9 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     const float temp = temp_p[0], eps = p.eps;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    for (int i = tid; i < N * KS; i += AF_THREADS) K[i] = 0.f;
+    if (second_pass && tfirst[(size_t)bh * N] != -1) return;          // finished in the first pass (uniform per CTA)
+    __syncthreads();
+    for (int i = tid; i < ncap * KS; i += AF_THREADS) K[i] = 0.f;
     for (int i = tid; i < N; i += AF_THREADS) tfirst[(size_t)bh * N + i] = (i == 0) ? 0 : T;
 
     // ---- chunk loader: 8-element items of q (first IPS) and k (next IPS), gate / fr on 16 threads ----
@@ -287,7 +295,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
                 } else if (o_new < eps && am < fe) {
                     fe = am;
                 }
-                if (lane == 0) { s_cur[0] = am; s_cur[1] = min(hw + 1, N - 1); }
+                if (lane == 0) { s_cur[0] = am; s_cur[1] = min(hw + 1, N - 1); }   // the next token's candidate limit
             }
             STEP_MARK(3);
             __syncthreads();
@@ -296,6 +304,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             {
                 const int am = s_cur[0];
                 lim = s_cur[1];
+                if (lim >= ncap) {                         // the next token may address a row this CTA does not hold
+                    if (tid == 0) tfirst[(size_t)bh * N] = -1;
+                    return;                                // uniform: every thread reads the same s_cur
+                }
                 if (wact && lane < NF) {
                     const float g = s_tok[4 * j + 2], omw = 1.f - g;
                     float* Kr = K + (size_t)am * KS + c0 + 4 * lane;
@@ -334,6 +346,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             if (n < N) ofin[(size_t)bh * N + n] = o_r[s];
         }
     }
+    for (int n = 32 * RPL + tid; n < N; n += AF_THREADS) ofin[(size_t)bh * N + n] = 0.f;   // rows this pass never held
 }
 
 }  // namespace slotscan

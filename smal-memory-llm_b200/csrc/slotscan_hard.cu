@@ -66,26 +66,37 @@ static cudaError_t opt_in_smem(F f, size_t bytes) {
     return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
+// rows a first-pass CTA of the forward address scan holds (see addr_fwd_direct_kernel)
+constexpr int AF_NCAP1 = 64;
+
+template <int DK, int RPL, typename Tin>
+static cudaError_t launch_addr_fwd_one(const slotscan_params& p, const void* q, const void* k, const float* gate,
+                                       const float* fr, const float* temp, const slotscan_log& L, int ncap, int second,
+                                       cudaStream_t st) {
+    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(ncap, DK, RPL, (int)sizeof(Tin)).total;
+    cudaError_t e;
+    if (p.occ_bin) {
+        auto kern = addr_fwd_direct_kernel<DK, RPL, true, Tin>;
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
+                                                L.ofin, L.tfirst, ncap, second);
+    } else {
+        auto kern = addr_fwd_direct_kernel<DK, RPL, false, Tin>;
+        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
+        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
+                                                L.ofin, L.tfirst, ncap, second);
+    }
+    return cudaGetLastError();
+}
+
 template <int DK, typename Tin>
 static cudaError_t launch_addr_fwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
                                    const float* fr, const float* temp, const slotscan_log& L, cudaStream_t st) {
-    const int rpl = p.N <= 192 ? 6 : 14;
-    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(p.N, DK, rpl, (int)sizeof(Tin)).total;
     cudaError_t e;
-#define AF_LAUNCH(RPL_, OCCB_)                                                                                     \
-    {                                                                                                              \
-        auto kern = addr_fwd_direct_kernel<DK, RPL_, OCCB_, Tin>;                                                 \
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                  \
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold,   \
-                                                L.kiold, L.ofin, L.tfirst);                                        \
-    }
-    if (p.N <= 192) {
-        if (p.occ_bin) AF_LAUNCH(6, true) else AF_LAUNCH(6, false)
-    } else {
-        if (p.occ_bin) AF_LAUNCH(14, true) else AF_LAUNCH(14, false)
-    }
-#undef AF_LAUNCH
-    return cudaGetLastError();
+    if (p.N <= AF_NCAP1) return launch_addr_fwd_one<DK, 2, Tin>(p, q, k, gate, fr, temp, L, p.N, 0, st);
+    if ((e = launch_addr_fwd_one<DK, 2, Tin>(p, q, k, gate, fr, temp, L, AF_NCAP1, 0, st)) != cudaSuccess) return e;
+    if (p.N <= 192) return launch_addr_fwd_one<DK, 6, Tin>(p, q, k, gate, fr, temp, L, p.N, 1, st);
+    return launch_addr_fwd_one<DK, 14, Tin>(p, q, k, gate, fr, temp, L, p.N, 1, st);
 }
 
 template <int DK, typename Tin>
