@@ -51,7 +51,7 @@ typedef struct {
 } slotscan_params;
 
 /* Argument check shared by every entry point: 0 or a SLOTSCAN_E_* code.  Supported: B,T,H,N,G >= 1;
- * DK, DV multiples of 8 in [8,128]; N*(DK+1) floats must fit the 227 KB shared memory of one CTA (N <= 440 at DK=128). */
+ * DK, DV in {8,16,32,64,128}; N <= 192 (the key rows of one sequence, N*(DK+4) floats, stay resident in one CTA's shared memory). */
 int slotscan_check(const slotscan_params* p);
 
 /* Log of one forward call: what the backward (and a caller that streams chunks) needs.  All caller-allocated.

@@ -26,6 +26,7 @@ struct AddrBwdSmem {
     int K, kinv, o, Qc, Dl, St, PD, misc, total;
     int qstride;
 };
+// N here is the number of key rows held in shared memory (the kernel's `ncap`)
 __host__ __device__ inline AddrBwdSmem addr_bwd_layout(int N, int DK) {
     AddrBwdSmem L;
     const int NP = (N + 3) & ~3;
@@ -42,20 +43,24 @@ __host__ __device__ inline AddrBwdSmem addr_bwd_layout(int N, int DK) {
     return L;
 }
 
-template <int DK, int RPL, bool OCCB, typename Tin>
-__global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
+// MINB = CTAs per SM asked of the compiler: the small first variant (ncap rows, RPL = 2) fits three.
+template <int DK, int RPL, bool OCCB, int MINB, typename Tin>
+__global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, const int* __restrict__ am_in,
     const float* __restrict__ kold, const float* __restrict__ oold_in, const float* __restrict__ kiold_in,
     const float* __restrict__ kfin, const float* __restrict__ ofin, const int* __restrict__ tfirst,
     const float* __restrict__ Din, Tin* __restrict__ dq, float* __restrict__ dg, float* __restrict__ dfr,
-    float* __restrict__ part /* [2][B*H]: dtemp, scalar dfr */) {
+    float* __restrict__ part /* [2][B*H]: dtemp, scalar dfr */, const int ncap, const int big_variant) {
+    // Two variants share the work: a sequence whose candidates all lie below row ncap (tfirst[ncap] == T) is taken
+    // by the small variant (ncap < N rows in shared memory, three CTAs per SM); the others by the full one
+    // (ncap = N, big_variant = 1).  Each CTA returns at once when the sequence belongs to the other variant.
     extern __shared__ __align__(16) float smem[];
     constexpr int NI = (DK + 15) / 16;
     constexpr int IPS = CH * DK / 8;                    // 8-element items per stream and chunk
     constexpr int NITEM = (3 * IPS + AB_THREADS - 1) / AB_THREADS;   // q, k, kold items per thread
     const int N = p.N, T = p.T, H = p.H;
-    const AddrBwdSmem L = addr_bwd_layout(N, DK);
+    const AddrBwdSmem L = addr_bwd_layout(ncap, DK);
     float* K = smem + L.K;
     float* s_kinv = smem + L.kinv;
     float* s_o = smem + L.o;
@@ -70,7 +75,6 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
     float* s_kiold = s_oold + CH;
     int* s_am = reinterpret_cast<int*>(s_kiold + CH);
     float* s_pr = reinterpret_cast<float*>(s_am + CH);  // [AB_WARPS][CH] partial <qn, dqn>
-    float* s_red = s_pr + CH * AB_WARPS;
 
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -78,17 +82,22 @@ __global__ void __launch_bounds__(AB_THREADS, 2) addr_bwd_chunked_kernel(
     const float temp = temp_p[0], eps = p.eps;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    for (int i = tid; i < N * DK; i += AB_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
-    for (int i = tid; i < N; i += AB_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
+    {
+        const int split = (ncap < N) ? ncap : 0;                    // 0: a single variant handles everything
+        const bool small_seq = split > 0 && tfirst[(size_t)bh * N + split] >= T;
+        if (big_variant ? small_seq : (split > 0 && !small_seq)) return;    // uniform per CTA
+    }
+    for (int i = tid; i < ncap * DK; i += AB_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
+    for (int i = tid; i < ncap; i += AB_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
     __syncthreads();
-    for (int n = warp; n < N; n += AB_WARPS) {          // norms of the final state
+    for (int n = warp; n < ncap; n += AB_WARPS) {       // norms of the final state
         const int col = lane * 4;
         const float4 Kn = (col < DK) ? ld4(K + (size_t)n * DK + col) : zero4;
         const float nsq = warp_sum(dot4(Kn, Kn));
         if (lane == 0) s_kinv[n] = fminf(rsqrtf(nsq), 1e6f);
     }
     // candidates at token t: rows n with tfirst[n] <= t; uniform, walked down as t decreases
-    int lim = N - 1;
+    int lim = ncap - 1;
     float dtemp_acc = 0.f, dfr_acc = 0.f;
     float dO_r[RPL];                                      // only used when the penalty is on o itself (!OCCB)
 #pragma unroll

@@ -19,7 +19,7 @@
 namespace slotscan {
 
 #ifdef SLOTSCAN_PHASE_TIMING
-__device__ unsigned long long g_phase_cycles[16];
+static __device__ unsigned long long g_phase_cycles[16];
 #define STEP_T0() long long _st = clock64()
 #define STEP_MARK(I) do { long long _n = clock64(); _acc[I] += _n - _st; _st = _n; } while (0)
 #else

@@ -17,9 +17,7 @@
 #include <vector>
 
 #include "slotscan_common.cuh"
-#include "slotscan_addr_fwd.cuh"
-#include "slotscan_addr_bwd.cuh"
-#include "slotscan_rows.cuh"
+#include "slotscan_launch.h"
 
 namespace slotscan {
 
@@ -61,157 +59,64 @@ struct ProfScope {
 
 constexpr size_t SMEM_CAP = 227 * 1024;
 
-template <typename F>
-static cudaError_t opt_in_smem(F f, size_t bytes) {
-    return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-}
-
-// rows a first-pass CTA of the forward address scan holds (see addr_fwd_direct_kernel)
-constexpr int AF_NCAP1 = 64;
-
-template <int DK, int RPL, typename Tin>
-static cudaError_t launch_addr_fwd_one(const slotscan_params& p, const void* q, const void* k, const float* gate,
-                                       const float* fr, const float* temp, const slotscan_log& L, int ncap, int second,
-                                       cudaStream_t st) {
-    const size_t sm = sizeof(float) * (size_t)addr_fwd_layout(ncap, DK, RPL, (int)sizeof(Tin)).total;
-    cudaError_t e;
-    if (p.occ_bin) {
-        auto kern = addr_fwd_direct_kernel<DK, RPL, true, Tin>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
-                                                L.ofin, L.tfirst, ncap, second);
-    } else {
-        auto kern = addr_fwd_direct_kernel<DK, RPL, false, Tin>;
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;
-        kern<<<p.B * p.H, AF_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.oold, L.kiold,
-                                                L.ofin, L.tfirst, ncap, second);
-    }
-    return cudaGetLastError();
-}
-
-template <int DK, typename Tin>
-static cudaError_t launch_addr_fwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
-                                   const float* fr, const float* temp, const slotscan_log& L, cudaStream_t st) {
-    cudaError_t e;
-    if (p.N <= AF_NCAP1) return launch_addr_fwd_one<DK, 2, Tin>(p, q, k, gate, fr, temp, L, p.N, 0, st);
-    if ((e = launch_addr_fwd_one<DK, 2, Tin>(p, q, k, gate, fr, temp, L, AF_NCAP1, 0, st)) != cudaSuccess) return e;
-    if (p.N <= 192) return launch_addr_fwd_one<DK, 6, Tin>(p, q, k, gate, fr, temp, L, p.N, 1, st);
-    return launch_addr_fwd_one<DK, 14, Tin>(p, q, k, gate, fr, temp, L, p.N, 1, st);
-}
-
-template <int DK, typename Tin>
-static cudaError_t launch_addr_bwd(const slotscan_params& p, const void* q, const void* k, const float* gate,
-                                   const float* fr, const float* temp, const slotscan_log& L, const float* Dn, void* dq,
-                                   float* dgate, float* dfr, float* part, cudaStream_t st) {
-    const size_t sm = sizeof(float) * (size_t)addr_bwd_layout(p.N, DK).total;
-    cudaError_t e;
-#define AB_LAUNCH(RPL_, OCCB_)                                                                                      \
-    {                                                                                                               \
-        auto kern = addr_bwd_chunked_kernel<DK, RPL_, OCCB_, Tin>;                                                  \
-        if ((e = opt_in_smem(kern, sm)) != cudaSuccess) return e;                                                   \
-        kern<<<p.B * p.H, AB_THREADS, sm, st>>>(p, (const Tin*)q, (const Tin*)k, gate, fr, temp, L.addr, L.kold,    \
-                                                L.oold, L.kiold, L.kfin, L.ofin, L.tfirst, Dn, (Tin*)dq, dgate, dfr, \
-                                                part);                                                              \
-    }
-    if (p.N <= 192) {
-        if (p.occ_bin) AB_LAUNCH(6, true) else AB_LAUNCH(6, false)
-    } else {
-        if (p.occ_bin) AB_LAUNCH(14, true) else AB_LAUNCH(14, false)
-    }
-#undef AB_LAUNCH
-    return cudaGetLastError();
-}
-
-template <int D, typename Tin, typename Tsn>
-static cudaError_t launch_replay(const slotscan_params& p, const void* x, const float* gate, const int* am,
-                                 const int* tfirst, void* xbuf, float* xold, float* xfin, cudaStream_t st) {
-    constexpr int RPB = ROW_THREADS / (D / 8);
-    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB);
-    replay_rows_kernel<D, Tin, Tsn><<<grid, ROW_THREADS, 0, st>>>(p, (const Tin*)x, gate, am, tfirst, (Tsn*)xbuf, xold, xfin);
-    return cudaGetLastError();
-}
-template <int D, typename Tin, typename Tsn>
-static cudaError_t launch_rows_bwd(const slotscan_params& p, int ntensors, const RowsBwdArgs<Tin, Tsn>& a0,
-                                   const RowsBwdArgs<Tin, Tsn>& a1, const float* gate, const int* am, const int* tfirst,
-                                   cudaStream_t st) {
-    constexpr int RPB = ROW_THREADS / (D / 8);
-    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB, ntensors);
-    constexpr size_t sm = rows_bwd_smem_bytes<D, Tin>();
-    auto kern = rows_bwd_kernel<D, Tin, Tsn>;
-    cudaError_t e = opt_in_smem(kern, sm);
-    if (e != cudaSuccess) return e;
-    kern<<<grid, ROW_THREADS, sm, st>>>(p, a0, a1, gate, am, tfirst);
-    return cudaGetLastError();
-}
-
-#define DISPATCH_D(D_, CALL)                                   \
-    switch (D_) {                                              \
-        case 8: { constexpr int DD = 8; CALL; } break;         \
-        case 16: { constexpr int DD = 16; CALL; } break;       \
-        case 32: { constexpr int DD = 32; CALL; } break;       \
-        case 64: { constexpr int DD = 64; CALL; } break;       \
-        case 128: { constexpr int DD = 128; CALL; } break;     \
-        default: { constexpr int DD = 0; (void)DD; return cudaErrorInvalidValue; }  \
-    }
-
-template <typename Tin, typename Tsn>
-static cudaError_t fwd_typed(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
-                             const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
-                             cudaStream_t st) {
+static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
+                           const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
+                           cudaStream_t st) {
     cudaError_t e;
     {
         ProfScope ps(K_ADDR_FWD, st);
-        DISPATCH_D(p.DK, e = (launch_addr_fwd<DD, Tin>(p, q ? q : k, k, gate, fr, temp, L, st)));
+        e = (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, st)
+                                         : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, st);
     }
     if (e != cudaSuccess) return e;
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
     {
         ProfScope ps(K_REPLAY_K, st);
-        DISPATCH_D(p.DK, e = (launch_replay<DD, Tin, Tsn>(p, k, gate, L.addr, L.tfirst, kbuf, L.kold, L.kfin, st)));
+        e = run_replay(p, p.DK, k, gate, L.addr, L.tfirst, kbuf, L.kold, L.kfin, st);
     }
     if (e != cudaSuccess) return e;
     {
         ProfScope ps(K_REPLAY_V, st);
-        DISPATCH_D(p.DV, e = (launch_replay<DD, Tin, Tsn>(p, v, gate, L.addr, L.tfirst, vbuf, L.vold, L.vfin, st)));
+        e = run_replay(p, p.DV, v, gate, L.addr, L.tfirst, vbuf, L.vold, L.vfin, st);
     }
     return e;
 }
 
-template <typename Tin, typename Tsn>
-static cudaError_t bwd_typed(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
-                             const float* fr, const float* temp, const slotscan_log& L, const void* dkbuf,
-                             const void* dvbuf, float* Dn, float* part, void* dk, void* dq, void* dv, float* dgate,
-                             float* dfr, float* dtemp, cudaStream_t st) {
+static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
+                           const float* fr, const float* temp, const slotscan_log& L, const void* dkbuf, const void* dvbuf,
+                           float* Dn, float* part, void* dk, void* dq, void* dv, float* dgate, float* dfr, float* dtemp,
+                           cudaStream_t st) {
     cudaError_t e;
     // keys and values are independent given the log: one launch (blockIdx.z) when dk == dv, each into its own D table
     float* DnV = Dn + (size_t)p.B * p.H * p.T * p.N;
-    const RowsBwdArgs<Tin, Tsn> ak{(const Tin*)k, L.kold, L.kfin, (const Tsn*)dkbuf, (Tin*)dk, Dn};
-    const RowsBwdArgs<Tin, Tsn> av{(const Tin*)v, L.vold, L.vfin, (const Tsn*)dvbuf, (Tin*)dv, DnV};
+    const RowsBwdPtrs ak{k, L.kold, L.kfin, dkbuf, dk, Dn};
+    const RowsBwdPtrs av{v, L.vold, L.vfin, dvbuf, dv, DnV};
     if (p.DK == p.DV) {
         ProfScope ps(K_ROWS_BWD_K, st);
-        DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 2, ak, av, gate, L.addr, L.tfirst, st)));
+        e = run_rows_bwd(p, p.DK, 2, ak, av, gate, L.addr, L.tfirst, st);
     } else {
         {
             ProfScope ps(K_ROWS_BWD_K, st);
-            DISPATCH_D(p.DK, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 1, ak, ak, gate, L.addr, L.tfirst, st)));
+            e = run_rows_bwd(p, p.DK, 1, ak, ak, gate, L.addr, L.tfirst, st);
         }
         if (e != cudaSuccess) return e;
         ProfScope ps(K_ROWS_BWD_V, st);
-        DISPATCH_D(p.DV, e = (launch_rows_bwd<DD, Tin, Tsn>(p, 1, av, av, gate, L.addr, L.tfirst, st)));
+        e = run_rows_bwd(p, p.DV, 1, av, av, gate, L.addr, L.tfirst, st);
     }
     if (e != cudaSuccess) return e;
     {
         ProfScope ps(K_ADDR_BWD, st);
-        DISPATCH_D(p.DK, e = (launch_addr_bwd<DD, Tin>(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st)));
+        e = (p.in_dtype == SLOTSCAN_F32)
+                ? run_addr_bwd_f32(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st)
+                : run_addr_bwd_bf16(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st);
     }
     if (e != cudaSuccess) return e;
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
     ProfScope ps(K_FINISH, st);
     finish_scalars_kernel<<<1, 32, 0, st>>>(part, p.B * p.H, p.fr_per_token, dtemp, dfr);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    if (q == nullptr) {
+    if (q == nullptr) {       // the search query is the stored key: both gradient paths land in dk
         const size_t n4 = (size_t)p.B * p.T * p.H * p.DK / 4;
-        add_into_kernel<Tin><<<592, 256, 0, st>>>((Tin*)dk, (const Tin*)dq, n4);
+        if (p.in_dtype == SLOTSCAN_F32) add_into_kernel<float><<<592, 256, 0, st>>>((float*)dk, (const float*)dq, n4);
+        else add_into_kernel<__nv_bfloat16><<<592, 256, 0, st>>>((__nv_bfloat16*)dk, (const __nv_bfloat16*)dq, n4);
         e = cudaGetLastError();
     }
     return e;
@@ -230,9 +135,9 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (p->B < 1 || p->T < 1 || p->H < 1 || p->N < 1 || p->G < 1) return SLOTSCAN_E_SHAPE;
     if (p->DK < 8 || p->DK > 128 || (p->DK & (p->DK - 1))) return SLOTSCAN_E_SHAPE;
     if (p->DV < 8 || p->DV > 128 || (p->DV & (p->DV - 1))) return SLOTSCAN_E_SHAPE;
-    if (sizeof(float) * (size_t)addr_fwd_layout(p->N, p->DK, p->N <= 192 ? 6 : 14, 4).total + 1024 > SMEM_CAP || p->N > 448)
+    if (p->N > 192) return SLOTSCAN_E_SHAPE;
+    if (addr_fwd_smem_bytes(p->N, p->DK, 4) + 1024 > SMEM_CAP || addr_bwd_smem_bytes(p->N, p->DK) + 1024 > SMEM_CAP)
         return SLOTSCAN_E_SHAPE;
-    if (sizeof(float) * (size_t)addr_bwd_layout(p->N, p->DK).total + 1024 > SMEM_CAP) return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
     if (p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
     if (p->snap_dtype != SLOTSCAN_F32 && p->snap_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
@@ -252,14 +157,7 @@ extern "C" int slotscan_hard_fwd(const slotscan_params* p, const void* k, const 
         misaligned(log->vold) || misaligned(log->kfin) || misaligned(log->vfin))
         return SLOTSCAN_E_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e;
-    if (p->in_dtype == SLOTSCAN_F32)
-        e = (p->snap_dtype == SLOTSCAN_F32) ? fwd_typed<float, float>(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st)
-                                            : fwd_typed<float, __nv_bfloat16>(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st);
-    else
-        e = (p->snap_dtype == SLOTSCAN_F32)
-                ? fwd_typed<__nv_bfloat16, float>(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st)
-                : fwd_typed<__nv_bfloat16, __nv_bfloat16>(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st);
+    const cudaError_t e = fwd_run(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st);
     return (int)e;
 }
 
@@ -293,43 +191,17 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
     float* Dn = (float*)scratch;
     float* part = (float*)((char*)scratch + dn);
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e;
-    if (p->in_dtype == SLOTSCAN_F32)
-        e = (p->snap_dtype == SLOTSCAN_F32)
-                ? bwd_typed<float, float>(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st)
-                : bwd_typed<float, __nv_bfloat16>(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st);
-    else
-        e = (p->snap_dtype == SLOTSCAN_F32)
-                ? bwd_typed<__nv_bfloat16, float>(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st)
-                : bwd_typed<__nv_bfloat16, __nv_bfloat16>(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st);
+    const cudaError_t e = bwd_run(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st);
     return (int)e;
-}
-
-template <typename F>
-static void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* name, F f) {
-    if (n < cap) {
-        cudaFuncAttributes a;
-        if (cudaFuncGetAttributes(&a, f) == cudaSuccess) {
-            snprintf(out[n].name, sizeof(out[n].name), "%s", name);
-            out[n].regs = a.numRegs;
-            out[n].local_bytes = (int)a.localSizeBytes;
-            out[n].static_smem = (int)a.sharedSizeBytes;
-            out[n].max_threads = a.maxThreadsPerBlock;
-        }
-    }
-    n++;
 }
 
 extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     int n = 0;
-    fill_attr(out, cap, n, "addr_fwd<128,f32>", addr_fwd_direct_kernel<128, 6, true, float>);
-    fill_attr(out, cap, n, "addr_fwd<128,bf16>", addr_fwd_direct_kernel<128, 6, true, __nv_bfloat16>);
-    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16>);
-    fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float>);
-    fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16>);
-    fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float>);
-    fill_attr(out, cap, n, "addr_bwd<128,f32>", addr_bwd_chunked_kernel<128, 6, true, float>);
-    fill_attr(out, cap, n, "addr_bwd<128,bf16>", addr_bwd_chunked_kernel<128, 6, true, __nv_bfloat16>);
+    attrs_addr_fwd_f32(out, cap, n);
+    attrs_addr_fwd_bf16(out, cap, n);
+    attrs_rows(out, cap, n);
+    attrs_addr_bwd_f32(out, cap, n);
+    attrs_addr_bwd_bf16(out, cap, n);
     return n;
 }
 
@@ -405,14 +277,3 @@ extern "C" int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k
                              dk, dq, dv, dgate, dfr, dtemp, stream);
 }
 
-#ifdef SLOTSCAN_PHASE_TIMING
-// development aid (not part of the ABI header): per-phase clock totals of the chunked kernels, summed over CTAs
-extern "C" int slotscan_debug_phase_cycles(unsigned long long* out8, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out8, slotscan::g_phase_cycles, 16 * sizeof(unsigned long long));
-    if (e == cudaSuccess && reset) {
-        unsigned long long z[16] = {0};
-        e = cudaMemcpyToSymbol(slotscan::g_phase_cycles, z, sizeof(z));
-    }
-    return (int)e;
-}
-#endif

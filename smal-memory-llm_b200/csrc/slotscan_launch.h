@@ -1,0 +1,71 @@
+// Internal launch interface between the translation units of libslotscan.so (not part of the C ABI).
+// The kernels are templates over key width, live row slots and dtypes; each .cu instantiates one family so the
+// library builds in parallel.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "slotscan.h"
+
+namespace slotscan {
+
+// rows a first-pass CTA of the address kernels holds in shared memory (sequences that need more rerun at full size)
+constexpr int AF_NCAP1 = 64;
+
+template <typename F>
+static inline cudaError_t opt_in_smem(F f, size_t bytes) {
+    return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+// in_dtype / snap_dtype of p select the instantiation
+cudaError_t run_addr_fwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
+                             const float* temp, const slotscan_log& L, cudaStream_t st);
+cudaError_t run_addr_fwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
+                              const float* temp, const slotscan_log& L, cudaStream_t st);
+cudaError_t run_addr_bwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
+                             const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
+                             float* part, cudaStream_t st);
+cudaError_t run_addr_bwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
+                              const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
+                              float* part, cudaStream_t st);
+// one tensor (keys: D = DK, values: D = DV) through the forward row replay
+cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
+                       void* xbuf, float* xold, float* xfin, cudaStream_t st);
+// reverse row scan; ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs the first set only
+struct RowsBwdPtrs { const void* x; const float* xold; const float* xfin; const void* dxbuf; void* dx; float* Dn; };
+cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
+                         const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+
+size_t addr_fwd_smem_bytes(int ncap, int DK, int in_bytes);
+size_t addr_bwd_smem_bytes(int ncap, int DK);
+void attrs_addr_fwd_f32(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_addr_fwd_bf16(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_addr_bwd_f32(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_addr_bwd_bf16(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_rows(slotscan_kernel_attr* out, int cap, int& n);
+
+template <typename F>
+static inline void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* name, F f) {
+    if (n < cap) {
+        cudaFuncAttributes a;
+        if (cudaFuncGetAttributes(&a, f) == cudaSuccess) {
+            snprintf(out[n].name, sizeof(out[n].name), "%s", name);
+            out[n].regs = a.numRegs;
+            out[n].local_bytes = (int)a.localSizeBytes;
+            out[n].static_smem = (int)a.sharedSizeBytes;
+            out[n].max_threads = a.maxThreadsPerBlock;
+        }
+    }
+    n++;
+}
+
+#define SLOTSCAN_DISPATCH_D(D_, CALL)                          \
+    switch (D_) {                                              \
+        case 8: { constexpr int DD = 8; CALL; } break;         \
+        case 16: { constexpr int DD = 16; CALL; } break;       \
+        case 32: { constexpr int DD = 32; CALL; } break;       \
+        case 64: { constexpr int DD = 64; CALL; } break;       \
+        case 128: { constexpr int DD = 128; CALL; } break;     \
+        default: return cudaErrorInvalidValue;                 \
+    }
+
+}  // namespace slotscan
