@@ -96,6 +96,21 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def max_over_ranks(values, device):
+    """Element-wise MAX of a list of floats over all ranks (the time of a multi-GPU step is its slowest rank's)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def whole_job_tokens_per_s(B_per_rank, T, world, steps, ms):
+    """Weak scaling: every rank scans its own B_per_rank sequences; the job's throughput counts all of them."""
+    return B_per_rank * T * world * steps / (ms * 1e-3)
+
+
 def make_host_inputs(B, T, H, DK, DV, seed, dist="bench"):
     from tests.scan_cases import make_inputs
     return make_inputs(dist, B, T, H, DK, DV, seed=seed)
@@ -240,21 +255,28 @@ def run_gpu(args, rank, local_rank, world):
     ms_e2e = f0.elapsed_time(f1)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = sum(t.numel() * t.element_size() for t in hout)
-    if dist_on:
-        tt = torch.tensor([ms, ms_e2e], device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = tt.tolist()
+    ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev)
     if rank == 0:
         toks = B * T * world * args.steps
         ab = algorithmic_bytes_per_token_head(N, DK, DV, G, 2, 2)
         peak, peak_kind = hbm_peak()
         # bytes each kernel is responsible for, per token and head (sums to ab["total"])
         kb_bytes = {"addr_fwd": 2 * DK * 2 + 8, "replay_rows_k": N * DK * 2 / G, "replay_rows_v": DV * 2 + N * DV * 2 / G,
-                    "rows_bwd_k": DK * 2 + N * DK * 2 / G + DK * 2, "rows_bwd_v": DV * 2 + N * DV * 2 / G + DV * 2,
+                    "rows_bwd_k": (DK + DV) * 2 + N * (DK + DV) * 2 / G + (DK + DV) * 2, "rows_bwd_v": 0,
                     "addr_bwd": DK * 2 + 8 + DK * 2 + 8, "finish": 0}
+        if DK != DV:     # keys and values then run as two launches
+            kb_bytes["rows_bwd_k"] = DK * 2 + N * DK * 2 / G + DK * 2
+            kb_bytes["rows_bwd_v"] = DV * 2 + N * DV * 2 / G + DV * 2
         launches = sum(c for c, _ in prof.values())
-        kern = {n: {"launches": c, "ms_per_launch": (t / c if c else None), "share": t / max(sum(x for _, x in prof.values()), 1e-9)}
-                for n, (c, t) in prof.items()}
+        tot_ms = max(sum(x for _, x in prof.values()), 1e-9)
+        kern = {}
+        for n, (c, t) in prof.items():
+            if not c:
+                continue
+            ms_l = t / c
+            gbs = kb_bytes[n] * B * T * H / (ms_l * 1e-3) / 1e9
+            kern[n] = {"launches": c, "ms_per_launch": ms_l, "share": t / tot_ms,
+                       "algorithmic_gbs": gbs, "frac_of_hbm_peak": gbs / peak}
         top = max(prof, key=lambda n: prof[n][1])
         top_ms = prof[top][1] / max(prof[top][0], 1)
         top_bytes = kb_bytes[top] * B * T * H
@@ -284,8 +306,9 @@ def run_gpu(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under profiles/
-TRAFFIC = {}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at the benchmark size, from the ncu captures
+# summarised under profiles/ (taken at B = 8 and scaled by 8: traffic is proportional to the batch)
+TRAFFIC = {"replay_rows_k": 8 * (13.03e6 + 274.17e6), "replay_rows_v": 8 * (13.03e6 + 274.17e6), "addr_fwd": 8 * 25.6e6}
 
 
 def main():

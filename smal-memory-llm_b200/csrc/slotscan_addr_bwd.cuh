@@ -51,7 +51,8 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
     const float* __restrict__ kold, const float* __restrict__ oold_in, const float* __restrict__ kiold_in,
     const float* __restrict__ kfin, const float* __restrict__ ofin, const int* __restrict__ tfirst,
     const float* __restrict__ Din, Tin* __restrict__ dq, float* __restrict__ dg, float* __restrict__ dfr,
-    float* __restrict__ part /* [2][B*H]: dtemp, scalar dfr */, const int ncap, const int big_variant) {
+    float* __restrict__ part /* [2][B*H][part_stride]: dtemp, scalar dfr; this kernel fills slot part_stride - 1 */,
+    const int ncap, const int big_variant, const int skip_rows, const int part_stride) {
     // Two variants share the work: a sequence whose candidates all lie below row ncap (tfirst[ncap] == T) is taken
     // by the small variant (ncap < N rows in shared memory, three CTAs per SM); the others by the full one
     // (ncap = N, big_variant = 1).  Each CTA returns at once when the sequence belongs to the other variant.
@@ -86,6 +87,8 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
         const int split = (ncap < N) ? ncap : 0;                    // 0: a single variant handles everything
         const bool small_seq = split > 0 && tfirst[(size_t)bh * N + split] >= T;
         if (big_variant ? small_seq : (split > 0 && !small_seq)) return;    // uniform per CTA
+        // sequences with at most skip_rows candidate rows are taken by the token-parallel kernel (slotscan_addr_gather.cuh)
+        if (skip_rows > 0 && (N <= skip_rows || tfirst[(size_t)bh * N + skip_rows] >= T)) return;
     }
     for (int i = tid; i < ncap * DK; i += AB_THREADS) K[i] = kfin[(size_t)bh * N * DK + i];
     for (int i = tid; i < ncap; i += AB_THREADS) s_o[i] = ofin[(size_t)bh * N + i];
@@ -406,8 +409,8 @@ _Pragma("unroll") \
     if (tid == 0) {
         float a = 0.f, c = 0.f;
         for (int w = 0; w < AB_WARPS; w++) { a += s_pr[w]; c += s_pr[AB_WARPS + w]; }
-        part[bh] = a;
-        part[(size_t)p.B * H + bh] = c;
+        part[(size_t)bh * part_stride + part_stride - 1] = a;
+        part[((size_t)p.B * H + bh) * part_stride + part_stride - 1] = c;
     }
 }
 

@@ -212,12 +212,15 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
             const int n = min(lane + 32 * s, N - 1);                                                           \
             const float* Kr = K + (size_t)n * KS + c0;                                                         \
-            float a0 = 0.f, a1 = 0.f, r0 = 0.f, r1 = 0.f;                                                      \
+            float4 aS = zero4, aR = zero4;      /* 8 independent FMA chains; summed once at the end */          \
             _Pragma("unroll") for (int i = 0; i < NF; i++) {                                                   \
                 const float4 K4 = ld4(Kr + 4 * i);                                                             \
-                if (i & 1) { a1 += dot4(K4, q4[i]); r1 += dot4(K4, k4[i]); }                                   \
-                else { a0 += dot4(K4, q4[i]); r0 += dot4(K4, k4[i]); }                                         \
+                aS.x = fmaf(K4.x, q4[i].x, aS.x); aS.y = fmaf(K4.y, q4[i].y, aS.y);                            \
+                aS.z = fmaf(K4.z, q4[i].z, aS.z); aS.w = fmaf(K4.w, q4[i].w, aS.w);                            \
+                aR.x = fmaf(K4.x, k4[i].x, aR.x); aR.y = fmaf(K4.y, k4[i].y, aR.y);                            \
+                aR.z = fmaf(K4.z, k4[i].z, aR.z); aR.w = fmaf(K4.w, k4[i].w, aR.w);                            \
             }                                                                                                  \
+            const float a0 = aS.x + aS.y, a1 = aS.z + aS.w, r0 = aR.x + aR.y, r1 = aR.z + aR.w;                \
             part[(s * AF_WARPS + warp) * 32 + lane] = make_float2(a0 + a1, r0 + r1);                           \
         }                                                                                                      \
       }                                                                                                        \

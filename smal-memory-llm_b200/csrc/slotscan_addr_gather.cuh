@@ -1,0 +1,197 @@
+// Address backward for sequences that use FEW rows (at most GATHER_ROWS = 32): token-parallel, no resident state.
+//
+// The chunked address backward (slotscan_addr_bwd.cuh) walks a sequence's chunks one after another because it carries
+// the key rows in shared memory.  But every version of every row already sits in memory: the undo log holds the row
+// BEFORE each write, kold[t], and kfin holds the rows after the last one.  The key row n as token t sees it is
+//     kold[t']  with t' = the first token >= t that writes row n,   or  kfin[n]  if no later token does,
+// and its norm / occupancy are kiold[t'], oold[t'] (or those of the final state).  So with a table of "next write of
+// row n at or after t" the tokens of a sequence are independent (occupancy penalty on [o >= eps]: no carried
+// occupancy adjoint) and the work spreads over (sequence, head) x (32-token chunk) CTAs:
+//   next_write_kernel    one warp per (sequence, head) walks the address log backwards once and stores, per chunk,
+//                        the next write of each of the 32 rows at the chunk's END;
+//   addr_bwd_gather_kernel  per CTA: warp 0 expands that to a per-token table; then each warp takes 4 tokens:
+//                        scores by 8 lanes per row (4 rows at a time, 3 shuffle stages), softmax adjoint with
+//                        lane = row, dq accumulated with lane = 4 columns over the rows (no reduction).
+// A sequence that ever made row 32 a candidate is left to the chunked kernel.  [reference addr_bwd, slotkern_cuda.py:264-443]
+#pragma once
+#include "slotscan_addr_fwd.cuh"
+
+namespace slotscan {
+
+constexpr int GATHER_ROWS = 32;      // lanes = rows in the softmax part
+constexpr int GC = 32;               // tokens per CTA
+constexpr int GA_THREADS = 256;
+constexpr int GA_WARPS = GA_THREADS / 32;
+
+// true if the sequence never had more than GATHER_ROWS candidate rows
+__device__ __forceinline__ bool gather_sequence(const int* tfirst_bh, int N, int T) {
+    return N <= GATHER_ROWS || tfirst_bh[GATHER_ROWS] >= T;
+}
+
+// vend[bh][c][n]: first token >= (c+1)*GC that writes row n, or -1
+static __global__ void __launch_bounds__(32) next_write_kernel(const slotscan_params p, const int* __restrict__ am,
+                                                        const int* __restrict__ tfirst, int* __restrict__ vend) {
+    const int N = p.N, T = p.T, H = p.H;
+    const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
+    if (!gather_sequence(tfirst + (size_t)bh * N, N, T)) return;
+    const int nc = (T + GC - 1) / GC;
+    int ver = -1;
+    for (int c = nc - 1; c >= 0; c--) {
+        vend[((size_t)bh * nc + c) * GATHER_ROWS + lane] = ver;
+        const int t = c * GC + lane;
+        const int a = (t < T) ? am[((size_t)b * T + t) * H + h] : -1;
+        for (int i = GC - 1; i >= 0; i--) {
+            const int ai = __shfl_sync(FULL, a, i);
+            if (ai == lane) ver = c * GC + i;
+        }
+    }
+}
+
+template <int DK, typename Tin>
+__global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
+    const slotscan_params p, const Tin* __restrict__ q, const float* __restrict__ gate, const float* __restrict__ fr,
+    const float* __restrict__ temp_p, const int* __restrict__ am, const float* __restrict__ kold,
+    const float* __restrict__ oold, const float* __restrict__ kiold, const float* __restrict__ kfin,
+    const float* __restrict__ ofin, const int* __restrict__ tfirst, const int* __restrict__ vend,
+    const float* __restrict__ Din, Tin* __restrict__ dq, float* __restrict__ dg, float* __restrict__ dfr,
+    float* __restrict__ part, const int part_stride) {
+    static_assert(DK >= 32, "8 lanes x float4 per row");
+    constexpr int CPL = DK / 8;                   // columns per lane in the score pass (8 lanes per row)
+    constexpr int NF = CPL / 4;
+    __shared__ int s_ver[GC][GATHER_ROWS];        // next write of row n as token i sees it
+    __shared__ int s_am[GC];
+    __shared__ int s_tf[GATHER_ROWS];
+    __shared__ float s_kfinv[GATHER_ROWS], s_ofin[GATHER_ROWS];
+    __shared__ float s_S[GA_WARPS][GATHER_ROWS];
+    __shared__ float s_red[2][GA_WARPS];
+    const int N = p.N, T = p.T, H = p.H;
+    const int c = blockIdx.x, bh = blockIdx.y, b = bh / H, h = bh % H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (!gather_sequence(tfirst + (size_t)bh * N, N, T)) return;          // uniform per CTA
+    const int nc = (T + GC - 1) / GC, t0 = c * GC, tc = min(GC, T - t0);
+    const int NR = min(N, GATHER_ROWS);
+    const float temp = temp_p[0], eps = p.eps;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    if (tid < GC) s_am[tid] = (tid < tc) ? am[((size_t)b * T + t0 + tid) * H + h] : -1;
+    if (tid >= 32 && tid < 32 + GATHER_ROWS) {
+        const int n = tid - 32;
+        s_tf[n] = (n < N) ? tfirst[(size_t)bh * N + n] : T;
+        s_ofin[n] = (n < N) ? ofin[(size_t)bh * N + n] : 0.f;
+    }
+    for (int n = warp; n < NR; n += GA_WARPS) {   // norms of the final rows
+        const int col = lane * 4;
+        const float4 Kn = (col < DK) ? ld4(kfin + ((size_t)bh * N + n) * DK + col) : zero4;
+        const float nsq = warp_sum(dot4(Kn, Kn));
+        if (lane == 0) s_kfinv[n] = fminf(rsqrtf(nsq), 1e6f);
+    }
+    __syncthreads();
+    if (warp == 0) {                              // per-token versions, walking the chunk backwards
+        int ver = vend[((size_t)bh * nc + c) * GATHER_ROWS + lane];
+        for (int i = GC - 1; i >= 0; i--) {
+            if (s_am[i] == lane) ver = t0 + i;
+            s_ver[i][lane] = ver;
+        }
+    }
+    __syncthreads();
+    float dtemp_acc = 0.f, dfr_acc = 0.f;
+    for (int i = warp; i < tc; i += GA_WARPS) {
+        const int t = t0 + i;
+        const size_t ix = ((size_t)b * T + t) * H + h;
+        int lim = NR - 1;
+        while (lim > 0 && s_tf[lim] > t) lim--;
+        // ---- scores: 8 lanes per row, 4 rows per pass ----
+        const int r = lane >> 3, cp = (lane & 7) * CPL;
+        float4 q4[NF];
+        float qq = 0.f;
+#pragma unroll
+        for (int f = 0; f < NF; f++) { q4[f] = ld4(q + ix * DK + cp + 4 * f); qq += dot4(q4[f], q4[f]); }
+        qq += __shfl_xor_sync(FULL, qq, 1); qq += __shfl_xor_sync(FULL, qq, 2); qq += __shfl_xor_sync(FULL, qq, 4);
+        const float qinv = fminf(rsqrtf(qq), 1e6f);
+        for (int base = 0; base <= lim; base += 4) {
+            const int n = min(base + r, lim);
+            const int ver = s_ver[i][n];
+            const float* row = (ver < 0) ? kfin + ((size_t)bh * N + n) * DK : kold + (((size_t)b * T + ver) * H + h) * DK;
+            float a = 0.f;
+#pragma unroll
+            for (int f = 0; f < NF; f++) a += dot4(ld4(row + cp + 4 * f), q4[f]);
+            a += __shfl_xor_sync(FULL, a, 1); a += __shfl_xor_sync(FULL, a, 2); a += __shfl_xor_sync(FULL, a, 4);
+            if ((lane & 7) == 0 && base + r <= lim) s_S[warp][base + r] = a;
+        }
+        __syncwarp();
+        // ---- softmax adjoint: lane = row ----
+        const bool in = lane <= lim;
+        const int ver = in ? s_ver[i][lane] : -1;
+        const size_t vix = ((size_t)b * T + (ver < 0 ? 0 : ver)) * H + h;
+        const float ki = !in ? 0.f : (ver < 0 ? s_kfinv[lane] : kiold[vix]);
+        const float oc = !in ? 0.f : (ver < 0 ? s_ofin[lane] : oold[vix]);
+        const float g = gate_eff(gate[ix], p.hard_gate), frv = p.fr_per_token ? fr[ix] : fr[0];
+        const float s = in ? temp * qinv * (ki * s_S[warp][lane]) : 0.f;
+        const float occ = oc >= eps ? 1.f : 0.f;
+        const float z = s - frv * occ;
+        const int ei = (int)__reduce_min_sync(FULL, (unsigned)((in && oc < eps) ? lane : BIGI));   // lowest free row
+        const bool ok = in && (oc >= eps || lane == ei);
+        const unsigned kk = __reduce_max_sync(FULL, ok ? ord_key(z) : 0u);
+        const float zmax = __uint_as_float((kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk);
+        float dw = 0.f;
+        if (in) {
+            const size_t di = ((size_t)bh * T + t) * N + lane;                 // key part + value part
+            dw = Din[di] + Din[(size_t)p.B * H * T * N + di];
+        }
+        const float e = ok ? __expf(z - zmax) : 0.f;
+        float se = e, sd = e * dw;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            se += __shfl_xor_sync(FULL, se, off);
+            sd += __shfl_xor_sync(FULL, sd, off);
+        }
+        const float sa = g * sd / se;
+        const float dz = ok ? (e / se) * (g * dw - sa) : 0.f;
+        if (lane == s_am[i]) dg[ix] = dw;
+        float f1 = -occ * dz, f2 = dz * s;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            f1 += __shfl_xor_sync(FULL, f1, off);
+            f2 += __shfl_xor_sync(FULL, f2, off);
+        }
+        if (lane == 0) {
+            if (p.fr_per_token) dfr[ix] = f1; else dfr_acc += f1;
+            dtemp_acc += f2 / temp;
+        }
+        __syncwarp();
+        s_S[warp][lane] = dz * temp * ki;                                      // C_n
+        __syncwarp();
+        // ---- dq: lane = 4 columns, rows in sequence ----
+        const int col = lane * 4;
+        const bool act = col < DK;
+        float4 acc = zero4;
+        for (int n = 0; n <= lim; n++) {
+            const float cn = s_S[warp][n];
+            const int vn = s_ver[i][n];
+            const float* row = (vn < 0) ? kfin + ((size_t)bh * N + n) * DK : kold + (((size_t)b * T + vn) * H + h) * DK;
+            const float4 K4 = act ? ld4(row + col) : zero4;
+            acc.x += cn * K4.x; acc.y += cn * K4.y; acc.z += cn * K4.z; acc.w += cn * K4.w;
+        }
+        const float4 qv = act ? ld4(q + ix * DK + col) : zero4;
+        const float4 qn = make_float4(qv.x * qinv, qv.y * qinv, qv.z * qinv, qv.w * qinv);
+        const float pr = warp_sum(dot4(acc, qn));
+        if (act) {
+            float4 out;
+            if (qinv >= 1e6f) out = make_float4(qinv * acc.x, qinv * acc.y, qinv * acc.z, qinv * acc.w);   // |q| under the clamp
+            else out = make_float4(qinv * (acc.x - qn.x * pr), qinv * (acc.y - qn.y * pr), qinv * (acc.z - qn.z * pr),
+                                   qinv * (acc.w - qn.w * pr));
+            st4(dq + ix * DK + col, out);
+        }
+        __syncwarp();
+    }
+    if (lane == 0) { s_red[0][warp] = dtemp_acc; s_red[1][warp] = dfr_acc; }
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.f, d = 0.f;
+        for (int w = 0; w < GA_WARPS; w++) { a += s_red[0][w]; d += s_red[1][w]; }
+        part[(size_t)bh * part_stride + c] = a;                                          // dtemp partial
+        part[((size_t)p.B * H + bh) * part_stride + c] = d;                              // scalar dfr partial
+    }
+}
+
+}  // namespace slotscan

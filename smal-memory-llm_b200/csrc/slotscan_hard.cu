@@ -21,11 +21,18 @@
 
 namespace slotscan {
 
-// fixed-order sum of the per-sequence partials -> dtemp, scalar dfr; with q == NULL also dk += dq
-__global__ void finish_scalars_kernel(const float* __restrict__ part, int BH, int fr_per_token, float* dtemp, float* dfr) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        float a = 0.f, c = 0.f;
-        for (int i = 0; i < BH; i++) { a += part[i]; c += part[BH + i]; }
+// fixed-order sum of the partial sums (per sequence and token chunk) -> dtemp, scalar dfr: each thread adds a strided
+// subset in index order, then the 256 subtotals are added in order, so the result is bitwise repeatable
+__global__ void __launch_bounds__(256) finish_scalars_kernel(const float* __restrict__ part, int n, int fr_per_token,
+                                                             float* dtemp, float* dfr) {
+    __shared__ float s_a[256], s_c[256];
+    float a = 0.f, c = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) { a += part[i]; c += part[n + i]; }
+    s_a[threadIdx.x] = a; s_c[threadIdx.x] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        a = 0.f; c = 0.f;
+        for (int i = 0; i < 256; i++) { a += s_a[i]; c += s_c[i]; }
         dtemp[0] = a;
         if (!fr_per_token) dfr[0] = c;
     }
@@ -83,9 +90,14 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
 
 static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
                            const float* fr, const float* temp, const slotscan_log& L, const void* dkbuf, const void* dvbuf,
-                           float* Dn, float* part, void* dk, void* dq, void* dv, float* dgate, float* dfr, float* dtemp,
-                           cudaStream_t st) {
+                           float* Dn, float* part, int* vend, void* dk, void* dq, void* dv, float* dgate, float* dfr,
+                           float* dtemp, cudaStream_t st) {
     cudaError_t e;
+    // partial sums of dtemp / scalar dfr: one slot per (sequence, 32-token chunk) + one per sequence; slots that no
+    // kernel fills must read as zero
+    const int part_stride = (p.T + GATHER_CHUNK - 1) / GATHER_CHUNK + 1;
+    const size_t part_n = (size_t)p.B * p.H * part_stride;
+    if ((e = cudaMemsetAsync(part, 0, 2 * part_n * sizeof(float), st)) != cudaSuccess) return e;
     // keys and values are independent given the log: one launch (blockIdx.z) when dk == dv, each into its own D table
     float* DnV = Dn + (size_t)p.B * p.H * p.T * p.N;
     const RowsBwdPtrs ak{k, L.kold, L.kfin, dkbuf, dk, Dn};
@@ -106,12 +118,12 @@ static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* 
     {
         ProfScope ps(K_ADDR_BWD, st);
         e = (p.in_dtype == SLOTSCAN_F32)
-                ? run_addr_bwd_f32(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st)
-                : run_addr_bwd_bf16(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, st);
+                ? run_addr_bwd_f32(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st)
+                : run_addr_bwd_bf16(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st);
     }
     if (e != cudaSuccess) return e;
     ProfScope ps(K_FINISH, st);
-    finish_scalars_kernel<<<1, 32, 0, st>>>(part, p.B * p.H, p.fr_per_token, dtemp, dfr);
+    finish_scalars_kernel<<<1, 256, 0, st>>>(part, (int)part_n, p.fr_per_token, dtemp, dfr);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (q == nullptr) {       // the search query is the stored key: both gradient paths land in dk
         const size_t n4 = (size_t)p.B * p.T * p.H * p.DK / 4;
@@ -161,12 +173,24 @@ extern "C" int slotscan_hard_fwd(const slotscan_params* p, const void* k, const 
     return (int)e;
 }
 
+// scratch layout: [D table keys | D table values] [partial sums 2 x B*H x (chunks + 1) f32] [next-write table B*H x chunks x 32 i32]
+static void bwd_scratch_layout(const slotscan_params* p, size_t* off_part, size_t* off_vend, size_t* total) {
+    const size_t BH = (size_t)p->B * p->H, nc = ((size_t)p->T + GATHER_CHUNK - 1) / GATHER_CHUNK;
+    size_t o = 2 * sizeof(float) * BH * p->T * p->N;       // one D table for the keys, one for the values
+    o = (o + 255) & ~(size_t)255;
+    *off_part = o;
+    o += sizeof(float) * 2 * BH * (nc + 1);
+    o = (o + 255) & ~(size_t)255;
+    *off_vend = o;
+    o += sizeof(int) * BH * nc * GATHER_ROWS_MAX;
+    *total = o;
+}
+
 extern "C" size_t slotscan_hard_bwd_scratch_bytes(const slotscan_params* p) {
     if (slotscan_check(p)) return 0;
-    const size_t BH = (size_t)p->B * p->H;
-    size_t dn = 2 * sizeof(float) * BH * p->T * p->N;      // one D table for the keys, one for the values
-    dn = (dn + 255) & ~(size_t)255;
-    return dn + sizeof(float) * 2 * BH;
+    size_t a, b, t;
+    bwd_scratch_layout(p, &a, &b, &t);
+    return t;
 }
 
 extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
@@ -185,13 +209,13 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
         misaligned(dq) || misaligned(dv) || misaligned(scratch) || misaligned(log->kold) || misaligned(log->vold) ||
         misaligned(log->kfin) || misaligned(log->vfin))
         return SLOTSCAN_E_ALIGN;
-    const size_t BH = (size_t)p->B * p->H;
-    size_t dn = 2 * sizeof(float) * BH * p->T * p->N;
-    dn = (dn + 255) & ~(size_t)255;
+    size_t off_part, off_vend, total;
+    bwd_scratch_layout(p, &off_part, &off_vend, &total);
     float* Dn = (float*)scratch;
-    float* part = (float*)((char*)scratch + dn);
+    float* part = (float*)((char*)scratch + off_part);
+    int* vend = (int*)((char*)scratch + off_vend);
     cudaStream_t st = (cudaStream_t)stream;
-    const cudaError_t e = bwd_run(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, dk, dq, dv, dgate, dfr, dtemp, st);
+    const cudaError_t e = bwd_run(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, vend, dk, dq, dv, dgate, dfr, dtemp, st);
     return (int)e;
 }
 
@@ -271,8 +295,9 @@ extern "C" int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k
         }
         scratch = g_fixed_scratch_addr[dev];
     }
-    // Nothing in the scratch has to start at zero: every D[t,n] and every partial sum that is read was written earlier
-    // in the same call (the key pass stores D, the value pass adds to it, the address pass reads it).
+    // The array keeps the previous call's contents.  Every D[t,n] and next-write entry that is read was written earlier
+    // in the same call; the partial-sum table, whose unused slots must read as zero, is cleared by the call itself
+    // (cudaMemsetAsync on the caller's stream, inside slotscan_hard_bwd).
     return slotscan_hard_bwd(p, k, q, v, gate, fr, temp, log, dkbuf, dvbuf, scratch, (size_t)SLOTSCAN_NOALLOC_SCRATCH_BYTES,
                              dk, dq, dv, dgate, dfr, dtemp, stream);
 }

@@ -23,10 +23,13 @@ cudaError_t run_addr_fwd_bf16(const slotscan_params& p, const void* q, const voi
                               const float* temp, const slotscan_log& L, cudaStream_t st);
 cudaError_t run_addr_bwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                              const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
-                             float* part, cudaStream_t st);
+                             float* part, int* vend, int part_stride, cudaStream_t st);
 cudaError_t run_addr_bwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                               const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
-                              float* part, cudaStream_t st);
+                              float* part, int* vend, int part_stride, cudaStream_t st);
+// tokens per CTA of the token-parallel address backward: the partial-sum table has one slot per such chunk (+ 1)
+constexpr int GATHER_CHUNK = 32;
+constexpr int GATHER_ROWS_MAX = 32;
 // one tensor (keys: D = DK, values: D = DV) through the forward row replay
 cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
                        void* xbuf, float* xold, float* xfin, cudaStream_t st);
