@@ -1,19 +1,22 @@
 // Forward address scan: which row does token t write?  [reference addr_fwd, slotkern_cuda.py:72-174]
 //
-// One CTA of 4 warps per (sequence, head), key rows resident in shared memory as f32 for the whole scan.
-// Work split per token: LANE = ROW (row n = lane + 32 s for slot s), WARP = COLUMN QUARTER.  Each lane reads its own
-// row slice (row stride DK + 4 floats: the 8 lanes of a quarter-warp fall into 8 different bank groups) against the
-// token's query and key slices (broadcast reads) and produces two partial dots, <K_n, q_t> and <K_n, k_t>.  After one
-// barrier warp 0 adds the four partials, forms  z_n = temp * qinv * kinv_n * <K_n, q_t> - fr * occ_n  over the
-// candidate rows and takes the argmax with two warp reductions (max of an order-preserving key, then min index).
-// The row norm is never reduced again: |K_a'|^2 = (1-g)^2 |K_a|^2 + 2 g (1-g) <K_a, k_t> + g^2 |k_t|^2, accumulated in
-// double.  After a second barrier every warp blends its column quarter of the chosen row.  Only rows up to the
-// highest row touched so far (+1) are visited: everything above is exactly zero.
+// One CTA of 5 warps per (sequence, head), key rows resident in shared memory as f32 for the whole scan.
+// Work split per token: LANE = ROW (row n = lane + 32 s for slot s); warps 1-4 each own a COLUMN QUARTER, warp 0
+// resolves.  A column warp's lane reads its own row slice (row stride DK + 4 floats: the 8 lanes of a quarter-warp
+// fall into 8 different bank groups) against the token's query and key slices (broadcast reads) and produces two
+// partial dots, <K_n, q_t> and <K_n, k_t>.  Warp 0 adds the four partials, forms
+// z_n = temp * qinv * kinv_n * <K_n, q_t> - fr * occ_n  over the candidate rows and takes the argmax with two warp
+// reductions (max of an order-preserving key, then min index).  The row norm is never reduced again:
+// |K_a'|^2 = (1-g)^2 |K_a|^2 + 2 g (1-g) <K_a, k_t> + g^2 |k_t|^2, accumulated in double.  The two halves run
+// CONCURRENTLY, one token apart (see the schedule comment in the kernel): one barrier per token.  Only rows up to
+// the highest row touched so far (+1) are visited: everything above is exactly zero.
 //
 // Against the reference this changes the order of operations (dot first, scale after; the reference normalises
 // first), which moves a score by float32 round-off only; addresses are checked against the float64 oracle with a
 // 1e-4 margin rule.
 #pragma once
+#include <type_traits>
+
 #include "slotscan_common.cuh"
 
 namespace slotscan {
@@ -22,13 +25,15 @@ namespace slotscan {
 static __device__ unsigned long long g_phase_cycles[16];
 #define STEP_T0() long long _st = clock64()
 #define STEP_MARK(I) do { long long _n = clock64(); _acc[I] += _n - _st; _st = _n; } while (0)
+#define SS_ULL(x) ((unsigned long long)(x))
 #else
 #define STEP_T0()
 #define STEP_MARK(I)
 #endif
 
 constexpr int CH = 8;                       // tokens staged per chunk
-constexpr int AF_THREADS = 128;
+constexpr int AF_CWARPS = 4;                // column warps: each owns a quarter of the key columns
+constexpr int AF_THREADS = 32 * (AF_CWARPS + 1);   // + warp 0, the resolver
 constexpr int AF_WARPS = AF_THREADS / 32;
 
 __device__ __forceinline__ unsigned ord_key(float f) {    // monotone float -> unsigned
@@ -63,24 +68,57 @@ template <> struct Pre8<__nv_bfloat16> {
     }
 };
 
+// tokens staged per chunk of the forward scan: the small variant has shared memory to spare for 16
+__host__ __device__ constexpr int af_ch(int RPL) { return RPL <= 2 ? 16 : 8; }
+
 struct AddrFwdSmem {       // offsets in floats into dynamic shared memory
-    int K, part, tok, tokd, log, cur, Qs, Ks, total;
-    int kstride;
+    int K, part, tok, tokd, cross, log, cur, Qs, Ks, total;
+    int kstride, stage;    // floats per key row; floats per staged chunk of one stream
 };
-// N here is the number of key rows held in shared memory (the kernel's `ncap`)
+// N here is the number of key rows held in shared memory (the kernel's `ncap`).  Everything per chunk exists twice:
+// the scan runs through chunk boundaries, one chunk is consumed while the next is staged.
 __host__ __device__ inline AddrFwdSmem addr_fwd_layout(int N, int DK, int RPL, int in_bytes) {
     AddrFwdSmem L;
+    const int C = af_ch(RPL);
+    if (RPL <= 2) in_bytes = 4;                   // the small variant stages the chunk as f32 (see Ts in the kernel)
     L.kstride = DK + 4;
+    L.stage = C * DK * in_bytes / 4;
     L.K = 0;
-    L.part = L.K + N * L.kstride;                 // [RPL][4 warps][32 lanes] float2 partial dots
-    L.tok = L.part + RPL * AF_WARPS * 32 * 2;     // [CH] float4: temp*qinv, fr, g, |k|^2
-    L.tokd = L.tok + 4 * CH;                      // [CH][4] double: (1-g)^2, 2 g (1-g), g^2 |k|^2, pad
-    L.log = L.tokd + 8 * CH;                      // am, oold, kiold [CH each]
-    L.cur = L.log + 3 * CH;                       // am, lim of the current token
-    L.Qs = L.cur + 4;                             // the chunk's queries and keys in their input dtype
-    L.Ks = L.Qs + CH * DK * in_bytes / 4;
-    L.total = L.Ks + CH * DK * in_bytes / 4;
+    L.part = L.K + N * L.kstride;                 // [2 buffers][RPL][4 column warps][32 lanes] float2 partial dots
+    L.tok = L.part + 2 * RPL * AF_CWARPS * 32 * 2;   // [2][C] float4: temp*qinv, fr, g, -
+    L.tokd = L.tok + 2 * 4 * C;                   // [2][C][4] double: (1-g)^2, 2 g (1-g), g^2 |k|^2, pad
+    L.cross = L.tokd + 2 * 8 * C;                 // [2][C][2]: <k_{t-1}, q_t>, <k_{t-1}, k_t>
+    L.log = L.cross + 2 * 2 * C;                  // [2][3][C]: am, oold, kiold
+    L.cur = L.log + 2 * 3 * C;                    // the next token's candidate limit, double-buffered by token parity
+    L.Qs = L.cur + 4;                             // [2] chunks of queries, then [2] chunks of keys, in_bytes per element
+    L.Ks = L.Qs + 2 * L.stage;
+    L.total = L.Ks + 2 * L.stage;
     return L;
+}
+
+// Per-token constants of the staged chunk, one token per half-warp: temp / max(|q|, 1e-6), the three coefficients of
+// the norm recurrence and the cross terms with the previous token's key (kprev).  All 32 lanes must call.
+template <int DK, typename Ts>
+__device__ __forceinline__ void af_token_consts(const Ts* __restrict__ qrow, const Ts* __restrict__ krow,
+                                                const Ts* __restrict__ kprev, int l16, float temp, float* tok4,
+                                                double* tokd4, float* cross2) {
+    float qq = 0.f, kk = 0.f, pq = 0.f, pk = 0.f;
+#pragma unroll
+    for (int cc = l16 * 4; cc < DK; cc += 64) {
+        const float4 q4 = ld4(qrow + cc), k4 = ld4(krow + cc), kp = ld4(kprev + cc);
+        qq += dot4(q4, q4); kk += dot4(k4, k4); pq += dot4(kp, q4); pk += dot4(kp, k4);
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) {
+        qq += __shfl_xor_sync(FULL, qq, off); kk += __shfl_xor_sync(FULL, kk, off);
+        pq += __shfl_xor_sync(FULL, pq, off); pk += __shfl_xor_sync(FULL, pk, off);
+    }
+    if (l16 == 0) {
+        tok4[0] = temp * fminf(rsqrtf(qq), 1e6f);                          // temp / max(|q|, 1e-6)
+        const double gd = (double)tok4[2], od = 1.0 - gd;   // |K'|^2 = od^2 |K|^2 + 2 gd od <K,k> + gd^2 |k|^2
+        tokd4[0] = od * od; tokd4[1] = 2.0 * gd * od; tokd4[2] = gd * gd * (double)kk;
+        cross2[0] = pq; cross2[1] = pk;
+    }
 }
 
 // RPL = row slots per lane (N <= 32 * RPL)
@@ -95,10 +133,17 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     // needs row ncap gives up, marks itself by tfirst[bh][0] = -1 and leaves.  Pass 2 (ncap = N, second_pass = 1)
     // redoes exactly the marked sequences from the start and returns at once for the others.
     extern __shared__ __align__(16) float smem[];
+    constexpr int C = af_ch(RPL);                         // tokens per staged chunk
+    constexpr int RING = 2 * C;                           // token t lives in slot t % RING of every per-token array
     constexpr int CW = (DK >= 16) ? DK / 4 : 4;           // columns per warp
     constexpr int NF = CW / 4;                            // float4 per lane and row slice
-    constexpr int IPS = CH * DK / 8;                      // 8-element items per stream and chunk
-    constexpr int NIT = (2 * IPS + AF_THREADS - 1) / AF_THREADS;
+    constexpr int LT = AF_THREADS - 32;                   // loader threads: warps 1..4
+    constexpr int IPS = C * DK / 8;                       // 8-element items per stream and chunk
+    constexpr int NIT = (2 * IPS + LT - 1) / LT;
+    // Staging type of the chunk's queries and keys.  Every lane of a column warp reads the warp's whole q and k slice
+    // per token, so unpacking bf16 there costs as many instructions as the dots themselves: the small variant converts
+    // once per chunk instead.  The full-size variant keeps the input dtype to save shared memory.
+    typedef typename std::conditional<(RPL <= 2), float, Tin>::type Ts;
     const int N = p.N, T = p.T, H = p.H;
     const AddrFwdSmem L = addr_fwd_layout(ncap, DK, RPL, (int)sizeof(Tin));
     const int KS = L.kstride;
@@ -106,111 +151,91 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     float2* part = reinterpret_cast<float2*>(smem + L.part);
     float* s_tok = smem + L.tok;
     double* s_tokd = reinterpret_cast<double*>(smem + L.tokd);
+    float* s_cross = smem + L.cross;
     int* s_am = reinterpret_cast<int*>(smem + L.log);
-    float* s_oold = smem + L.log + CH;
-    float* s_kiold = smem + L.log + 2 * CH;
+    float* s_oold = smem + L.log + RING;
+    float* s_kiold = smem + L.log + 2 * RING;
     int* s_cur = reinterpret_cast<int*>(smem + L.cur);
-    Tin* Qs = reinterpret_cast<Tin*>(smem + L.Qs);
-    Tin* Ks = reinterpret_cast<Tin*>(smem + L.Ks);
+    Ts* Qs = reinterpret_cast<Ts*>(smem + L.Qs);
+    Ts* Ks = reinterpret_cast<Ts*>(smem + L.Ks);
 
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int c0 = warp * CW;                             // first column of this warp
-    const bool wact = c0 < DK;
+    const int ltid = tid - 32;                            // loader thread index (warps 1..4)
+    const int cw = warp - 1;                              // column warp index (warp 0 is the resolver)
+    const int c0 = cw * CW;                               // first column of this warp
+    const bool wact = warp >= 1 && c0 < DK;
     const float temp = temp_p[0], eps = p.eps;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     if (second_pass && tfirst[(size_t)bh * N] != -1) return;          // finished in the first pass (uniform per CTA)
     __syncthreads();
     for (int i = tid; i < ncap * KS; i += AF_THREADS) K[i] = 0.f;
+    for (int i = tid; i < DK; i += AF_THREADS) Ks[(RING - 1) * DK + i] = (Ts)0.f;    // "the key before token 0"
     for (int i = tid; i < N; i += AF_THREADS) tfirst[(size_t)bh * N + i] = (i == 0) ? 0 : T;
 
-    // ---- chunk loader: 8-element items of q (first IPS) and k (next IPS), gate / fr on 16 threads ----
+    // ---- chunk loader (warps 1..4): 8-element items of q (first IPS) and k (next IPS); gate / fr on 2 C threads ----
     Pre8<Tin> pre[NIT];
     float pre_s = 0.f;
 #define AF_ISSUE_LOADS(T0)                                                                                 \
     {                                                                                                      \
         _Pragma("unroll") for (int r_ = 0; r_ < NIT; r_++) {                                               \
-            const int id_ = tid + r_ * AF_THREADS;                                                         \
+            const int id_ = ltid + r_ * LT;                                                                \
             if (id_ < 2 * IPS) {                                                                           \
                 const int s_ = id_ / IPS, rr_ = id_ % IPS, j_ = rr_ / (DK / 8), c_ = (rr_ % (DK / 8)) * 8; \
                 if ((T0) + j_ < T) pre[r_].load((s_ ? k : q) + (((size_t)b * T + (T0) + j_) * H + h) * DK + c_); \
                 else pre[r_].zero();                                                                       \
             }                                                                                              \
         }                                                                                                  \
-        if (tid < 2 * CH) {                                                                                \
-            const int tt_ = (T0) + (tid & (CH - 1));                                                       \
+        if (ltid < 2 * C) {                                                                                \
+            const int tt_ = (T0) + (ltid & (C - 1));                                                       \
             const size_t ix_ = ((size_t)b * T + tt_) * H + h;                                              \
-            if (tid < CH) pre_s = (tt_ < T) ? gate[ix_] : 0.f;   /* no arithmetic: the load stays in flight */ \
+            if (ltid < C) pre_s = (tt_ < T) ? gate[ix_] : 0.f;   /* no arithmetic: the load stays in flight */ \
             else pre_s = (tt_ < T) ? (p.fr_per_token ? fr[ix_] : fr[0]) : 0.f;                             \
         }                                                                                                  \
     }
-#define AF_COMMIT_LOADS()                                                                                  \
+    // S0 = first ring slot of the chunk (0 or C)
+#define AF_COMMIT_LOADS(S0)                                                                                \
     {                                                                                                      \
         _Pragma("unroll") for (int r_ = 0; r_ < NIT; r_++) {                                               \
-            const int id_ = tid + r_ * AF_THREADS;                                                         \
+            const int id_ = ltid + r_ * LT;                                                                \
             if (id_ < 2 * IPS) {                                                                           \
                 const int s_ = id_ / IPS, rr_ = id_ % IPS;                                                 \
-                pre[r_].store_raw((s_ ? Ks : Qs) + rr_ * 8);                                               \
+                Ts* d_ = (s_ ? Ks : Qs) + (S0) * DK + rr_ * 8;                                             \
+                if constexpr (std::is_same<Ts, Tin>::value) pre[r_].store_raw(d_);                         \
+                else pre[r_].store(d_);                                                                    \
             }                                                                                              \
         }                                                                                                  \
-        if (tid < CH) s_tok[4 * tid + 2] = gate_eff(pre_s, p.hard_gate);                                   \
-        else if (tid < 2 * CH) s_tok[4 * (tid - CH) + 1] = pre_s;                                          \
+        if (ltid < C) s_tok[4 * ((S0) + ltid) + 2] = gate_eff(pre_s, p.hard_gate);                         \
+        else if (ltid < 2 * C) s_tok[4 * ((S0) + ltid - C) + 1] = pre_s;                                   \
+    }
+    // per-token constants of 8 tokens of the chunk at ring slot S0: one token per half-warp of warps 1..4
+#define AF_TOKEN_CONSTS(S0, ROUND)                                                                         \
+    {                                                                                                      \
+        const int sl_ = (S0) + (ROUND) * 8 + cw * 2 + (lane >> 4), sp_ = (sl_ + RING - 1) & (RING - 1);    \
+        af_token_consts<DK, Ts>(Qs + sl_ * DK, Ks + sl_ * DK, Ks + sp_ * DK, lane & 15, temp, s_tok + 4 * sl_, \
+                                s_tokd + 4 * sl_, s_cross + 2 * sl_);                                      \
     }
 
-    // resolver state (warp 0), per owned row lane + 32 s: |K|^2 (double: the recurrence must not drift),
-    // 1 / max(|K|, 1e-6) and the occupancy
-    double nsq_r[RPL];
-    float kinv_r[RPL], o_r[RPL];
-#pragma unroll
-    for (int s = 0; s < RPL; s++) { nsq_r[s] = 0.0; kinv_r[s] = 1e6f; o_r[s] = 0.f; }
-    int hw = -1, fe = 0, lim = 0;                         // highest row touched; lowest free row (N if none)
-
-    AF_ISSUE_LOADS(0);
-    AF_COMMIT_LOADS();
-    __syncthreads();
-
-#ifdef SLOTSCAN_PHASE_TIMING
-    long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#endif
-    STEP_T0();
-    for (int t0 = 0; t0 < T; t0 += CH) {
-        const int cn = min(CH, T - t0);
-        if (t0 + CH < T) AF_ISSUE_LOADS(t0 + CH);         // next chunk's global loads fly through the whole chunk
-        // per-token constants: warp w handles tokens w and w + 4
-        for (int j = warp; j < CH; j += AF_WARPS) {
-            float qq = 0.f, kk = 0.f;
-            for (int cc = lane * 4; cc < DK; cc += 128) {
-                const float4 q4 = ld4(Qs + j * DK + cc), k4 = ld4(Ks + j * DK + cc);
-                qq += dot4(q4, q4); kk += dot4(k4, k4);
-            }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                qq += __shfl_xor_sync(FULL, qq, off);
-                kk += __shfl_xor_sync(FULL, kk, off);
-            }
-            if (lane == 0) {
-                s_tok[4 * j] = temp * fminf(rsqrtf(qq), 1e6f);                                        // 1 / max(|q|, 1e-6)
-                const double gd = (double)s_tok[4 * j + 2], od = 1.0 - gd;     // |K'|^2 = od^2 |K|^2 + 2 gd od <K,k> + gd^2 |k|^2
-                s_tokd[4 * j] = od * od; s_tokd[4 * j + 1] = 2.0 * gd * od; s_tokd[4 * j + 2] = gd * gd * (double)kk;
-            }
-        }
-        __syncthreads();
-        STEP_MARK(0);
-        for (int j = 0; j < cn; j++) {
-            const int t = t0 + j;
-            // The step is compiled once per number of live row slots (rows above the highest touched one are exactly
-            // zero and are not visited): the common case of few occupied rows runs a short instruction stream.
-#define AF_DOTS(NS)                                                                                            \
+    // Schedule.  The scan never stops at a chunk boundary and has ONE barrier per token.  In the phase of token t
+    //   warp 0        finishes the bookkeeping of token t-1 (norm, occupancy, free row: in the shadow of its loads),
+    //                 then resolves token t from the partial dots of buffer t & 1;
+    //   warps 1..4    apply the write of token t-1 to their column quarter of the rows, then compute the partial dots
+    //                 of token t+1 into buffer (t+1) & 1.  Those rows lack exactly one write, token t's, and warp 0
+    //                 repairs that one row when it reads the partials, by linearity:
+    //                     <K_a', q_{t+1}> = (1-g_t) <K_a, q_{t+1}> + g_t <k_t, q_{t+1}>      (same with k_{t+1})
+    //                 with the cross terms <k_t, q_{t+1}>, <k_t, k_{t+1}> computed once per chunk;
+    //                 in phases 1..3 of a chunk they also stage the next chunk (loaded one chunk earlier into
+    //                 registers), compute its per-token constants and write the previous chunk's log out.
+#define AF_DOTS(NS, SL, BUF)                                                                                   \
     {                                                                                                          \
-      if (wact) {                                                                                              \
         float4 q4[NF], k4[NF];                                                                                 \
         _Pragma("unroll") for (int i = 0; i < NF; i++) {                                                       \
-            q4[i] = ld4(Qs + j * DK + c0 + 4 * i);                                                             \
-            k4[i] = ld4(Ks + j * DK + c0 + 4 * i);                                                             \
+            q4[i] = ld4(Qs + (SL) * DK + c0 + 4 * i);                                                          \
+            k4[i] = ld4(Ks + (SL) * DK + c0 + 4 * i);                                                          \
         }                                                                                                      \
         _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
-            const int n = min(lane + 32 * s, N - 1);                                                           \
+            const int n = min(lane + 32 * s, ncap - 1);                                                        \
             const float* Kr = K + (size_t)n * KS + c0;                                                         \
             float4 aS = zero4, aR = zero4;      /* 8 independent FMA chains; summed once at the end */          \
             _Pragma("unroll") for (int i = 0; i < NF; i++) {                                                   \
@@ -220,136 +245,231 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
                 aR.x = fmaf(K4.x, k4[i].x, aR.x); aR.y = fmaf(K4.y, k4[i].y, aR.y);                            \
                 aR.z = fmaf(K4.z, k4[i].z, aR.z); aR.w = fmaf(K4.w, k4[i].w, aR.w);                            \
             }                                                                                                  \
-            const float a0 = aS.x + aS.y, a1 = aS.z + aS.w, r0 = aR.x + aR.y, r1 = aR.z + aR.w;                \
-            part[(s * AF_WARPS + warp) * 32 + lane] = make_float2(a0 + a1, r0 + r1);                           \
+            part[(((BUF) * RPL + s) * AF_CWARPS + cw) * 32 + lane] =                                           \
+                make_float2((aS.x + aS.y) + (aS.z + aS.w), (aR.x + aR.y) + (aR.z + aR.w));                     \
         }                                                                                                      \
-      }                                                                                                        \
     }
-            // lane = row, warp = column quarter
-            if (lim < 32) AF_DOTS(1)
-            else if (lim < 64) AF_DOTS(RPL < 2 ? RPL : 2)
-            else if (lim < 96) AF_DOTS(RPL < 3 ? RPL : 3)
-            else if (lim < 128) AF_DOTS(RPL < 4 ? RPL : 4)
-            else if (lim < 192) AF_DOTS(RPL < 6 ? RPL : 6)
-            else AF_DOTS(RPL)
-#undef AF_DOTS
-            STEP_MARK(1);
-            __syncthreads();
-            STEP_MARK(2);
-            // ---------------- resolve (warp 0) ----------------
-#define AF_RESOLVE(NS)                                                                                         \
+    // compiled once per number of live 32-row slots: rows above the candidate limit are exactly zero and not visited
+#define AF_DOTS_DISPATCH(LIMD, SL, BUF)                                  \
+    if ((LIMD) < 32) AF_DOTS(1, SL, BUF)                                 \
+    else if ((LIMD) < 64) AF_DOTS((RPL < 2 ? RPL : 2), SL, BUF)          \
+    else if ((LIMD) < 96) AF_DOTS((RPL < 3 ? RPL : 3), SL, BUF)          \
+    else if ((LIMD) < 128) AF_DOTS((RPL < 4 ? RPL : 4), SL, BUF)         \
+    else AF_DOTS(RPL, SL, BUF)
+#define AF_WRITE_ROW(SL)                                                                                       \
+    if (lane < NF) {                                                                                           \
+        const int a_ = s_am[SL];                                                                               \
+        const float g_ = s_tok[4 * (SL) + 2], omw_ = 1.f - g_;                                                 \
+        const float4 kt_ = ld4(Ks + (SL) * DK + c0 + 4 * lane);                                                \
+        float* Kr_ = K + (size_t)a_ * KS + c0 + 4 * lane;                                                      \
+        float4 Kn_ = ld4(Kr_);                                                                                 \
+        Kn_.x = blend(Kn_.x, kt_.x, g_, omw_); Kn_.y = blend(Kn_.y, kt_.y, g_, omw_);                          \
+        Kn_.z = blend(Kn_.z, kt_.z, g_, omw_); Kn_.w = blend(Kn_.w, kt_.w, g_, omw_);                          \
+        st4(Kr_, Kn_);                                                                                         \
+    }                                                                                                          \
+    __syncwarp();      /* a column warp only ever reads the columns it writes */
+    // warp 0: the bookkeeping of the token resolved in the previous phase (am_prev, its constants in pc, the owner
+    // lane's <K_am, k> in Rb_prev).  The owner lane is the one that holds row am_prev.
+#define AF_FINISH_PREV(NS)                                                                                     \
+    if (am_prev >= 0) {                                                                                        \
+        const bool owner_ = (am_prev & 31) == lane;                                                            \
+        const int ai_ = am_prev >> 5;                                                                          \
+        float o_new = 0.f;                                                                                     \
+        _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
+            if (owner_ && s == ai_) {                                                                          \
+                const double nn = fmax(fma(pc.d0, nsq_r[s], fma(pc.d1, (double)Rb_prev, pc.d2)), 0.0);         \
+                s_oold[pslot] = o_r[s]; s_kiold[pslot] = kinv_r[s];                                            \
+                nsq_r[s] = nn;                                                                                 \
+                kinv_r[s] = fminf(rsqrtf((float)nn), 1e6f);                                                    \
+                o_r[s] = __fmaf_rn(1.f - pc.g, o_r[s], pc.g);                                                  \
+                o_new = o_r[s];                                                                                \
+            }                                                                                                  \
+        }                                                                                                      \
+        o_new = __shfl_sync(FULL, o_new, am_prev & 31);                                                        \
+        if (am_prev == fe && o_new >= eps) {               /* the free row got taken: find the next one */     \
+            int m = BIGI;                                                                                      \
+            _Pragma("unroll") for (int s = RPL - 1; s >= 0; s--) {                                             \
+                const int n = lane + 32 * s;                                                                   \
+                if (n < N && o_r[s] < eps) m = n;                                                              \
+            }                                                                                                  \
+            m = (int)__reduce_min_sync(FULL, (unsigned)m);                                                     \
+            fe = (m == BIGI) ? N : m;                                                                          \
+        } else if (o_new < eps && am_prev < fe) {                                                              \
+            fe = am_prev;                                                                                      \
+        }                                                                                                      \
+    }
+#define AF_RESOLVE(NS, BUF)                                                                                    \
     {                                                                                                          \
-        float bz = -INFINITY, Rb = 0.f;                                                                        \
+        float2 pr[NS][AF_CWARPS];                                                                              \
+        _Pragma("unroll") for (int s = 0; s < (NS); s++)                                                       \
+            _Pragma("unroll") for (int w = 0; w < AF_CWARPS; w++)                                              \
+                if (w * CW < DK) pr[s][w] = part[(((BUF) * RPL + s) * AF_CWARPS + w) * 32 + lane];             \
+        AF_FINISH_PREV(NS)                                                                                     \
+        float bz = -INFINITY;                                                                                  \
         int bi = BIGI;                                                                                         \
+        Rb = 0.f;                                                                                              \
         _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
             const int n = lane + 32 * s;                                                                       \
             float S = 0.f, R = 0.f;                                                                            \
-            _Pragma("unroll") for (int w = 0; w < AF_WARPS; w++) {                                             \
-                if (w * CW < DK) { const float2 pr = part[(s * AF_WARPS + w) * 32 + lane]; S += pr.x; R += pr.y; } \
+            _Pragma("unroll") for (int w = 0; w < AF_CWARPS; w++)                                              \
+                if (w * CW < DK) { S += pr[s][w].x; R += pr[s][w].y; }                                         \
+            if (n == am_prev) {    /* the one row whose latest write the dots have not seen */                 \
+                S = blend(S, cc.x0, pc.g, 1.f - pc.g);                                                         \
+                R = blend(R, cc.x1, pc.g, 1.f - pc.g);                                                         \
             }                                                                                                  \
             const float oc = o_r[s];                                                                           \
-            const float sc = tq * (kinv_r[s] * S);                                                             \
-            const float z = (OCCB ? (sc - frv * (oc >= eps ? 1.f : 0.f)) : (sc - frv * oc)) + 0.f;             \
+            const float sc = cc.tq * (kinv_r[s] * S);                                                          \
+            const float z = (OCCB ? (sc - cc.frv * (oc >= eps ? 1.f : 0.f)) : (sc - cc.frv * oc)) + 0.f;       \
             if (n <= lim && (oc >= eps || n == fe) && z > bz) { bz = z; bi = n; Rb = R; }   /* ascending n */  \
         }                                                                                                      \
         const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);                                                  \
         const unsigned kmax = __reduce_max_sync(FULL, key);                                                    \
         am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));                \
-        /* the owner lane's best row IS am (it holds the maximum), so Rb is <K_am, k_t> there */               \
-        const bool owner = (am & 31) == lane;                                                                  \
-        const int ai = am >> 5;                                                                                \
-        _Pragma("unroll") for (int s = 0; s < (NS); s++) {                                                     \
-            if (owner && s == ai) {                                                                            \
-                const double nn = fmax(fma(s_tokd[4 * j], nsq_r[s], fma(s_tokd[4 * j + 1], (double)Rb, s_tokd[4 * j + 2])), 0.0); \
-                s_am[j] = am; s_oold[j] = o_r[s]; s_kiold[j] = kinv_r[s];                                      \
-                nsq_r[s] = nn;                                                                                 \
-                kinv_r[s] = fminf(rsqrtf((float)nn), 1e6f);                                                    \
-                o_r[s] = __fmaf_rn(omw, o_r[s], g);                                                            \
-                o_new = o_r[s];                                                                                \
-            }                                                                                                  \
-        }                                                                                                      \
+        /* the owner lane's best row IS am (it holds the maximum), so its Rb is <K_am, k_t> */                 \
     }
-            if (warp == 0) {
-                const float4 c4 = ld4(s_tok + 4 * j);
-                const float tq = c4.x, frv = c4.y, g = c4.z, omw = 1.f - g;
-                int am = 0;
-                float o_new = 0.f;
-                if (lim < 32) AF_RESOLVE(1)
-                else if (lim < 64) AF_RESOLVE(RPL < 2 ? RPL : 2)
-                else if (lim < 96) AF_RESOLVE(RPL < 3 ? RPL : 3)
-                else if (lim < 128) AF_RESOLVE(RPL < 4 ? RPL : 4)
-                else if (lim < 192) AF_RESOLVE(RPL < 6 ? RPL : 6)
-                else AF_RESOLVE(RPL)
-#undef AF_RESOLVE
-                o_new = __shfl_sync(FULL, o_new, am & 31);
-                if (am > hw) {
-                    hw = am;
-                    if (lane == 0 && am + 1 < N) tfirst[(size_t)bh * N + am + 1] = t + 1;
-                }
-                if (am == fe && o_new >= eps) {            // the free row got taken: find the next one
-                    int m = BIGI;
+    struct TokC { float tq, frv, g, x0, x1; double d0, d1, d2; };
+#define AF_LOAD_CONSTS(DST, SL)                                                                                \
+    {                                                                                                          \
+        const float4 c4_ = ld4(s_tok + 4 * (SL));                                                              \
+        const float2 x2_ = *reinterpret_cast<const float2*>(s_cross + 2 * (SL));                               \
+        const double2 d2_ = *reinterpret_cast<const double2*>(s_tokd + 4 * (SL));                              \
+        DST.tq = c4_.x; DST.frv = c4_.y; DST.g = c4_.z; DST.x0 = x2_.x; DST.x1 = x2_.y;                        \
+        DST.d0 = d2_.x; DST.d1 = d2_.y; DST.d2 = s_tokd[4 * (SL) + 2];                                         \
+    }
+
+    // resolver state (warp 0), per owned row lane + 32 s: |K|^2 (double: the recurrence must not drift),
+    // 1 / max(|K|, 1e-6) and the occupancy
+    double nsq_r[RPL];
+    float kinv_r[RPL], o_r[RPL];
 #pragma unroll
-                    for (int s = RPL - 1; s >= 0; s--) {
-                        const int n = lane + 32 * s;
-                        if (n < N && o_r[s] < eps) m = n;
-                    }
-                    m = (int)__reduce_min_sync(FULL, (unsigned)m);
-                    fe = (m == BIGI) ? N : m;
-                } else if (o_new < eps && am < fe) {
-                    fe = am;
-                }
-                if (lane == 0) { s_cur[0] = am; s_cur[1] = min(hw + 1, N - 1); }   // the next token's candidate limit
-            }
-            STEP_MARK(3);
-            __syncthreads();
-            STEP_MARK(4);
-            // ---------------- the write: every warp blends its column quarter of the chosen row ----------------
-            {
-                const int am = s_cur[0];
-                lim = s_cur[1];
-                if (lim >= ncap) {                         // the next token may address a row this CTA does not hold
-                    if (tid == 0) tfirst[(size_t)bh * N] = -1;
-                    return;                                // uniform: every thread reads the same s_cur
-                }
-                if (wact && lane < NF) {
-                    const float g = s_tok[4 * j + 2], omw = 1.f - g;
-                    float* Kr = K + (size_t)am * KS + c0 + 4 * lane;
-                    float4 Kn = ld4(Kr);
-                    const float4 kt = ld4(Ks + j * DK + c0 + 4 * lane);
-                    Kn.x = blend(Kn.x, kt.x, g, omw); Kn.y = blend(Kn.y, kt.y, g, omw);
-                    Kn.z = blend(Kn.z, kt.z, g, omw); Kn.w = blend(Kn.w, kt.w, g, omw);
-                    st4(Kr, Kn);
-                }
-                __syncwarp();                              // a warp only ever reads the columns it writes
-            }
-            STEP_MARK(5);
-        }
-        // ---------------- flush the chunk's log, land the next chunk ----------------
-        __syncthreads();
-        if (tid < cn) {
-            const size_t ix = ((size_t)b * T + t0 + tid) * H + h;
-            am_out[ix] = s_am[tid];
-            oold_out[ix] = s_oold[tid];
-            kiold_out[ix] = s_kiold[tid];
-        }
-        if (t0 + CH < T) AF_COMMIT_LOADS();
-        __syncthreads();
-        STEP_MARK(6);
-    }
+    for (int s = 0; s < RPL; s++) { nsq_r[s] = 0.0; kinv_r[s] = 1e6f; o_r[s] = 0.f; }
+    int hw = -1, fe = 0, lim = 0;                         // highest row touched; lowest free row (N if none)
+    int am_prev = -1, pslot = 0;                          // the token whose bookkeeping is still open
+    float Rb_prev = 0.f;
+    TokC cc = {}, pc = {}, nc = {};                       // constants of the current, previous and next token
+
 #ifdef SLOTSCAN_PHASE_TIMING
-    if (tid == 0)
-        for (int i = 0; i < 16; i++) atomicAdd(&g_phase_cycles[i], (unsigned long long)_acc[i]);
+    long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #endif
-#undef AF_ISSUE_LOADS
-#undef AF_COMMIT_LOADS
+    // ---- prologue: stage chunk 0, its constants, the plain dots of token 0 ----
+    if (warp >= 1) {
+        AF_ISSUE_LOADS(0);
+        AF_COMMIT_LOADS(0);
+    }
+    __syncthreads();
+    if (warp >= 1) {
+        if (C < T) AF_ISSUE_LOADS(C);
+#pragma unroll
+        for (int r = 0; r < C / 8; r++) AF_TOKEN_CONSTS(0, r);
+    }
+    __syncthreads();
+    if (wact) { AF_DOTS(1, 0, 0) }
+    if (warp == 0) AF_LOAD_CONSTS(cc, 0);
+    __syncthreads();
+    STEP_T0();
+
+    // The two roles run separate loops (their register states never mix) and meet at one named barrier per token.
+#define AF_PHASE_BARRIER() asm volatile("bar.sync 1, %0;" ::"n"(AF_THREADS) : "memory")
     if (warp == 0) {
+        for (int t = 0; t < T; t++) {
+            const int sl = t & (RING - 1);
+            if (t + 1 < T) AF_LOAD_CONSTS(nc, (t + 1) & (RING - 1));
+            int am = 0;
+            float Rb = 0.f;
+            if (lim < 32) AF_RESOLVE(1, t & 1)
+            else if (lim < 64) AF_RESOLVE((RPL < 2 ? RPL : 2), t & 1)
+            else if (lim < 96) AF_RESOLVE((RPL < 3 ? RPL : 3), t & 1)
+            else if (lim < 128) AF_RESOLVE((RPL < 4 ? RPL : 4), t & 1)
+            else AF_RESOLVE(RPL, t & 1)
+            if (am > hw) {
+                hw = am;
+                if (lane == 0 && am + 1 < N) tfirst[(size_t)bh * N + am + 1] = t + 1;
+            }
+            lim = min(hw + 1, N - 1);                      // the next token's candidate limit
+            if (lane == 0) {
+                s_am[sl] = am;
+                s_cur[t & 1] = lim;
+            }
+            am_prev = am; Rb_prev = Rb; pslot = sl;
+            pc = cc; cc = nc;
+            STEP_MARK(0);
+            AF_PHASE_BARRIER();
+            STEP_MARK(1);
+            if (lim >= ncap) {                             // the next token may address a row this CTA does not hold
+                if (lane == 0) tfirst[(size_t)bh * N] = -1;
+                return;                                    // the column warps read the same limit and leave too
+            }
+        }
+        AF_FINISH_PREV(RPL)
 #pragma unroll
         for (int s = 0; s < RPL; s++) {
             const int n = lane + 32 * s;
             if (n < N) ofin[(size_t)bh * N + n] = o_r[s];
         }
+    } else {
+        for (int t = 0; t < T; t++) {
+            const int jj = t & (C - 1);
+            if (wact) {
+                if (t >= 1) { AF_WRITE_ROW((t - 1) & (RING - 1)) }
+                STEP_MARK(2);
+                if (t + 1 < T) {
+                    const int limd = min(lim + 1, ncap - 1);      // token t can raise the candidate limit by one
+                    AF_DOTS_DISPATCH(limd, (t + 1) & (RING - 1), (t + 1) & 1)
+                }
+                STEP_MARK(3);
+            }
+            // chunk duties, spread over the phases 1.. of the chunk
+            const int tn = t - jj + C;                     // first token of the next chunk
+            if (jj == 1) {
+                if (t - jj >= C && ltid < C) {             // the previous chunk's log goes out
+                    const int tp = t - jj - C + ltid, sp = tp & (RING - 1);
+                    const size_t ix = ((size_t)b * T + tp) * H + h;
+                    am_out[ix] = s_am[sp];
+                    oold_out[ix] = s_oold[sp];
+                    kiold_out[ix] = s_kiold[sp];
+                }
+                if (tn < T) {
+                    AF_COMMIT_LOADS(tn & (RING - 1));
+                    if (tn + C < T) AF_ISSUE_LOADS(tn + C);
+                }
+            } else if (jj >= 2 && jj < 2 + C / 8 && tn < T) {
+                AF_TOKEN_CONSTS(tn & (RING - 1), jj - 2);
+            }
+            STEP_MARK(5);
+            AF_PHASE_BARRIER();
+            STEP_MARK(4);
+            lim = s_cur[t & 1];
+            if (lim >= ncap) return;
+        }
     }
+#undef AF_PHASE_BARRIER
     for (int n = 32 * RPL + tid; n < N; n += AF_THREADS) ofin[(size_t)bh * N + n] = 0.f;   // rows this pass never held
+    __syncthreads();
+    {   // the log entries not written out yet: the last chunk, and the one before it if the last stopped before phase 1
+        const int cl = (T - 1) / C;
+        const int f0 = (((T - 1) & (C - 1)) >= 1 ? cl : max(cl - 1, 0)) * C;
+        for (int tp = f0 + tid; tp < T; tp += AF_THREADS) {
+            const int sp = tp & (RING - 1);
+            const size_t ix = ((size_t)b * T + tp) * H + h;
+            am_out[ix] = s_am[sp];
+            oold_out[ix] = s_oold[sp];
+            kiold_out[ix] = s_kiold[sp];
+        }
+    }
+#ifdef SLOTSCAN_PHASE_TIMING
+    if (tid == 0) { atomicAdd(&g_phase_cycles[0], SS_ULL(_acc[0])); atomicAdd(&g_phase_cycles[1], SS_ULL(_acc[1])); }
+    if (tid == 32) { atomicAdd(&g_phase_cycles[2], SS_ULL(_acc[2])); atomicAdd(&g_phase_cycles[3], SS_ULL(_acc[3]));
+                     atomicAdd(&g_phase_cycles[4], SS_ULL(_acc[4])); atomicAdd(&g_phase_cycles[5], SS_ULL(_acc[5])); }
+#endif
+#undef AF_DOTS
+#undef AF_DOTS_DISPATCH
+#undef AF_WRITE_ROW
+#undef AF_FINISH_PREV
+#undef AF_RESOLVE
+#undef AF_LOAD_CONSTS
+#undef AF_TOKEN_CONSTS
+#undef AF_ISSUE_LOADS
+#undef AF_COMMIT_LOADS
 }
 
 }  // namespace slotscan
