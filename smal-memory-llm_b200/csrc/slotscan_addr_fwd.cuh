@@ -249,9 +249,39 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
                 make_float2((aS.x + aS.y) + (aS.z + aS.w), (aR.x + aR.y) + (aR.z + aR.w));                     \
         }                                                                                                      \
     }
-    // compiled once per number of live 32-row slots: rows above the candidate limit are exactly zero and not visited
+    // Few live rows (< 32 / F): a lane takes row lane % (32 / F) and the F-th part lane / (32 / F) of the warp's columns,
+    // and F lanes add up by shuffles.  What bounds this kernel is the shared-memory return path (every LDS.128 delivers
+    // 512 B to the warp, broadcast or not): F-fold fewer loads per token for the same rows.
+#define AF_DOTS_SPLIT(F, SL, BUF)                                                                              \
+    {                                                                                                          \
+        constexpr int FF = (NF >= (F)) ? (F) : 1, R_ = 32 / FF, NFS = NF / FF;                                 \
+        const int cb = c0 + (lane / R_) * (CW / FF);                                                           \
+        float4 q4[NFS], k4[NFS];                                                                               \
+        _Pragma("unroll") for (int i = 0; i < NFS; i++) {                                                      \
+            q4[i] = ld4(Qs + (SL) * DK + cb + 4 * i);                                                          \
+            k4[i] = ld4(Ks + (SL) * DK + cb + 4 * i);                                                          \
+        }                                                                                                      \
+        const float* Kr = K + (size_t)min(lane & (R_ - 1), ncap - 1) * KS + cb;                                \
+        float4 aS = zero4, aR = zero4;                                                                         \
+        _Pragma("unroll") for (int i = 0; i < NFS; i++) {                                                      \
+            const float4 K4 = ld4(Kr + 4 * i);                                                                 \
+            aS.x = fmaf(K4.x, q4[i].x, aS.x); aS.y = fmaf(K4.y, q4[i].y, aS.y);                                \
+            aS.z = fmaf(K4.z, q4[i].z, aS.z); aS.w = fmaf(K4.w, q4[i].w, aS.w);                                \
+            aR.x = fmaf(K4.x, k4[i].x, aR.x); aR.y = fmaf(K4.y, k4[i].y, aR.y);                                \
+            aR.z = fmaf(K4.z, k4[i].z, aR.z); aR.w = fmaf(K4.w, k4[i].w, aR.w);                                \
+        }                                                                                                      \
+        float sS = (aS.x + aS.y) + (aS.z + aS.w), sR = (aR.x + aR.y) + (aR.z + aR.w);                          \
+        _Pragma("unroll") for (int off = 16; off >= R_; off >>= 1) {                                           \
+            sS += __shfl_xor_sync(FULL, sS, off);                                                              \
+            sR += __shfl_xor_sync(FULL, sR, off);                                                              \
+        }                                                                                                      \
+        if (lane < R_) part[((BUF) * RPL * AF_CWARPS + cw) * 32 + lane] = make_float2(sS, sR);                 \
+    }
+    // compiled once per number of live rows: rows above the candidate limit are exactly zero and not visited
 #define AF_DOTS_DISPATCH(LIMD, SL, BUF)                                  \
-    if ((LIMD) < 32) AF_DOTS(1, SL, BUF)                                 \
+    if ((LIMD) < 8) AF_DOTS_SPLIT(4, SL, BUF)                            \
+    else if ((LIMD) < 16) AF_DOTS_SPLIT(2, SL, BUF)                      \
+    else if ((LIMD) < 32) AF_DOTS(1, SL, BUF)                            \
     else if ((LIMD) < 64) AF_DOTS((RPL < 2 ? RPL : 2), SL, BUF)          \
     else if ((LIMD) < 96) AF_DOTS((RPL < 3 ? RPL : 3), SL, BUF)          \
     else if ((LIMD) < 128) AF_DOTS((RPL < 4 ? RPL : 4), SL, BUF)         \
@@ -304,7 +334,9 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         _Pragma("unroll") for (int s = 0; s < (NS); s++)                                                       \
             _Pragma("unroll") for (int w = 0; w < AF_CWARPS; w++)                                              \
                 if (w * CW < DK) pr[s][w] = part[(((BUF) * RPL + s) * AF_CWARPS + w) * 32 + lane];             \
+        STEP_MARK(11);                                                                                         \
         AF_FINISH_PREV(NS)                                                                                     \
+        STEP_MARK(8);                                                                                          \
         float bz = -INFINITY;                                                                                  \
         int bi = BIGI;                                                                                         \
         Rb = 0.f;                                                                                              \
@@ -322,9 +354,11 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             const float z = (OCCB ? (sc - cc.frv * (oc >= eps ? 1.f : 0.f)) : (sc - cc.frv * oc)) + 0.f;       \
             if (n <= lim && (oc >= eps || n == fe) && z > bz) { bz = z; bi = n; Rb = R; }   /* ascending n */  \
         }                                                                                                      \
+        STEP_MARK(9);                                                                                          \
         const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);                                                  \
         const unsigned kmax = __reduce_max_sync(FULL, key);                                                    \
         am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));                \
+        STEP_MARK(10);                                                                                         \
         /* the owner lane's best row IS am (it holds the maximum), so its Rb is <K_am, k_t> */                 \
     }
     struct TokC { float tq, frv, g, x0, x1; double d0, d1, d2; };
@@ -363,7 +397,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         for (int r = 0; r < C / 8; r++) AF_TOKEN_CONSTS(0, r);
     }
     __syncthreads();
-    if (wact) { AF_DOTS(1, 0, 0) }
+    if (wact) { AF_DOTS_SPLIT(4, 0, 0) }
     if (warp == 0) AF_LOAD_CONSTS(cc, 0);
     __syncthreads();
     STEP_T0();
@@ -457,12 +491,15 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         }
     }
 #ifdef SLOTSCAN_PHASE_TIMING
+    if (tid == 0) { atomicAdd(&g_phase_cycles[8], SS_ULL(_acc[8])); atomicAdd(&g_phase_cycles[9], SS_ULL(_acc[9]));
+                    atomicAdd(&g_phase_cycles[10], SS_ULL(_acc[10])); atomicAdd(&g_phase_cycles[11], SS_ULL(_acc[11])); }
     if (tid == 0) { atomicAdd(&g_phase_cycles[0], SS_ULL(_acc[0])); atomicAdd(&g_phase_cycles[1], SS_ULL(_acc[1])); }
     if (tid == 32) { atomicAdd(&g_phase_cycles[2], SS_ULL(_acc[2])); atomicAdd(&g_phase_cycles[3], SS_ULL(_acc[3]));
                      atomicAdd(&g_phase_cycles[4], SS_ULL(_acc[4])); atomicAdd(&g_phase_cycles[5], SS_ULL(_acc[5])); }
 #endif
 #undef AF_DOTS
 #undef AF_DOTS_DISPATCH
+#undef AF_DOTS_SPLIT
 #undef AF_WRITE_ROW
 #undef AF_FINISH_PREV
 #undef AF_RESOLVE
