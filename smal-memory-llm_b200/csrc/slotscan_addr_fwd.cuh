@@ -358,6 +358,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);                                                  \
         const unsigned kmax = __reduce_max_sync(FULL, key);                                                    \
         am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));                \
+        am = min(am, lim);         /* no candidate compares greater (NaN scores): stay inside the rows */      \
         STEP_MARK(10);                                                                                         \
         /* the owner lane's best row IS am (it holds the maximum), so its Rb is <K_am, k_t> */                 \
     }
