@@ -117,6 +117,27 @@ int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k, const voi
                               const void* dvbuf, void* dk, void* dq, void* dv, float* dgate, float* dfr, float* dtemp,
                               void* stream);
 
+/* Writer epilogue and storage quantiser over emitted snapshot rows, one streaming pass.
+ * [replaces memlm_sh.py:464-475 (nsq = sum kbuf^2 in fp32, kinv = rsqrt(max(nsq, 1e-12)), valid = nsq > 1e-12, cast of
+ * the snapshots to the model dtype) and memlm_sh.py:221-234 (_fq, _quantize_mem).]
+ *   x      rows x D elements (in_dtype): kbuf or vbuf as the scan emitted them, any leading shape flattened
+ *   y      rows x D elements (out_dtype), or NULL when only kinv / valid are wanted
+ *   kinv   rows fp32 and valid rows bytes (0 / 1): both or neither (NULL, NULL for value rows)
+ *   bits   0: y = x.  2, 3, 4 or 8 (memlm_sh.py:81): y = _fq(x, bits, group), the midrise quantiser with one
+ *          absmax scale per `group` channels, evaluated in the reference's arithmetic including its straight-through
+ *          form x + (q - x); an all-zero group stays exactly zero.  group: a power of two, 4 <= group <= D.
+ *   kinv and valid are taken from the quantised row before the cast, as _quantize_mem does (:232-234).
+ * Forward values only (the reference's gradient is the identity through _fq). */
+typedef struct {
+    int64_t rows;
+    int32_t D;              /* 8, 16, 32, 64 or 128 */
+    int32_t in_dtype, out_dtype;
+    int32_t bits, group;
+} slotscan_epilogue_params;
+int slotscan_epilogue_check(const slotscan_epilogue_params* p);
+int slotscan_writer_epilogue(const slotscan_epilogue_params* p, const void* x, void* y, float* kinv, uint8_t* valid,
+                             void* stream);
+
 /* Registers / spilled bytes / static shared memory / max threads of each kernel, the analogue of kernel_attrs
  * (gqa25/slotkern_cuda.py:467-479).  Fills up to `cap` entries (HOST memory), returns how many kernels exist. */
 typedef struct {

@@ -1,0 +1,149 @@
+// Writer epilogue and storage quantiser: one streaming pass over the emitted snapshots.
+//   [reference memlm_sh.py:464-475 (nsq, kinv, valid, cast to the model dtype), :221-234 (_fq, _quantize_mem)]
+//
+// Per snapshot row of D elements:  y = fq(x) (midrise, per group of `group` channels) or y = x;  the stored copy is
+// cast to the output dtype;  for key rows  nsq = sum y^2 (fp32),  kinv = rsqrt(max(nsq, 1e-12)),  valid = nsq > 1e-12.
+// The reference does this in four eager passes over 2 x 4.8 GB; here each element is read once and written once.
+//
+// Layout: LPR = D / 8 lanes per row, 8 consecutive elements per lane (one 16-byte load for bf16, two for f32), so a
+// warp reads 32 / LPR whole rows back to back: fully coalesced.  A quantisation group of >= 8 channels spans
+// group / 8 neighbouring lanes (absmax by shuffles); groups of 4 are two per lane.  Grid: a multiple of the SM
+// count, grid-stride over rows.  HBM-bound: (e_in + e_out) * D bytes per row plus 5 bytes for kinv and valid.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "slotscan.h"
+#include "slotscan_common.cuh"
+#include "slotscan_launch.h"
+
+namespace slotscan {
+
+constexpr int EP_THREADS = 256;
+
+__device__ __forceinline__ float round_to(float v, float) { return v; }
+__device__ __forceinline__ float round_to(float v, __nv_bfloat16) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// fq of one group member, in the arithmetic of the reference: s = max(a / half, 1e-30),
+// q = (clamp(floor(x / s), -half, half - 1) + 0.5) * s, zero for an all-zero group, returned in the straight-through
+// form x + (q - x) evaluated in the input dtype (memlm_sh.py:229).
+template <typename Tin>
+__device__ __forceinline__ float fq_one(float x, float a, float half) {
+    const float s = fmaxf(__fdiv_rn(a, half), 1e-30f);
+    float f = floorf(__fdiv_rn(x, s));
+    f = fminf(fmaxf(f, -half), half - 1.f);
+    const float q = (a > 0.f) ? __fmul_rn(__fadd_rn(f, 0.5f), s) : 0.f;
+    const float qd = round_to(q, Tin());
+    const float diff = round_to(__fsub_rn(qd, x), Tin());
+    return round_to(__fadd_rn(x, diff), Tin());
+}
+
+template <int D, typename Tin, typename Tout>
+__global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
+                                                                     float* __restrict__ kinv,
+                                                                     uint8_t* __restrict__ valid, const long long rows,
+                                                                     const int bits, const int group) {
+    constexpr int LPR = D / 8, RPB = EP_THREADS / LPR;
+    const int r = threadIdx.x / LPR, c = threadIdx.x % LPR;
+    const float half = bits ? (float)(1 << (bits - 1)) : 0.f;
+    for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += (long long)gridDim.x * RPB) {
+        const long long row = row0 + r;
+        const bool live = row < rows;                    // dead lanes keep running the shuffles on zeros
+        float v[8];
+        if (live) ld8(v, x + row * D + c * 8);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = 0.f;
+        }
+        if (bits) {
+            if (group >= 8) {
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
+                for (int off = 1; off < group / 8; off <<= 1) a = fmaxf(a, __shfl_xor_sync(FULL, a, off));
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = fq_one<Tin>(v[j], a, half);
+            } else {                                     // group == 4: two groups inside the lane
+#pragma unroll
+                for (int g = 0; g < 2; g++) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) a = fmaxf(a, fabsf(v[4 * g + j]));
+#pragma unroll
+                    for (int j = 0; j < 4; j++) v[4 * g + j] = fq_one<Tin>(v[4 * g + j], a, half);
+                }
+            }
+        }
+        if (y != nullptr && live) st8(y + row * D + c * 8, v);
+        if (kinv != nullptr) {
+            float nsq = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) nsq = fmaf(v[j], v[j], nsq);
+            nsq = group_sum<LPR>(nsq);
+            if (live && c == 0) {
+                kinv[row] = rsqrtf(fmaxf(nsq, 1e-12f));
+                valid[row] = nsq > 1e-12f ? 1 : 0;
+            }
+        }
+    }
+}
+
+template <int D, typename Tin, typename Tout>
+static cudaError_t launch_ep(const void* x, void* y, float* kinv, uint8_t* valid, long long rows, int bits, int group,
+                             cudaStream_t st) {
+    constexpr int RPB = EP_THREADS / (D / 8);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long long want = (rows + RPB - 1) / RPB;
+    const long long cap = (long long)sms * 8;           // 8 resident CTAs of 256 threads per SM
+    const int grid = (int)(want < cap ? (want > 0 ? want : 1) : cap);
+    writer_epilogue_kernel<D, Tin, Tout><<<grid, EP_THREADS, 0, st>>>((const Tin*)x, (Tout*)y, kinv, valid, rows, bits, group);
+    return cudaGetLastError();
+}
+
+template <typename Tin, typename Tout>
+static cudaError_t launch_ep_d(int D, const void* x, void* y, float* kinv, uint8_t* valid, long long rows, int bits,
+                               int group, cudaStream_t st) {
+    cudaError_t e = cudaErrorInvalidValue;
+    SLOTSCAN_DISPATCH_D(D, e = (launch_ep<DD, Tin, Tout>(x, y, kinv, valid, rows, bits, group, st)));
+    return e;
+}
+
+}  // namespace slotscan
+
+using namespace slotscan;
+
+extern "C" int slotscan_epilogue_check(const slotscan_epilogue_params* p) {
+    if (p == nullptr) return SLOTSCAN_E_NULL;
+    if (p->rows < 0) return SLOTSCAN_E_SHAPE;
+    const int D = p->D;
+    if (!(D == 8 || D == 16 || D == 32 || D == 64 || D == 128)) return SLOTSCAN_E_SHAPE;
+    if ((p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) ||
+        (p->out_dtype != SLOTSCAN_F32 && p->out_dtype != SLOTSCAN_BF16))
+        return SLOTSCAN_E_DTYPE;
+    if (p->bits != 0) {
+        if (!(p->bits == 2 || p->bits == 3 || p->bits == 4 || p->bits == 8)) return SLOTSCAN_E_MODE;   /* memlm_sh.py:81 */
+        const int g = p->group;
+        if (g < 4 || g > D || (g & (g - 1)) != 0) return SLOTSCAN_E_MODE;   /* power of two that divides D (:82-83) */
+    }
+    return SLOTSCAN_OK;
+}
+
+extern "C" int slotscan_writer_epilogue(const slotscan_epilogue_params* p, const void* x, void* y, float* kinv,
+                                        uint8_t* valid, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int rc = slotscan_epilogue_check(p);
+    if (rc != SLOTSCAN_OK) return rc;
+    if (x == nullptr || (kinv == nullptr) != (valid == nullptr) || (y == nullptr && kinv == nullptr)) return SLOTSCAN_E_NULL;
+    if (((uintptr_t)x | (uintptr_t)y) & 15) return SLOTSCAN_E_ALIGN;
+    if (p->rows == 0) return SLOTSCAN_OK;
+    cudaError_t e;
+    const bool ib = p->in_dtype == SLOTSCAN_BF16, ob = p->out_dtype == SLOTSCAN_BF16;
+    if (ib && ob) e = launch_ep_d<__nv_bfloat16, __nv_bfloat16>(p->D, x, y, kinv, valid, p->rows, p->bits, p->group, stream);
+    else if (ib) e = launch_ep_d<__nv_bfloat16, float>(p->D, x, y, kinv, valid, p->rows, p->bits, p->group, stream);
+    else if (ob) e = launch_ep_d<float, __nv_bfloat16>(p->D, x, y, kinv, valid, p->rows, p->bits, p->group, stream);
+    else e = launch_ep_d<float, float>(p->D, x, y, kinv, valid, p->rows, p->bits, p->group, stream);
+    return (int)e;             /* 0, or the positive CUDA error code like the scan entry points */
+}

@@ -25,6 +25,12 @@ class Log(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")]
 
 
+class EpilogueParams(ctypes.Structure):
+    """slotscan_epilogue_params of include/slotscan.h."""
+    _fields_ = [("rows", ctypes.c_int64), ("D", ctypes.c_int32), ("in_dtype", ctypes.c_int32),
+                ("out_dtype", ctypes.c_int32), ("bits", ctypes.c_int32), ("group", ctypes.c_int32)]
+
+
 class KernelAttr(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char * 48), ("regs", ctypes.c_int32), ("local_bytes", ctypes.c_int32),
                 ("static_smem", ctypes.c_int32), ("max_threads", ctypes.c_int32)]
@@ -57,6 +63,10 @@ def lib():
         L.slotscan_hard_bwd_noalloc.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.slotscan_hard_bwd_noalloc.restype = ci
         L.slotscan_hard_bwd_noalloc_capacity.restype = sz
+        L.slotscan_epilogue_check.argtypes = [ctypes.POINTER(EpilogueParams)]
+        L.slotscan_epilogue_check.restype = ci
+        L.slotscan_writer_epilogue.argtypes = [ctypes.POINTER(EpilogueParams), vp, vp, vp, vp, vp]
+        L.slotscan_writer_epilogue.restype = ci
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
         L.slotscan_profile_enable.argtypes = [ci]
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]

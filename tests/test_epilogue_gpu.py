@@ -1,0 +1,163 @@
+"""Writer epilogue + storage quantiser (CUDA, through the C ABI) against the reference's golden vectors, the CPU
+oracle and, for bfloat16 inputs, a torch restatement of the reference formula (memlm_sh.py:221-234, 464-475)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _S():
+    import slotscan_b200 as S
+    return S
+
+
+def _fq_torch(x, bits, group):
+    """memlm_sh.py:221-229 restated (forward value), any float dtype, on the tensor's device."""
+    sh = x.shape
+    xg = x.float().reshape(*sh[:-1], sh[-1] // group, group)
+    a = xg.abs().amax(-1, keepdim=True)
+    half = 2 ** (bits - 1)
+    s = (a / half).clamp_min(1e-30)
+    q = (torch.floor(xg / s).clamp(-half, half - 1) + 0.5) * s
+    q = torch.where(a > 0, q, torch.zeros_like(q)).reshape(sh)
+    return x + (q.to(x.dtype) - x)
+
+
+def test_fq_golden_bit_exact():
+    S = _S()
+    z = np.load(os.path.join(GOLDEN, "quant_fq.npz"))
+    x = torch.from_numpy(z["x"]).cuda()
+    for bits in (2, 3, 4, 8):
+        for group in (16, 64):
+            y = S.fq(x, bits, group).cpu().numpy()
+            assert np.array_equal(y, z["fq_b%d_g%d" % (bits, group)]), (bits, group)
+
+
+def test_quantize_mem_golden():
+    S = _S()
+    z = np.load(os.path.join(GOLDEN, "quant_fq.npz"))
+    x = torch.from_numpy(z["x"]).cuda()
+    # the fixture was made with _quantize_mem(x, 0.5 * x, 3, 16) (tests/golden/make_golden.py)
+    kq, vq, kinv, valid = S.quantize_mem(x, x * 0.5, 3, 16)
+    assert np.array_equal(kq.cpu().numpy(), z["qm_k"]) and np.array_equal(vq.cpu().numpy(), z["qm_v"])
+    assert np.array_equal(valid.cpu().numpy(), z["qm_valid"])
+    v = z["qm_valid"]
+    assert np.abs(kinv.cpu().numpy()[v] / z["qm_kinv"][v] - 1).max() < 1e-6
+    assert np.abs(kinv.cpu().numpy()[~v] / 1e6 - 1).max() < 1e-6        # rsqrt(1e-12) for the never-written rows
+
+
+@pytest.mark.parametrize("D", [8, 16, 32, 64, 128])
+def test_fq_matches_oracle_all_widths(D):
+    S = _S()
+    g = torch.Generator().manual_seed(D)
+    x = torch.randn(3, 7, 5, 11, D, generator=g) * torch.rand(3, 7, 5, 11, 1, generator=g)
+    x[0, 0] = 0                                                          # never-written rows
+    x[1, 1, 1, :, : D // 2] = 0                                          # a zero group beside a live one
+    for bits in (2, 3, 4, 8):
+        group = 4
+        while group <= D:
+            want = O.fq(x.numpy(), bits, group, dtype=np.float32)
+            got = S.fq(x.cuda(), bits, group).cpu().numpy()
+            assert np.array_equal(got, want), (D, bits, group)
+            group *= 2
+
+
+def test_epilogue_unquantised_matches_oracle():
+    S = _S()
+    g = torch.Generator().manual_seed(1)
+    kbuf = torch.randn(2, 9, 6, 50, 128, generator=g)
+    kbuf[:, 0] = 0                                                       # snapshot 0 is the all-zero state
+    kbuf[1, 3, 2, 7] = 1e-8                                              # below the validity threshold: nsq = 1.28e-14
+    vbuf = torch.randn(2, 9, 6, 50, 64, generator=g)
+    kinv_w, valid_w = O.epilogue(kbuf.numpy(), dtype=np.float32)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        kq, vq, kinv, valid = S.writer_epilogue(kbuf.cuda(), vbuf.cuda(), out_dtype)
+        assert kq.dtype == out_dtype and vq.dtype == out_dtype and valid.dtype == torch.bool
+        assert torch.equal(kq.cpu(), kbuf.to(out_dtype)) and torch.equal(vq.cpu(), vbuf.to(out_dtype))
+        assert np.array_equal(valid.cpu().numpy(), valid_w)
+        assert np.abs(kinv.cpu().numpy() / kinv_w - 1).max() < 1e-6
+    assert not valid[:, 0].any() and not valid[1, 3, 2, 7]
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+def test_epilogue_quantised_storage_modes(in_dtype):
+    """Quantise in the scan's dtype, store in the model dtype, kinv / valid from the quantised keys before the cast."""
+    S = _S()
+    g = torch.Generator().manual_seed(2)
+    kbuf = (torch.randn(2, 5, 6, 33, 128, generator=g)).to(in_dtype).cuda()
+    vbuf = (0.5 * torch.randn(2, 5, 6, 33, 128, generator=g)).to(in_dtype).cuda()
+    kbuf[:, 0] = 0
+    for bits, group in ((3, 16), (8, 128), (4, 32), (2, 8)):
+        kq_w = _fq_torch(kbuf, bits, group)
+        vq_w = _fq_torch(vbuf, bits, group)
+        nsq = kq_w.float().pow(2).sum(-1)
+        kq, vq, kinv, valid = S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=group)
+        assert torch.equal(kq, kq_w.to(torch.bfloat16)) and torch.equal(vq, vq_w.to(torch.bfloat16)), (bits, group)
+        assert torch.equal(valid, nsq > 1e-12)
+        want = torch.rsqrt(nsq.clamp_min(1e-12))
+        assert ((kinv / want - 1).abs().max() < 1e-6)
+        # every element lands within one step of the midrise grid; all-zero rows stay exactly zero
+        a = kbuf.float().reshape(-1, group).abs().amax(-1, keepdim=True)
+        err = (kq.float().reshape(-1, group) - kbuf.float().reshape(-1, group)).abs()
+        assert (err <= a / 2 ** (bits - 1) * 1.02 + 1e-30).all()
+        assert (kq[:, 0] == 0).all()
+
+
+def test_gradients():
+    S = _S()
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 3, 4, 5, 32, generator=g).cuda().requires_grad_()
+    w = torch.randn(2, 3, 4, 5, 32, generator=g).cuda()
+    (S.fq(x, 3, 16) * w).sum().backward()
+    assert torch.equal(x.grad, w)                                        # straight through (memlm_sh.py:229)
+    # kinv carries gradient into the keys (memlm_sh.py:474-475); float64 autograd of the same formula is the check
+    kb = torch.randn(2, 3, 4, 5, 32, generator=g)
+    kb[0, 0] = 0
+    wk, wi = torch.randn(2, 3, 4, 5, 32, generator=g), torch.randn(2, 3, 4, 5, generator=g)
+    k1 = kb.cuda().requires_grad_()
+    kq, vq, kinv, valid = S.writer_epilogue(k1, k1.detach(), torch.float32)
+    ((kq * wk.cuda()).sum() + (kinv * wi.cuda()).sum()).backward()
+    k2 = kb.double().requires_grad_()
+    nsq = k2.pow(2).sum(-1)
+    ((k2 * wk.double()).sum() + (torch.rsqrt(nsq.clamp_min(1e-12)) * wi.double()).sum()).backward()
+    assert (k1.grad.cpu().double() - k2.grad).abs().max() < 1e-5 * k2.grad.abs().max()
+
+
+def test_contract():
+    S = _S()
+    x = torch.randn(4, 48)
+    with pytest.raises(RuntimeError):
+        S.fq(x, 3, 16)                                                   # CPU tensor: no CPU implementation
+    with pytest.raises(ValueError):
+        S.fq(x.cuda(), 3, 16)                                            # D = 48 is not a supported width
+    with pytest.raises(ValueError):
+        S.fq(torch.randn(4, 64).cuda(), 5, 16)                           # bits outside {2, 3, 4, 8}
+    with pytest.raises(ValueError):
+        S.fq(torch.randn(4, 64).cuda(), 3, 24)                           # group does not divide the channels
+    y = S.fq(torch.zeros(0, 64).cuda(), 3, 16)                           # empty input
+    assert y.shape == (0, 64)
+
+
+def test_full_size_snapshot_properties():
+    """Config-1 snapshot tensor (B 64 x NB 128 x H 6 x N 192 rows of 128 bf16 = 2.4 GB): rows that were never written
+    stay exactly zero and invalid, every element moves by less than one quantisation step, and a strided sample of rows
+    agrees with the torch restatement bit for bit."""
+    S = _S()
+    B, NB, H, N, D = 64, 128, 6, 192, 128
+    g = torch.Generator(device="cuda").manual_seed(4)
+    kbuf = torch.randn(B, NB, H, N, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    kbuf[:, :, :, 12:] = 0                                               # the benchmark's scans touch ~12 rows
+    kq, kinv, valid = torch.ops.slotscan.epilogue(kbuf, True, 3, 16)
+    assert not valid[:, :, :, 12:].any() and valid[:, :, :, :12].all()
+    assert (kq[:, :, :, 12:] == 0).all()
+    sample = kbuf[::7, ::5, :, :12]
+    assert torch.equal(kq[::7, ::5, :, :12], _fq_torch(sample, 3, 16))
+    a = sample.float().reshape(-1, 16).abs().amax(-1, keepdim=True)
+    err = (kq[::7, ::5, :, :12].float().reshape(-1, 16) - sample.float().reshape(-1, 16)).abs()
+    assert (err <= a / 4 * 1.01).all()                                   # one step of the 3-bit midrise grid
