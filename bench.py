@@ -311,6 +311,48 @@ def run_gpu(args, rank, local_rank, world):
 TRAFFIC = {"replay_rows_k": 8 * (13.03e6 + 274.17e6), "replay_rows_v": 8 * (13.03e6 + 274.17e6), "addr_fwd": 8 * 25.6e6}
 
 
+def run_epilogue(args, local_rank):
+    """Secondary line (`--workload epilogue`): the writer epilogue + 3-bit storage quantiser over the snapshots of the
+    config-1 scan (keys with kinv / valid, then values), bf16 in, bf16 out.  One GPU; HBM-bound streaming."""
+    import torch
+    import slotscan_b200 as S
+    torch.cuda.set_device(local_rank)
+    B, T, H, N, D, G = (args.B or SHAPE["B"]), (args.T or SHAPE["T"]), SHAPE["H"], SHAPE["N"], SHAPE["DK"], SHAPE["G"]
+    NB = (T + G - 1) // G
+    g = torch.Generator(device="cuda").manual_seed(0)
+    kbuf = torch.randn(B, NB, H, N, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    vbuf = torch.randn(B, NB, H, N, D, generator=g, device="cuda", dtype=torch.bfloat16)
+    rows = kbuf.numel() // D
+    out = {}
+    with ClockSampler(local_rank) as clk:
+        for bits in (0, 3):
+            for _ in range(max(args.warmup, 3)):
+                S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
+            b.record()
+            torch.cuda.synchronize()
+            out[bits] = a.elapsed_time(b) / args.steps
+    peak, which = hbm_peak()
+    # bits 0: keys are read, written and normed by the kernel; the values' cast bf16 -> bf16 is the identity (no pass)
+    alg0 = rows * (2 * D * 2 + 5)
+    alg3 = 2 * rows * 2 * D * 2 + rows * 5
+    line = {"metric": "writer epilogue GB/s (config-1 snapshots, bf16)", "value": alg3 / out[3] / 1e6, "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out[3],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16 storage",
+            "data": "synthetic", "gpu_launches": 2 * args.steps,
+            "config": {"workload": "writer epilogue + _fq(3 bits, group 16) over (%d,%d,%d,%d,%d) keys and values"
+                                   % (B, NB, H, N, D), "l2": "inputs (2 x %.1f GB) larger than L2" % (rows * D * 2 / 1e9)},
+            "roofline": {"bound": "hbm", "achieved": alg3 / out[3] / 1e6, "peak": peak, "unit": "GB/s",
+                         "frac": alg3 / out[3] / 1e6 / peak, "traffic": None, "peak_source": which},
+            "unquantised": {"ms_per_step": out[0], "achieved": alg0 / out[0] / 1e6, "frac": alg0 / out[0] / 1e6 / peak},
+            "clocks": clk.summary()}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -321,6 +363,8 @@ def main():
     ap.add_argument("--T", type=int, default=0, help="tokens per sequence (default 1024)")
     ap.add_argument("--dist", default="bench", help="input distribution: bench (the benchmark's) | fill (every slot used) | clustered")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--workload", default="scan", choices=["scan", "epilogue"],
+                    help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass (1 GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -328,6 +372,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload == "epilogue":
+        if rank == 0:
+            run_epilogue(args, local_rank)
     else:
         run_gpu(args, rank, local_rank, world)
 

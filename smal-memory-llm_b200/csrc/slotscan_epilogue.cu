@@ -28,12 +28,28 @@ __device__ __forceinline__ float round_to(float v, __nv_bfloat16) { return __bfl
 // fq of one group member, in the arithmetic of the reference: s = max(a / half, 1e-30),
 // q = (clamp(floor(x / s), -half, half - 1) + 0.5) * s, zero for an all-zero group, returned in the straight-through
 // form x + (q - x) evaluated in the input dtype (memlm_sh.py:229).
+// The IEEE division x / s is what costs: it is replaced by x * (1 / s) wherever that provably has the same floor (the
+// product is off by a few ulp of a quotient that is at most 128 in size, so any result further than 1e-3 from an
+// integer floors alike), by the known answer for the group's own extreme (x = +-a gives exactly +-half), and kept for
+// the rare rest.  s, 1 / s are per group.
+struct FqScale { float a, half, s, rs; bool plain; };
+__device__ __forceinline__ FqScale fq_scale(float a, float half) {
+    FqScale g;
+    g.a = a; g.half = half;
+    g.s = fmaxf(__fdiv_rn(a, half), 1e-30f);
+    g.rs = __frcp_rn(g.s);
+    g.plain = a > 1e-20f;                    // s = a / half exactly: not clamped, not denormal
+    return g;
+}
 template <typename Tin>
-__device__ __forceinline__ float fq_one(float x, float a, float half) {
-    const float s = fmaxf(__fdiv_rn(a, half), 1e-30f);
-    float f = floorf(__fdiv_rn(x, s));
-    f = fminf(fmaxf(f, -half), half - 1.f);
-    const float q = (a > 0.f) ? __fmul_rn(__fadd_rn(f, 0.5f), s) : 0.f;
+__device__ __forceinline__ float fq_one(float x, const FqScale& g) {
+    float f;
+    const float qt = x * g.rs, fl = floorf(qt), fr = qt - fl;
+    if (g.plain && fabsf(x) == g.a) f = x > 0.f ? g.half : -g.half;
+    else if (g.plain && fr > 1e-3f && fr < 0.999f) f = fl;
+    else f = floorf(__fdiv_rn(x, g.s));
+    f = fminf(fmaxf(f, -g.half), g.half - 1.f);
+    const float q = (g.a > 0.f) ? __fmul_rn(__fadd_rn(f, 0.5f), g.s) : 0.f;
     const float qd = round_to(q, Tin());
     const float diff = round_to(__fsub_rn(qd, x), Tin());
     return round_to(__fadd_rn(x, diff), Tin());
@@ -62,16 +78,18 @@ __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* 
 #pragma unroll
                 for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
                 for (int off = 1; off < group / 8; off <<= 1) a = fmaxf(a, __shfl_xor_sync(FULL, a, off));
+                const FqScale gs = fq_scale(a, half);
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = fq_one<Tin>(v[j], a, half);
+                for (int j = 0; j < 8; j++) v[j] = fq_one<Tin>(v[j], gs);
             } else {                                     // group == 4: two groups inside the lane
 #pragma unroll
                 for (int g = 0; g < 2; g++) {
                     float a = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; j++) a = fmaxf(a, fabsf(v[4 * g + j]));
+                    const FqScale gs = fq_scale(a, half);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) v[4 * g + j] = fq_one<Tin>(v[4 * g + j], a, half);
+                    for (int j = 0; j < 4; j++) v[4 * g + j] = fq_one<Tin>(v[4 * g + j], gs);
                 }
             }
         }

@@ -86,3 +86,27 @@ def test_custom_op_has_fake_kernel_for_compiled_callers():
     assert out[0].shape == (2, 2, 3, 24, 32) and out[0].dtype == torch.bfloat16 and out[2].dtype == torch.int32
     gr = torch.ops.slotscan.hard_bwd(k, k, k, g, g, t1, *out[2:], out[0], out[1], 24, 8, False, 1e-4, True, True)
     assert gr[0].shape == k.shape and gr[5].shape == (1,)
+
+
+def test_epilogue_validation_and_host_names():
+    """Writer epilogue / quantiser boundary: argument checks need no GPU; the host functions carry the reference's
+    argument order (gqa25/memlm_sh.py:221, :231) and trace on meta tensors."""
+    import slotscan_b200 as S
+    from slotscan_b200 import _lib
+    L = _lib.lib()
+    ok = _lib.EpilogueParams(100, 128, 1, 1, 3, 16)
+    assert L.slotscan_epilogue_check(ctypes.byref(ok)) == 0
+    for field, val in (("D", 48), ("rows", -1), ("in_dtype", 5), ("bits", 5), ("group", 24), ("group", 2), ("group", 256)):
+        p = _lib.EpilogueParams(100, 128, 1, 1, 3, 16)
+        setattr(p, field, val)
+        assert L.slotscan_epilogue_check(ctypes.byref(p)) < 0, field
+    assert L.slotscan_epilogue_check(None) == -1
+    assert L.slotscan_writer_epilogue(ctypes.byref(ok), None, None, None, None, None) == -1
+    assert list(inspect.signature(S.fq).parameters) == ["x", "bits", "group"]
+    assert list(inspect.signature(S.quantize_mem).parameters) == ["kbuf", "buf", "bits", "group"]
+    with pytest.raises(RuntimeError, match="CUDA"):
+        S.fq(torch.randn(4, 64), 3, 16)
+    x = torch.empty(2, 5, 3, 7, 64, device="meta")
+    assert torch.ops.slotscan.fq(x, 3, 16).shape == x.shape
+    kq, kinv, valid = torch.ops.slotscan.epilogue(x, True, 3, 16)
+    assert kq.dtype == torch.bfloat16 and kinv.shape == (2, 5, 3, 7) and valid.dtype == torch.uint8
