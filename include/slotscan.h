@@ -138,6 +138,23 @@ int slotscan_epilogue_check(const slotscan_epilogue_params* p);
 int slotscan_writer_epilogue(const slotscan_epilogue_params* p, const void* x, void* y, float* kinv, uint8_t* valid,
                              void* stream);
 
+/* Cosine read of the stride-G snapshots, forward.  [replaces the core of SharedMixer._read, gqa25/memlm_sh.py:379-397:
+ * fp32 L2-normalisation of the queries with clamp 1e-6 (:379), logits = (q . kbuf^T) * kinv * sharpness (:383-393),
+ * masked softmax over the valid rows with an all-invalid snapshot reading exactly zero (:394), rd = att . buf (:395).]
+ *   qr     (B, T, H, NQ, DK)  read queries as projected by the caller (q_dtype); normalised inside
+ *   sharp  (B, T, H, NQ) fp32: the product exp(log_rsel) * exp(C tanh(read_s / C)) the caller forms (:383-393)
+ *   kbuf   (B, NB, H, N, DK), vbuf (B, NB, H, N, DV)  snapshots (snap_dtype), NB = ceil(T / G)
+ *   kinv   (B, NB, H, N) fp32, valid (B, NB, H, N) bytes: from slotscan_writer_epilogue
+ *   rd     (B, T, H, NQ, DV) (q_dtype): token t reads snapshot t / G only
+ * Any DK, DV <= 128, N <= 2048.  Forward only in this version. */
+typedef struct {
+    int32_t B, T, H, NQ, N, DK, DV, G;
+    int32_t q_dtype, snap_dtype;
+} slotscan_read_params;
+int slotscan_read_check(const slotscan_read_params* p);
+int slotscan_read_fwd(const slotscan_read_params* p, const void* qr, const float* sharp, const void* kbuf,
+                      const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, void* stream);
+
 /* Registers / spilled bytes / static shared memory / max threads of each kernel, the analogue of kernel_attrs
  * (gqa25/slotkern_cuda.py:467-479).  Fills up to `cap` entries (HOST memory), returns how many kernels exist. */
 typedef struct {

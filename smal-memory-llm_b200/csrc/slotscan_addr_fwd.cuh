@@ -21,6 +21,10 @@
 
 namespace slotscan {
 
+// Optional instrumentation (-DSLOTSCAN_PHASE_TIMING, never in the shipped library): clock64 deltas summed per role and
+// phase, read back through slotscan_debug_phase_cycles_<dtype>.  Forward scan slots: 0 resolver work, 1 resolver
+// barrier wait, 2 / 3 column warps before / in the dots, 4 column barrier wait, 5 chunk duties, 8-11 inside the resolver
+// (bookkeeping, scores, argmax, load issue).  The marks perturb the schedule; use them for shares, not for totals.
 #ifdef SLOTSCAN_PHASE_TIMING
 static __device__ unsigned long long g_phase_cycles[16];
 #define STEP_T0() long long _st = clock64()

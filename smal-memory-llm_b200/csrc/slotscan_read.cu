@@ -1,0 +1,201 @@
+// Cosine read of the stride-G snapshots, forward.   [reference SharedMixer._read, gqa25/memlm_sh.py:379-397]
+//
+// Token t reads the snapshot of block t / G only.  Per (sequence, block, head) the G tokens x NQ queries of the block
+// share one snapshot:  q is L2-normalised in fp32 (clamp 1e-6),  logit_n = <q, K_n> * kinv_n * sharp  over the VALID rows
+// (sharp = the per-(token, head, query) multiplier exp(log_rsel) * exp(C tanh(.)) the caller forms, :383-393), softmax
+// over the valid rows (an all-invalid snapshot reads exactly zero, :394), rd = att . V.
+//
+// One CTA of 4 warps per (sequence, block, head).  Warp 0 compacts the list of valid rows (rows are occupied in index
+// order, so with the benchmark's scans ~12 of 192): all work and all memory traffic scale with the valid rows, not
+// with N.  Each warp then takes 4 queries at a time: lane = columns (lane, lane + 32, ...), a key row is loaded once
+// per warp for its 4 queries, logits are reduced by shuffles, the softmax runs with lane = row, and the value pass
+// accumulates 4 queries x columns in registers.  Any dk, dv <= 128.  This first version uses the CUDA cores: with
+// M = G * NQ = 16 queries per snapshot the contraction is far below what would need the tensor cores to stay
+// HBM-bound when only the valid rows are read.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "slotscan.h"
+#include "slotscan_common.cuh"
+
+namespace slotscan {
+
+constexpr int RD_THREADS = 128, RD_WARPS = 4, RD_QPW = 4, RD_MAXC = 4;     // columns per lane: up to 128 / 32
+
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename Tq, typename Tsn>
+__global__ void __launch_bounds__(RD_THREADS) read_fwd_kernel(const slotscan_read_params p, const Tq* __restrict__ qr,
+                                                             const float* __restrict__ sharp,
+                                                             const Tsn* __restrict__ kbuf, const Tsn* __restrict__ vbuf,
+                                                             const float* __restrict__ kinv,
+                                                             const uint8_t* __restrict__ valid, Tq* __restrict__ rd) {
+    extern __shared__ __align__(16) float rsm[];
+    const int N = p.N, T = p.T, H = p.H, NQ = p.NQ, DK = p.DK, DV = p.DV, G = p.G;
+    const int NB = (T + G - 1) / G;
+    int* s_rows = reinterpret_cast<int*>(rsm);                 // [N] indices of the valid rows
+    float* s_ki = rsm + N;                                     // [N] their kinv
+    float* s_sc = rsm + ((2 * N + 3) & ~3);                    // [warps][N][4] logits, then attention weights (16-byte aligned)
+    __shared__ int s_nv;
+    const int so = blockIdx.x;                                 // (b * NB + nb) * H + h
+    const int h = so % H, nb = (so / H) % NB, b = so / (H * NB);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (warp == 0) {
+        int nv = 0;
+        for (int base = 0; base < N; base += 32) {
+            const int n = base + lane;
+            const bool v = n < N && valid[(size_t)so * N + n] != 0;
+            const unsigned bal = __ballot_sync(FULL, v);
+            if (v) {
+                const int pos = nv + __popc(bal & ((1u << lane) - 1u));
+                s_rows[pos] = n;
+                s_ki[pos] = kinv[(size_t)so * N + n];
+            }
+            nv += __popc(bal);
+        }
+        if (lane == 0) s_nv = nv;
+    }
+    __syncthreads();
+    const int nv = s_nv;
+    const int t0 = nb * G, tc = min(G, T - t0), M = tc * NQ;   // queries that read this snapshot
+    float* sc = s_sc + (size_t)warp * N * RD_QPW;
+    const Tsn* Kb = kbuf + (size_t)so * N * DK;
+    const Tsn* Vb = vbuf + (size_t)so * N * DV;
+
+    for (int q0 = warp * RD_QPW; q0 < M; q0 += RD_WARPS * RD_QPW) {
+        size_t qi[RD_QPW];
+        float qv[RD_QPW][RD_MAXC], scale[RD_QPW];
+#pragma unroll
+        for (int u = 0; u < RD_QPW; u++) {
+            const int m = min(q0 + u, M - 1);                  // a short last group repeats its last query
+            qi[u] = (((size_t)b * T + t0 + m / NQ) * H + h) * NQ + m % NQ;
+            float qq = 0.f;
+#pragma unroll
+            for (int c = 0; c < RD_MAXC; c++) {
+                const int col = lane + 32 * c;
+                qv[u][c] = col < DK ? ldf(qr + qi[u] * DK + col) : 0.f;
+                qq = fmaf(qv[u][c], qv[u][c], qq);
+            }
+            qq = warp_sum(qq);
+            scale[u] = sharp[qi[u]] / fmaxf(sqrtf(qq), 1e-6f);
+        }
+        // ---- logits over the valid rows ----
+        for (int j = 0; j < nv; j++) {
+            const Tsn* row = Kb + (size_t)s_rows[j] * DK;
+            float kx[RD_MAXC];
+#pragma unroll
+            for (int c = 0; c < RD_MAXC; c++) kx[c] = (lane + 32 * c) < DK ? ldf(row + lane + 32 * c) : 0.f;
+            float d[RD_QPW];
+#pragma unroll
+            for (int u = 0; u < RD_QPW; u++) {
+                float a = 0.f;
+#pragma unroll
+                for (int c = 0; c < RD_MAXC; c++) a = fmaf(kx[c], qv[u][c], a);
+                d[u] = warp_sum(a);
+            }
+            if (lane == 0) {
+                const float ki = s_ki[j];
+                *reinterpret_cast<float4*>(sc + 4 * j) =
+                    make_float4(d[0] * ki * scale[0], d[1] * ki * scale[1], d[2] * ki * scale[2], d[3] * ki * scale[3]);
+            }
+        }
+        __syncwarp();
+        // ---- softmax over the valid rows, lane = row ----
+#pragma unroll
+        for (int u = 0; u < RD_QPW; u++) {
+            float m = -INFINITY;
+            for (int j = lane; j < nv; j += 32) m = fmaxf(m, sc[4 * j + u]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, off));
+            float se = 0.f;
+            for (int j = lane; j < nv; j += 32) {
+                const float e = expf(sc[4 * j + u] - m);
+                sc[4 * j + u] = e;
+                se += e;
+            }
+            se = warp_sum(se);
+            const float inv = 1.f / se;
+            for (int j = lane; j < nv; j += 32) sc[4 * j + u] *= inv;
+        }
+        __syncwarp();
+        // ---- rd = att . V ----
+        float acc[RD_QPW][RD_MAXC];
+#pragma unroll
+        for (int u = 0; u < RD_QPW; u++)
+#pragma unroll
+            for (int c = 0; c < RD_MAXC; c++) acc[u][c] = 0.f;
+        for (int j = 0; j < nv; j++) {
+            const Tsn* row = Vb + (size_t)s_rows[j] * DV;
+            const float4 a4 = *reinterpret_cast<const float4*>(sc + 4 * j);
+            const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+            for (int c = 0; c < RD_MAXC; c++) {
+                const float vx = (lane + 32 * c) < DV ? ldf(row + lane + 32 * c) : 0.f;
+#pragma unroll
+                for (int u = 0; u < RD_QPW; u++) acc[u][c] = fmaf(a[u], vx, acc[u][c]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RD_QPW; u++) {
+            if (q0 + u < M) {
+#pragma unroll
+                for (int c = 0; c < RD_MAXC; c++)
+                    if (lane + 32 * c < DV) stf(rd + qi[u] * DV + lane + 32 * c, acc[u][c]);   // nv == 0: exactly zero
+            }
+        }
+        __syncwarp();
+    }
+}
+
+template <typename Tq, typename Tsn>
+static cudaError_t launch_read(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf,
+                               const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st) {
+    const int NB = (p.T + p.G - 1) / p.G;
+    const size_t sm = sizeof(float) * ((size_t)((2 * p.N + 3) & ~3) + (size_t)p.N * RD_WARPS * RD_QPW);
+    auto kern = read_fwd_kernel<Tq, Tsn>;
+    if (sm > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return e;
+    }
+    kern<<<p.B * NB * p.H, RD_THREADS, sm, st>>>(p, (const Tq*)qr, sharp, (const Tsn*)kbuf, (const Tsn*)vbuf, kinv, valid,
+                                                  (Tq*)rd);
+    return cudaGetLastError();
+}
+
+}  // namespace slotscan
+
+using namespace slotscan;
+
+extern "C" int slotscan_read_check(const slotscan_read_params* p) {
+    if (p == nullptr) return SLOTSCAN_E_NULL;
+    if (p->B < 1 || p->T < 1 || p->H < 1 || p->NQ < 1 || p->G < 1) return SLOTSCAN_E_SHAPE;
+    if (p->N < 1 || p->N > 2048) return SLOTSCAN_E_SHAPE;                   /* 72 N bytes of shared memory */
+    if (p->DK < 1 || p->DK > 32 * RD_MAXC || p->DV < 1 || p->DV > 32 * RD_MAXC) return SLOTSCAN_E_SHAPE;
+    if ((long long)p->B * ((p->T + p->G - 1) / p->G) * p->H > 2147483647LL) return SLOTSCAN_E_SHAPE;
+    if ((p->q_dtype != SLOTSCAN_F32 && p->q_dtype != SLOTSCAN_BF16) ||
+        (p->snap_dtype != SLOTSCAN_F32 && p->snap_dtype != SLOTSCAN_BF16))
+        return SLOTSCAN_E_DTYPE;
+    return SLOTSCAN_OK;
+}
+
+extern "C" int slotscan_read_fwd(const slotscan_read_params* p, const void* qr, const float* sharp, const void* kbuf,
+                                 const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, void* stream_) {
+    const int rc = slotscan_read_check(p);
+    if (rc != SLOTSCAN_OK) return rc;
+    if (!qr || !sharp || !kbuf || !vbuf || !kinv || !valid || !rd) return SLOTSCAN_E_NULL;
+    cudaStream_t st = (cudaStream_t)stream_;
+    cudaError_t e;
+    const bool qb = p->q_dtype == SLOTSCAN_BF16, sb = p->snap_dtype == SLOTSCAN_BF16;
+    if (qb && sb) e = launch_read<__nv_bfloat16, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    else if (qb) e = launch_read<__nv_bfloat16, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    else if (sb) e = launch_read<float, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    else e = launch_read<float, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    return (int)e;
+}

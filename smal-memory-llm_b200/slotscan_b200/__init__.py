@@ -4,3 +4,4 @@ loudly if it is not built."""
 from .scan import kv_scan_c, kv_scan_g, scan_kv, scan_with_log  # noqa: F401
 from ._lib import kernel_attrs  # noqa: F401
 from .epilogue import fq, quantize_mem, writer_epilogue  # noqa: F401
+from .read import read_snapshots  # noqa: F401

@@ -31,6 +31,11 @@ class EpilogueParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int32), ("bits", ctypes.c_int32), ("group", ctypes.c_int32)]
 
 
+class ReadParams(ctypes.Structure):
+    """slotscan_read_params of include/slotscan.h."""
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "T", "H", "NQ", "N", "DK", "DV", "G", "q_dtype", "snap_dtype")]
+
+
 class KernelAttr(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char * 48), ("regs", ctypes.c_int32), ("local_bytes", ctypes.c_int32),
                 ("static_smem", ctypes.c_int32), ("max_threads", ctypes.c_int32)]
@@ -67,6 +72,10 @@ def lib():
         L.slotscan_epilogue_check.restype = ci
         L.slotscan_writer_epilogue.argtypes = [ctypes.POINTER(EpilogueParams), vp, vp, vp, vp, vp]
         L.slotscan_writer_epilogue.restype = ci
+        L.slotscan_read_check.argtypes = [ctypes.POINTER(ReadParams)]
+        L.slotscan_read_check.restype = ci
+        L.slotscan_read_fwd.argtypes = [ctypes.POINTER(ReadParams), vp, vp, vp, vp, vp, vp, vp, vp]
+        L.slotscan_read_fwd.restype = ci
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
         L.slotscan_profile_enable.argtypes = [ci]
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]

@@ -110,3 +110,23 @@ def test_epilogue_validation_and_host_names():
     assert torch.ops.slotscan.fq(x, 3, 16).shape == x.shape
     kq, kinv, valid = torch.ops.slotscan.epilogue(x, True, 3, 16)
     assert kq.dtype == torch.bfloat16 and kinv.shape == (2, 5, 3, 7) and valid.dtype == torch.uint8
+
+
+def test_read_validation_and_fake_kernel():
+    import slotscan_b200 as S
+    from slotscan_b200 import _lib
+    L = _lib.lib()
+    ok = _lib.ReadParams(2, 40, 3, 2, 24, 128, 128, 8, 1, 1)
+    assert L.slotscan_read_check(ctypes.byref(ok)) == 0
+    for field, val in (("DK", 129), ("DV", 0), ("N", 0), ("N", 4096), ("G", 0), ("NQ", 0), ("q_dtype", 3)):
+        p = _lib.ReadParams(2, 40, 3, 2, 24, 128, 128, 8, 1, 1)
+        setattr(p, field, val)
+        assert L.slotscan_read_check(ctypes.byref(p)) < 0, field
+    assert L.slotscan_read_fwd(ctypes.byref(ok), None, None, None, None, None, None, None, None) == -1
+    m = lambda *s, dt=torch.float32: torch.empty(*s, device="meta", dtype=dt)
+    rd = torch.ops.slotscan.read_fwd(m(2, 40, 3, 2, 64), m(2, 40, 3, 2), m(2, 5, 3, 24, 64), m(2, 5, 3, 24, 32),
+                                     m(2, 5, 3, 24), m(2, 5, 3, 24, dt=torch.uint8), 8)
+    assert rd.shape == (2, 40, 3, 2, 32)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        S.read_snapshots(torch.randn(1, 4, 1, 1, 8), torch.ones(1, 4, 1, 1), torch.randn(1, 1, 1, 2, 8),
+                         torch.randn(1, 1, 1, 2, 8), torch.ones(1, 1, 1, 2), torch.ones(1, 1, 1, 2, dtype=torch.bool), 4)

@@ -1,0 +1,98 @@
+"""Cosine read of the snapshots (CUDA, through the C ABI) against the reference's golden vector and the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _S():
+    import slotscan_b200 as S
+    return S
+
+
+def rel(a, b):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(b, np.float64)).max() / max(np.abs(b).max(), 1e-30))
+
+
+def test_read_golden():
+    S = _S()
+    z = np.load(os.path.join(GOLDEN, "read_rsharp_nq2.npz"))
+    G = int(z["G"])
+    f = lambda n: torch.from_numpy(z[n].astype(np.float32)).cuda()
+    with torch.no_grad():
+        rd = S.read_snapshots(f("qr"), f("sharp"), f("kbuf"), f("vbuf"), f("kinv"), torch.from_numpy(z["valid"]).cuda(), G)
+    assert rel(rd.cpu().numpy(), z["rd"]) < 1e-5                       # float32 mode tolerance
+    assert rd[:, :G].abs().max() == 0                                  # block 0 reads the empty memory: exactly zero
+
+
+def _case(B, T, H, NQ, N, DK, DV, G, nvalid, seed):
+    g = torch.Generator().manual_seed(seed)
+    NB = (T + G - 1) // G
+    qr = torch.randn(B, T, H, NQ, DK, generator=g)
+    sharp = torch.nn.functional.softplus(torch.randn(B, T, H, NQ, generator=g)) + 1
+    kbuf = torch.randn(B, NB, H, N, DK, generator=g)
+    vbuf = 0.5 * torch.randn(B, NB, H, N, DV, generator=g)
+    # rows fill in index order as the scan proceeds; snapshot 0 is empty
+    occ = torch.minimum(torch.arange(NB) * 2, torch.tensor(nvalid)).view(1, NB, 1, 1)
+    live = torch.arange(N).view(1, 1, 1, N) < occ
+    kbuf = kbuf * live.unsqueeze(-1)
+    vbuf = vbuf * live.unsqueeze(-1)
+    return qr, sharp, kbuf, vbuf
+
+
+@pytest.mark.parametrize("shape", [(2, 40, 3, 2, 24, 128, 128, 8, 13), (1, 37, 2, 1, 192, 64, 64, 7, 192),
+                                   (2, 16, 2, 4, 10, 16, 8, 16, 10), (1, 9, 1, 3, 70, 100, 36, 1, 40)],
+                         ids=["sh25_like", "all_rows_T%G", "G16_NQ4_small", "G1_odd_widths"])
+def test_read_matches_oracle_f32(shape):
+    S = _S()
+    B, T, H, NQ, N, DK, DV, G, nvalid = shape
+    qr, sharp, kbuf, vbuf = _case(*shape, seed=5)
+    kinv, valid = O.epilogue(kbuf.numpy(), dtype=np.float32)
+    want = O.read_fwd(qr.numpy(), sharp.numpy(), kbuf.numpy(), vbuf.numpy(), kinv, valid, G, dtype=np.float64)
+    with torch.no_grad():
+        rd = S.read_snapshots(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).cuda(),
+                              torch.from_numpy(valid).cuda(), G)
+    assert rel(rd.cpu().numpy(), want) < 1e-5
+    assert rd[:, :G].abs().max() == 0
+
+
+def test_read_after_scan_and_epilogue_bf16():
+    """The three ops in sequence as the writer and a reader layer use them: scan -> epilogue -> read, bf16 storage."""
+    S = _S()
+    from tests.scan_cases import make_inputs
+    B, T, H, N, D, G, NQ = 2, 64, 3, 24, 32, 8, 2
+    inp = make_inputs("bench", B, T, H, D, D, seed=7)
+    k, q, v = (inp[n].cuda().to(torch.bfloat16) for n in ("k", "q", "v"))
+    with torch.no_grad():
+        kbuf, vbuf = S.kv_scan_g(k, v, inp["gate"].cuda(), inp["fr"].cuda(), N, 16.0, G=G, hard=True, detach_addr=True,
+                                 q=q, occ_bin=True, out_dtype=torch.bfloat16)
+        kq, vq, kinv, valid = S.writer_epilogue(kbuf, vbuf, torch.bfloat16)
+        g = torch.Generator().manual_seed(8)
+        qr = torch.randn(B, T, H, NQ, D, generator=g).cuda().to(torch.bfloat16)
+        sharp = (torch.nn.functional.softplus(torch.randn(B, T, H, NQ, generator=g)) + 1).cuda()
+        rd = S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
+    want = O.read_fwd(qr.float().cpu().numpy(), sharp.cpu().numpy(), kq.float().cpu().numpy(), vq.float().cpu().numpy(),
+                      kinv.cpu().numpy(), valid.cpu().numpy(), G, dtype=np.float64)
+    got = rd.float().cpu().numpy()
+    # bf16 output: the oracle rounded to bf16, +- 1 ulp, plus the 2e-3 band of the bf16 mode
+    assert np.all(np.abs(got - want) <= 2e-3 * np.abs(want).max() + np.abs(want) * 2.0 ** -7)
+    assert rd.dtype == torch.bfloat16 and rd[:, :G].abs().max() == 0
+
+
+def test_read_contract():
+    S = _S()
+    qr, sharp, kbuf, vbuf = _case(1, 8, 1, 1, 4, 16, 16, 4, 4, seed=1)
+    kinv, valid = O.epilogue(kbuf.numpy(), dtype=np.float32)
+    ki, va = torch.from_numpy(kinv), torch.from_numpy(valid)
+    with pytest.raises(RuntimeError):
+        S.read_snapshots(qr, sharp, kbuf, vbuf, ki, va, 4)            # CPU tensors
+    with pytest.raises(ValueError):
+        S.read_snapshots(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), ki.cuda(), va.cuda(), 3)   # NB mismatch
+    with pytest.raises(NotImplementedError):
+        S.read_snapshots(qr.cuda().requires_grad_(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), ki.cuda(), va.cuda(), 4)
