@@ -122,8 +122,13 @@ def cpu_leg(steps, warmup, sample_B=2, threads=None, budget_s=90.0):
     on a bounded sample: `sample_B` sequences of the full T / H / N / D."""
     import numpy as np
     from oracle import oracle as O
-    if threads:
-        O.set_threads(threads)
+    # all host cores the process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its children)
+    if not threads:
+        try:
+            threads = len(os.sched_getaffinity(0))
+        except AttributeError:
+            threads = os.cpu_count() or 1
+    O.set_threads(threads)
     s = SHAPE
     inp = make_host_inputs(sample_B, s["T"], s["H"], s["DK"], s["DV"], seed=0)
     kw = dict(N=s["N"], temp=16.0, G=s["G"], hard=True, q=inp["q"], occ_bin=True, dtype=np.float32)
