@@ -358,6 +358,54 @@ def run_epilogue(args, local_rank):
     print(json.dumps(line))
 
 
+def run_read(args, local_rank):
+    """Secondary line (`--workload read`): one reader layer's cosine read (NQ = 2 queries per head) over the snapshots of
+    the config-1 scan: scan -> writer epilogue once (untimed), then the read is timed.  One GPU."""
+    import torch
+    import slotscan_b200 as S
+    torch.cuda.set_device(local_rank)
+    s = SHAPE
+    B, T, H, N, D, G, NQ = (args.B or s["B"]), (args.T or s["T"]), s["H"], s["N"], s["DK"], s["G"], 2
+    inp = make_host_inputs(B, T, H, D, D, seed=0, dist=args.dist)
+    k, q, v = (inp[n].cuda().to(torch.bfloat16) for n in ("k", "q", "v"))
+    with torch.no_grad():
+        kbuf, vbuf = S.kv_scan_g(k, v, inp["gate"].cuda(), inp["fr"].cuda(), N, 16.0, G=G, hard=True, detach_addr=True,
+                                 q=q, occ_bin=True, out_dtype=torch.bfloat16)
+        kq, vq, kinv, valid = S.writer_epilogue(kbuf, vbuf, torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        qr = torch.randn(B, T, H, NQ, D, generator=g, device="cuda", dtype=torch.bfloat16)
+        sharp = torch.nn.functional.softplus(torch.randn(B, T, H, NQ, generator=g, device="cuda")) + 1
+        with ClockSampler(local_rank) as clk:
+            for _ in range(max(args.warmup, 3)):
+                S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
+            b.record()
+            torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+    peak, which = hbm_peak()
+    rows = kq.numel() // D
+    alg = qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 5      # q, rd, sharp, both snapshots, kinv+valid
+    touched = qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * int(valid.sum()) * D * 2 + rows * 5
+    line = {"metric": "snapshot read tokens/s per reader layer (config-1 shape, NQ=2, bf16)", "value": B * T / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16 storage",
+            "data": "synthetic", "gpu_launches": args.steps,
+            "config": {"workload": "cosine read, forward: B=%d T=%d H=%d NQ=%d N=%d dk=dv=%d G=%d over the snapshots of the "
+                                   "config-1 scan (dist=%s), valid rows per snapshot %.1f of %d"
+                                   % (B, T, H, NQ, N, D, G, args.dist, float(valid.sum()) / (rows / N), N)},
+            # invalid rows are masked out of the softmax and never loaded: the bytes that count are those of the valid
+            # rows; the all-rows figure (what a dense batched GEMM reads) is given beside it
+            "roofline": {"bound": "hbm", "achieved": touched / ms / 1e6, "peak": peak, "unit": "GB/s",
+                         "frac": touched / ms / 1e6 / peak, "traffic": None, "peak_source": which,
+                         "algorithmic_bytes": touched, "bytes_all_rows": alg, "achieved_all_rows": alg / ms / 1e6},
+            "clocks": clk.summary()}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,8 +416,9 @@ def main():
     ap.add_argument("--T", type=int, default=0, help="tokens per sequence (default 1024)")
     ap.add_argument("--dist", default="bench", help="input distribution: bench (the benchmark's) | fill (every slot used) | clustered")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="scan", choices=["scan", "epilogue"],
-                    help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass (1 GPU)")
+    ap.add_argument("--workload", default="scan", choices=["scan", "epilogue", "read"],
+                    help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass; "
+                         "read: one reader layer's cosine read of the snapshots (secondary lines, 1 GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -380,6 +429,9 @@ def main():
     elif args.workload == "epilogue":
         if rank == 0:
             run_epilogue(args, local_rank)
+    elif args.workload == "read":
+        if rank == 0:
+            run_read(args, local_rank)
     else:
         run_gpu(args, rank, local_rank, world)
 
