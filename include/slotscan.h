@@ -146,7 +146,11 @@ int slotscan_writer_epilogue(const slotscan_epilogue_params* p, const void* x, v
  *   kbuf   (B, NB, H, N, DK), vbuf (B, NB, H, N, DV)  snapshots (snap_dtype), NB = ceil(T / G)
  *   kinv   (B, NB, H, N) fp32, valid (B, NB, H, N) bytes: from slotscan_writer_epilogue
  *   rd     (B, T, H, NQ, DV) (q_dtype): token t reads snapshot t / G only
- * Any DK, DV <= 128, N <= 2048.  Forward only in this version. */
+ * Any DK, DV <= 128, N <= 2048.
+ * slotscan_read_bwd is the adjoint for an upstream gradient drd (shape and dtype of rd): dqr (like qr), dsharp (like
+ * sharp), dkbuf / dvbuf (like kbuf / vbuf, exact zeros in the rows that are not valid) and dkinv (B, NB, H, N) fp32, the
+ * gradient of the kinv INPUT (the writer epilogue differentiates kinv = rsqrt(nsq) itself; the reference gets the
+ * same total from autograd).  Its shared-memory tables hold (G * NQ) x N entries: SLOTSCAN_E_TOO_LARGE beyond 200 KB. */
 typedef struct {
     int32_t B, T, H, NQ, N, DK, DV, G;
     int32_t q_dtype, snap_dtype;
@@ -154,6 +158,9 @@ typedef struct {
 int slotscan_read_check(const slotscan_read_params* p);
 int slotscan_read_fwd(const slotscan_read_params* p, const void* qr, const float* sharp, const void* kbuf,
                       const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, void* stream);
+int slotscan_read_bwd(const slotscan_read_params* p, const void* qr, const float* sharp, const void* kbuf,
+                      const void* vbuf, const float* kinv, const uint8_t* valid, const void* drd, void* dqr,
+                      float* dsharp, void* dkbuf, void* dvbuf, float* dkinv, void* stream);
 
 /* Registers / spilled bytes / static shared memory / max threads of each kernel, the analogue of kernel_attrs
  * (gqa25/slotkern_cuda.py:467-479).  Fills up to `cap` entries (HOST memory), returns how many kernels exist. */

@@ -76,6 +76,8 @@ def lib():
         L.slotscan_read_check.restype = ci
         L.slotscan_read_fwd.argtypes = [ctypes.POINTER(ReadParams), vp, vp, vp, vp, vp, vp, vp, vp]
         L.slotscan_read_fwd.restype = ci
+        L.slotscan_read_bwd.argtypes = [ctypes.POINTER(ReadParams)] + [vp] * 13
+        L.slotscan_read_bwd.restype = ci
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
         L.slotscan_profile_enable.argtypes = [ci]
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]

@@ -94,5 +94,53 @@ def test_read_contract():
         S.read_snapshots(qr, sharp, kbuf, vbuf, ki, va, 4)            # CPU tensors
     with pytest.raises(ValueError):
         S.read_snapshots(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), ki.cuda(), va.cuda(), 3)   # NB mismatch
-    with pytest.raises(NotImplementedError):
-        S.read_snapshots(qr.cuda().requires_grad_(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), ki.cuda(), va.cuda(), 4)
+
+
+def test_read_backward_golden():
+    """Gradients of the read against the reference's autograd (golden vector): kinv is computed from kbuf under
+    autograd there, so the chain here is writer_epilogue -> read_snapshots."""
+    S = _S()
+    z = np.load(os.path.join(GOLDEN, "read_rsharp_nq2.npz"))
+    G = int(z["G"])
+    f = lambda n: torch.from_numpy(z[n].astype(np.float32)).cuda()
+    qr, sharp = f("qr").requires_grad_(), f("sharp").requires_grad_()
+    kbuf, vbuf = f("kbuf").requires_grad_(), f("vbuf").requires_grad_()
+    kq, vq, kinv, valid = S.writer_epilogue(kbuf, vbuf, torch.float32)
+    rd = S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
+    rd.backward(f("drd"))
+    assert rel(qr.grad.cpu().numpy(), z["dqr"]) < 1e-5
+    assert rel(vbuf.grad.cpu().numpy(), z["dvbuf"]) < 1e-5
+    assert rel(kbuf.grad.cpu().numpy(), z["dkbuf"]) < 1e-5
+    C = float(z["C"])
+    ds_raw = sharp.grad.cpu().numpy() * z["sharp"] * (1 - np.tanh(z["s_raw"].reshape(z["sharp"].shape) / C) ** 2)
+    assert rel(ds_raw.reshape(z["ds_raw"].shape), z["ds_raw"]) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(2, 40, 3, 2, 24, 128, 128, 8, 13), (1, 37, 2, 1, 192, 64, 64, 7, 192),
+                                   (2, 16, 2, 4, 10, 16, 8, 16, 10), (1, 9, 1, 3, 70, 100, 36, 1, 40)],
+                         ids=["sh25_like", "all_rows_T%G", "G16_NQ4_small", "G1_odd_widths"])
+def test_read_backward_matches_oracle(shape):
+    S = _S()
+    B, T, H, NQ, N, DK, DV, G, nvalid = shape
+    qr, sharp, kbuf, vbuf = _case(*shape, seed=6)
+    drd = torch.randn(B, T, H, NQ, DV, generator=torch.Generator().manual_seed(9))
+    kinv, valid = O.epilogue(kbuf.numpy(), dtype=np.float64)
+    want = O.read_bwd(qr.numpy(), sharp.numpy(), kbuf.numpy(), vbuf.numpy(), kinv, valid, G, drd.numpy(),
+                      kinv_const=True, dtype=np.float64)
+    dqr, dsharp, dkbuf, dvbuf, dkinv = torch.ops.slotscan.read_bwd(
+        qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).float().cuda(),
+        torch.from_numpy(valid).cuda(), drd.cuda(), G)
+    assert rel(dqr.cpu().numpy(), want["dqr"]) < 1e-5
+    assert rel(dsharp.cpu().numpy(), want["dsharp"]) < 1e-5
+    assert rel(dvbuf.cpu().numpy(), want["dvbuf"]) < 1e-5
+    assert rel(dkbuf.cpu().numpy(), want["dkbuf"]) < 1e-5
+    # the kinv path: oracle with kinv differentiated = direct part + dkinv * d kinv / d kbuf
+    full = O.read_bwd(qr.numpy(), sharp.numpy(), kbuf.numpy(), vbuf.numpy(), kinv, valid, G, drd.numpy(),
+                      kinv_const=False, dtype=np.float64)
+    mine = dkbuf.cpu().double().numpy() + (dkinv.cpu().double().numpy() * -(kinv ** 3))[..., None] * kbuf.double().numpy() * valid[..., None]
+    assert rel(mine, full["dkbuf"]) < 1e-5
+    # rows that are not valid get exact zeros; repeatable bit for bit
+    assert (dkbuf.cpu()[~torch.from_numpy(valid)] == 0).all() and (dvbuf.cpu()[~torch.from_numpy(valid)] == 0).all()
+    again = torch.ops.slotscan.read_bwd(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).float().cuda(),
+                                        torch.from_numpy(valid).cuda(), drd.cuda(), G)
+    assert all(torch.equal(a, b) for a, b in zip(again, (dqr, dsharp, dkbuf, dvbuf, dkinv)))
