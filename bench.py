@@ -386,6 +386,16 @@ def run_read(args, local_rank):
             b.record()
             torch.cuda.synchronize()
         ms = a.elapsed_time(b) / args.steps
+        drd = torch.randn(B, T, H, NQ, D, generator=g, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            torch.ops.slotscan.read_bwd(qr, sharp, kq, vq, kinv, valid.to(torch.uint8), drd, G)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(args.steps):
+            torch.ops.slotscan.read_bwd(qr, sharp, kq, vq, kinv, valid.to(torch.uint8), drd, G)
+        b.record()
+        torch.cuda.synchronize()
+        ms_bwd = a.elapsed_time(b) / args.steps
     peak, which = hbm_peak()
     rows = kq.numel() // D
     alg = qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 5      # q, rd, sharp, both snapshots, kinv+valid
@@ -402,6 +412,11 @@ def run_read(args, local_rank):
             "roofline": {"bound": "hbm", "achieved": touched / ms / 1e6, "peak": peak, "unit": "GB/s",
                          "frac": touched / ms / 1e6 / peak, "traffic": None, "peak_source": which,
                          "algorithmic_bytes": touched, "bytes_all_rows": alg, "achieved_all_rows": alg / ms / 1e6},
+            # backward: re-reads what the forward read plus drd, writes dqr, dsharp and BOTH snapshot gradients in full
+            # (exact zeros in the rows that are not valid) and dkinv
+            "backward": {"ms_per_step": ms_bwd, "algorithmic_bytes": touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4,
+                         "achieved": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6,
+                         "frac": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6 / peak},
             "clocks": clk.summary()}
     print(json.dumps(line))
 

@@ -212,6 +212,19 @@ extern "C" int slotscan_read_fwd(const slotscan_read_params* p, const void* qr, 
 // Rows that are not valid get exact zeros.
 namespace slotscan {
 
+// zero n elements at p with the whole CTA: 16-byte stores when the block allows it
+template <typename T>
+__device__ __forceinline__ void zero_fill(T* p, size_t n, int tid) {
+    const size_t bytes = n * sizeof(T);
+    if (((reinterpret_cast<uintptr_t>(p) | bytes) & 15) == 0) {
+        uint4* p4 = reinterpret_cast<uint4*>(p);
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        for (size_t i = tid; i < bytes / 16; i += RD_THREADS) p4[i] = z;
+    } else {
+        for (size_t i = tid; i < n; i += RD_THREADS) stf(p + i, 0.f);
+    }
+}
+
 struct ReadBwdSmem { int rows, ki, qinv, sc, sd, dki, att, cf, total; };
 __host__ __device__ inline ReadBwdSmem read_bwd_layout(int N, int M) {
     ReadBwdSmem L;
@@ -262,8 +275,8 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
         if (lane == 0) s_nv = nv;
     }
     // zero the whole block of snapshot gradients first; the valid rows are overwritten after the barrier below
-    for (size_t i = tid; i < (size_t)N * DK; i += RD_THREADS) stf(dkbuf + (size_t)so * N * DK + i, 0.f);
-    for (size_t i = tid; i < (size_t)N * DV; i += RD_THREADS) stf(dvbuf + (size_t)so * N * DV + i, 0.f);
+    zero_fill(dkbuf + (size_t)so * N * DK, (size_t)N * DK, tid);
+    zero_fill(dvbuf + (size_t)so * N * DV, (size_t)N * DV, tid);
     for (int i = tid; i < N; i += RD_THREADS) dkinv[(size_t)so * N + i] = 0.f;
     __syncthreads();
     const int nv = s_nv;
