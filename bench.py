@@ -298,7 +298,7 @@ def run_gpu(args, rank, local_rank, world):
                         "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "peak_kind": peak_kind, "traffic": TRAFFIC.get(top),
+                             "frac": achieved / peak, "peak_kind": peak_kind, "traffic": TRAFFIC.get(top) if (B == SHAPE["B"] and T == SHAPE["T"] and args.dist == "bench") else None,
                              "algorithmic_bytes_per_launch": top_bytes,
                              "step": {"algorithmic_bytes": ab["total"] * H * B * T, "achieved": step_gbs, "frac": step_gbs / peak}},
                 "kernels": kern,
@@ -313,7 +313,10 @@ def run_gpu(args, rank, local_rank, world):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at the benchmark size, from the ncu captures
 # summarised under profiles/ (taken at B = 8 and scaled by 8: traffic is proportional to the batch)
-TRAFFIC = {"replay_rows_k": 8 * (13.03e6 + 274.17e6), "replay_rows_v": 8 * (13.03e6 + 274.17e6), "addr_fwd": 8 * 25.6e6}
+# rows_bwd reads far fewer bytes than its algorithmic figure with the benchmark's inputs: snapshot-gradient rows of
+# slots that were never candidates have no path to any input gradient and are skipped
+TRAFFIC = {"replay_rows_k": 8 * (13.03e6 + 274.17e6), "replay_rows_v": 8 * (13.03e6 + 274.17e6), "addr_fwd": 8 * 25.6e6,
+           "rows_bwd_k": 8 * (107.8e6 + 16.7e6), "addr_bwd": 8 * (52.34e6 + 0.96e6)}
 
 
 def run_epilogue(args, local_rank):
