@@ -1,6 +1,6 @@
 """Generates the golden fixtures of this directory by RUNNING THE REFERENCE's own torch code on CPU.
 
-Needs the reference checkout (default /root/reference, or $SLOTSCAN_REFERENCE); it imports, unmodified,
+Needs the reference checkout (its location: $SLOTSCAN_REFERENCE, else the default in REF below); it imports, unmodified,
     gqa25/slotkern_kv.py   _ref_scan_kv_impl / ref_scan_kv     (the scan; gradients by torch autograd)
     gqa25/memlm_sh.py      SharedMixer._read, _fq, _quantize_mem (the read and the storage quantiser)
 and writes one compressed .npz per case.  The fixtures travel with the repository; the reference does not.
