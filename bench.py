@@ -239,16 +239,37 @@ def run_gpu(args, rank, local_rank, world):
     prof = _lib.profile_read()
     _lib.profile_enable(False)
     # ---- end-to-end leg: host inputs in, input gradients out, every step ----
-    hout = None
+    # The batch goes through in P chunks on P streams, so that the host->device copy of one chunk, the kernels of
+    # another and the device->host copy of a third overlap (sequences are independent; the copies use both directions
+    # of the link).  All through the public call, kv_scan_g, as a user would write it.
+    P = args.e2e_chunks if B % args.e2e_chunks == 0 and B >= 2 * args.e2e_chunks else 1
+    bs = B // P
+    streams = [torch.cuda.Stream(device=dev) for _ in range(P)]
+    hout = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (host["k"], host["q"], host["v"], host["gate"], host["fr"])]
+    htemp = torch.empty(P, dtype=torch.float32).pin_memory()
+
     def e2e_step():
-        nonlocal hout
-        x = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
-        grads = step(x)
-        if hout is None:
-            hout = [torch.empty(g_.shape, dtype=g_.dtype).pin_memory() for g_ in grads]
-        for h_, g_ in zip(hout, grads):
-            h_.copy_(g_, non_blocking=True)
-        torch.cuda.current_stream().synchronize()          # the caller holds the gradients on the host
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(cur)
+        for i, st in enumerate(streams):
+            sl = slice(i * bs, (i + 1) * bs)
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                x = {n: t[sl].to(dev, non_blocking=True) for n, t in host.items()}
+                k, q, v = (x[n].requires_grad_() for n in ("k", "q", "v"))
+                g, fr = x["gate"].requires_grad_(), x["fr"].requires_grad_()
+                tp = temp.detach().requires_grad_()
+                kb, vb = S.kv_scan_g(k, v, g, fr, N, tp, G=G, hard=True, hard_gate=False, detach_addr=True, q=q,
+                                     occ_bin=True, out_dtype=bf)
+                torch.autograd.backward([kb, vb], [dkb[sl], dvb[sl]])
+                for h_, g_ in zip(hout, (k.grad, q.grad, v.grad, g.grad, fr.grad)):
+                    h_[sl].copy_(g_, non_blocking=True)
+                htemp[i:i + 1].copy_(tp.grad, non_blocking=True)
+        for st in streams:
+            cur.wait_stream(st)
+        cur.synchronize()                                  # the caller holds the gradients on the host
+        return float(htemp.sum())                          # dtemp is the sum over the chunks
     e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -259,7 +280,7 @@ def run_gpu(args, rank, local_rank, world):
     barrier()
     ms_e2e = f0.elapsed_time(f1)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = sum(t.numel() * t.element_size() for t in hout)
+    d2h = sum(t.numel() * t.element_size() for t in hout) + 4 * P
     ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev)
     if rank == 0:
         toks = B * T * world * args.steps
@@ -295,7 +316,7 @@ def run_gpu(args, rank, local_rank, world):
                            "global_batch": B * world, "seq_len": T, "sharding": "batch, no collective",
                            "l2": "working set %.1f GB per step >> 126 MB L2 (no flush needed)" % (ab["total"] * H * B * T / 1e9)},
                 "e2e": {"value": toks / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e / args.steps},
+                        "ms_per_step": ms_e2e / args.steps, "pipeline": "%d batch chunks on %d streams" % (P, P)},
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
                              "frac": achieved / peak, "peak_kind": peak_kind, "traffic": TRAFFIC.get(top) if (B == SHAPE["B"] and T == SHAPE["T"] and args.dist == "bench") else None,
@@ -434,6 +455,7 @@ def main():
     ap.add_argument("--T", type=int, default=0, help="tokens per sequence (default 1024)")
     ap.add_argument("--dist", default="bench", help="input distribution: bench (the benchmark's) | fill (every slot used) | clustered")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks (= streams) of the end-to-end leg")
     ap.add_argument("--workload", default="scan", choices=["scan", "epilogue", "read"],
                     help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass; "
                          "read: one reader layer's cosine read of the snapshots (secondary lines, 1 GPU)")
