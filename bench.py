@@ -31,6 +31,25 @@ SHAPE = dict(B=64, T=1024, H=6, N=192, DK=128, DV=128, G=8)
 FALLBACK_HBM_GBS = 6650.0
 
 
+_OUT = None
+
+
+def claim_stdout():
+    """Keep the process's real stdout for the one JSON line and point file descriptor 1 at stderr for everything else:
+    libraries print there too (NCCL writes its version banner to stdout from C code)."""
+    global _OUT
+    if _OUT is None:
+        sys.stdout.flush()
+        _OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line):
+    out = _OUT if _OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def algorithmic_bytes_per_token_head(N, DK, DV, G, e_in, e_s):
     """Drop-in form, per token and head: forward reads k,q,v + gate,fr and writes the snapshots; backward re-reads the
     inputs, reads the snapshot gradients and writes dk,dq,dv,dgate,dfr.  Logs and scratch are not counted."""
@@ -172,7 +191,7 @@ def run_reference(args, rank, world):
             "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
             "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------------------------
@@ -327,7 +346,7 @@ def run_gpu(args, rank, local_rank, world):
         if world == 1 and not args.no_cpu:
             r = cpu_leg(1, 0)
             line["cpu_baseline"] = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist_on:
         dist.destroy_process_group()
 
@@ -379,7 +398,7 @@ def run_epilogue(args, local_rank):
                          "frac": alg3 / out[3] / 1e6 / peak, "traffic": None, "peak_source": which},
             "unquantised": {"ms_per_step": out[0], "achieved": alg0 / out[0] / 1e6, "frac": alg0 / out[0] / 1e6 / peak},
             "clocks": clk.summary()}
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_read(args, local_rank):
@@ -442,7 +461,7 @@ def run_read(args, local_rank):
                          "achieved": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6,
                          "frac": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6 / peak},
             "clocks": clk.summary()}
-    print(json.dumps(line))
+    emit(line)
 
 
 def main():
@@ -460,6 +479,7 @@ def main():
                     help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass; "
                          "read: one reader layer's cosine read of the snapshots (secondary lines, 1 GPU)")
     args = ap.parse_args()
+    claim_stdout()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
