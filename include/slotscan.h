@@ -105,6 +105,8 @@ int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, co
  *   - Limit: slotscan_hard_bwd_scratch_bytes(p) must not exceed the capacity, i.e. roughly B*H*T*N <= 1 M table
  *     entries; beyond that the call returns SLOTSCAN_E_TOO_LARGE and launches nothing.
  *   - The call itself allocates no device memory and frees none.
+ *   - On EVERY call the current device (cudaGetDevice) must be the one that owns `stream` and all the pointers: the
+ *     array used is the current device's copy.  Inputs found on another device are refused with SLOTSCAN_E_MODE.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
  *     current); make that first call outside any stream capture.
  *   - Every call on a device shares the one array, which still holds the previous call's table: nothing in it needs

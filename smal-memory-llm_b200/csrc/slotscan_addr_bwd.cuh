@@ -143,10 +143,6 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
     AB_ISSUE_LOADS((nchunk - 1) * CH);
     __syncthreads();
 
-#ifdef SLOTSCAN_PHASE_TIMING
-    long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#endif
-    STEP_T0();
     for (int ck = nchunk - 1; ck >= 0; ck--) {
         const int t0 = ck * CH, cn = min(CH, T - t0);
         // ---- land the chunk's scalars, then its rows ----
@@ -163,7 +159,6 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
             else if (s_ == 1) pre_q[r].store(Dl + j_ * DK + c_);
         }
         __syncthreads();
-        STEP_MARK(0);
         // kold: delta_j = g_j (k_j - kold_j) into Dl, and the row restore for the EARLIEST hit of each row
 #pragma unroll
         for (int r = 0; r < NITEM; r++) {
@@ -199,7 +194,6 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
             }
         }
         __syncthreads();
-        STEP_MARK(1);
         // ---------------- score phase ----------------
         {
             float4 Qr[NI];
@@ -236,7 +230,6 @@ __global__ void __launch_bounds__(AB_THREADS, MINB) addr_bwd_chunked_kernel(
             }
         }
         __syncthreads();
-        STEP_MARK(2);
         // ---------------- softmax adjoint: warp j handles token j (all tokens at once when OCCB) ----------------
         {
             int am_c[CH];
@@ -343,7 +336,6 @@ _Pragma("unroll") \
             }
         }
         __syncthreads();
-        STEP_MARK(3);
         // ---------------- query gradient: warp w owns 16 output columns, lane = (token j, 4 columns) ----------------
         {
             const int j = lane & 7, cc = (warp * 16) + (lane >> 3) * 4;           // column base of this lane
@@ -373,7 +365,6 @@ _Pragma("unroll") \
             pr += __shfl_xor_sync(FULL, pr, 16);                                   // over this warp's 16 columns
             if ((lane >> 3) == 0) s_pr[warp * CH + j] = pr;
             __syncthreads();
-        STEP_MARK(4);
             float prj = 0.f;
 #pragma unroll
             for (int w = 0; w < AB_WARPS; w++) prj += s_pr[w * CH + j];            // fixed order: repeatable
@@ -396,12 +387,7 @@ _Pragma("unroll") \
             if (first) { s_kinv[a] = s_kiold[tid]; s_o[a] = s_oold[tid]; }
         }
         __syncthreads();
-        STEP_MARK(5);
     }
-#ifdef SLOTSCAN_PHASE_TIMING
-    if (tid == 0)
-        for (int i = 0; i < 8; i++) atomicAdd(&g_phase_cycles[8 + i], (unsigned long long)_acc[i]);
-#endif
 #undef AB_ITEM
 #undef AB_ISSUE_LOADS
     if (lane == 0) { s_pr[warp] = dtemp_acc; s_pr[AB_WARPS + warp] = dfr_acc; }

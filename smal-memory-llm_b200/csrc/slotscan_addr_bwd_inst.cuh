@@ -42,7 +42,7 @@ static cudaError_t launch_gather(const slotscan_params& p, const void* q, const 
         next_write_kernel<<<p.B * p.H, 32, 0, st>>>(p, L.addr, L.tfirst, vend);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
-        dim3 grid((p.T + GC - 1) / GC, p.B * p.H);
+        dim3 grid(p.B * p.H, (p.T + GC - 1) / GC);
         addr_bwd_gather_kernel<DK, Tin><<<grid, GA_THREADS, 0, st>>>(p, (const Tin*)q, gate, fr, temp, L.addr, L.kold, L.oold,
                                                                       L.kiold, L.kfin, L.ofin, L.tfirst, vend, Dn, (Tin*)dq,
                                                                       dgate, dfr, part, part_stride);

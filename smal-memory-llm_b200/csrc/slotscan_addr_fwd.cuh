@@ -21,20 +21,6 @@
 
 namespace slotscan {
 
-// Optional instrumentation (-DSLOTSCAN_PHASE_TIMING, never in the shipped library): clock64 deltas summed per role and
-// phase, read back through slotscan_debug_phase_cycles_<dtype>.  Forward scan slots: 0 resolver work, 1 resolver
-// barrier wait, 2 / 3 column warps before / in the dots, 4 column barrier wait, 5 chunk duties, 8-11 inside the resolver
-// (bookkeeping, scores, argmax, load issue).  The marks perturb the schedule; use them for shares, not for totals.
-#ifdef SLOTSCAN_PHASE_TIMING
-static __device__ unsigned long long g_phase_cycles[16];
-#define STEP_T0() long long _st = clock64()
-#define STEP_MARK(I) do { long long _n = clock64(); _acc[I] += _n - _st; _st = _n; } while (0)
-#define SS_ULL(x) ((unsigned long long)(x))
-#else
-#define STEP_T0()
-#define STEP_MARK(I)
-#endif
-
 constexpr int CH = 8;                       // tokens staged per chunk
 constexpr int AF_CWARPS = 4;                // column warps: each owns a quarter of the key columns
 constexpr int AF_THREADS = 32 * (AF_CWARPS + 1);   // + warp 0, the resolver
@@ -338,9 +324,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         _Pragma("unroll") for (int s = 0; s < (NS); s++)                                                       \
             _Pragma("unroll") for (int w = 0; w < AF_CWARPS; w++)                                              \
                 if (w * CW < DK) pr[s][w] = part[(((BUF) * RPL + s) * AF_CWARPS + w) * 32 + lane];             \
-        STEP_MARK(11);                                                                                         \
         AF_FINISH_PREV(NS)                                                                                     \
-        STEP_MARK(8);                                                                                          \
         float bz = -INFINITY;                                                                                  \
         int bi = BIGI;                                                                                         \
         Rb = 0.f;                                                                                              \
@@ -358,12 +342,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             const float z = (OCCB ? (sc - cc.frv * (oc >= eps ? 1.f : 0.f)) : (sc - cc.frv * oc)) + 0.f;       \
             if (n <= lim && (oc >= eps || n == fe) && z > bz) { bz = z; bi = n; Rb = R; }   /* ascending n */  \
         }                                                                                                      \
-        STEP_MARK(9);                                                                                          \
         const unsigned key = (bi == BIGI) ? 0u : ord_key(bz);                                                  \
         const unsigned kmax = __reduce_max_sync(FULL, key);                                                    \
         am = (int)__reduce_min_sync(FULL, (unsigned)((key == kmax && bi != BIGI) ? bi : BIGI));                \
         am = min(am, lim);         /* no candidate compares greater (NaN scores): stay inside the rows */      \
-        STEP_MARK(10);                                                                                         \
         /* the owner lane's best row IS am (it holds the maximum), so its Rb is <K_am, k_t> */                 \
     }
     struct TokC { float tq, frv, g, x0, x1; double d0, d1, d2; };
@@ -387,9 +369,6 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     float Rb_prev = 0.f;
     TokC cc = {}, pc = {}, nc = {};                       // constants of the current, previous and next token
 
-#ifdef SLOTSCAN_PHASE_TIMING
-    long long _acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#endif
     // ---- prologue: stage chunk 0, its constants, the plain dots of token 0 ----
     if (warp >= 1) {
         AF_ISSUE_LOADS(0);
@@ -405,7 +384,6 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     if (wact) { AF_DOTS_SPLIT(4, 0, 0) }
     if (warp == 0) AF_LOAD_CONSTS(cc, 0);
     __syncthreads();
-    STEP_T0();
 
     // The two roles run separate loops (their register states never mix) and meet at one named barrier per token.
 #define AF_PHASE_BARRIER() asm volatile("bar.sync 1, %0;" ::"n"(AF_THREADS) : "memory")
@@ -431,9 +409,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             }
             am_prev = am; Rb_prev = Rb; pslot = sl;
             pc = cc; cc = nc;
-            STEP_MARK(0);
             AF_PHASE_BARRIER();
-            STEP_MARK(1);
             if (lim >= ncap) {                             // the next token may address a row this CTA does not hold
                 if (lane == 0) tfirst[(size_t)bh * N] = -1;
                 return;                                    // the column warps read the same limit and leave too
@@ -450,12 +426,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             const int jj = t & (C - 1);
             if (wact) {
                 if (t >= 1) { AF_WRITE_ROW((t - 1) & (RING - 1)) }
-                STEP_MARK(2);
                 if (t + 1 < T) {
                     const int limd = min(lim + 1, ncap - 1);      // token t can raise the candidate limit by one
                     AF_DOTS_DISPATCH(limd, (t + 1) & (RING - 1), (t + 1) & 1)
                 }
-                STEP_MARK(3);
             }
             // chunk duties, spread over the phases 1.. of the chunk
             const int tn = t - jj + C;                     // first token of the next chunk
@@ -474,9 +448,7 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             } else if (jj >= 2 && jj < 2 + C / 8 && tn < T) {
                 AF_TOKEN_CONSTS(tn & (RING - 1), jj - 2);
             }
-            STEP_MARK(5);
             AF_PHASE_BARRIER();
-            STEP_MARK(4);
             lim = s_cur[t & 1];
             if (lim >= ncap) return;
         }
@@ -495,13 +467,6 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
             kiold_out[ix] = s_kiold[sp];
         }
     }
-#ifdef SLOTSCAN_PHASE_TIMING
-    if (tid == 0) { atomicAdd(&g_phase_cycles[8], SS_ULL(_acc[8])); atomicAdd(&g_phase_cycles[9], SS_ULL(_acc[9]));
-                    atomicAdd(&g_phase_cycles[10], SS_ULL(_acc[10])); atomicAdd(&g_phase_cycles[11], SS_ULL(_acc[11])); }
-    if (tid == 0) { atomicAdd(&g_phase_cycles[0], SS_ULL(_acc[0])); atomicAdd(&g_phase_cycles[1], SS_ULL(_acc[1])); }
-    if (tid == 32) { atomicAdd(&g_phase_cycles[2], SS_ULL(_acc[2])); atomicAdd(&g_phase_cycles[3], SS_ULL(_acc[3]));
-                     atomicAdd(&g_phase_cycles[4], SS_ULL(_acc[4])); atomicAdd(&g_phase_cycles[5], SS_ULL(_acc[5])); }
-#endif
 #undef AF_DOTS
 #undef AF_DOTS_DISPATCH
 #undef AF_DOTS_SPLIT

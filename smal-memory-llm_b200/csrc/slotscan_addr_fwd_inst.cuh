@@ -54,14 +54,3 @@ void SS_CAT(attrs_addr_fwd_, SLOTSCAN_SUFFIX)(slotscan_kernel_attr* out, int cap
 
 }  // namespace slotscan
 
-#ifdef SLOTSCAN_PHASE_TIMING
-// debug builds only: read (and optionally clear) the cycle counters of the forward address scan
-extern "C" int SS_CAT(slotscan_debug_phase_cycles_, SLOTSCAN_SUFFIX)(unsigned long long* out16, int clear) {
-    cudaError_t e = cudaMemcpyFromSymbol(out16, slotscan::g_phase_cycles, 16 * sizeof(unsigned long long));
-    if (e == cudaSuccess && clear) {
-        unsigned long long z[16] = {0};
-        e = cudaMemcpyToSymbol(slotscan::g_phase_cycles, z, sizeof(z));
-    }
-    return (int)e;
-}
-#endif

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
     __shared__ float s_S[GA_WARPS][GATHER_ROWS];
     __shared__ float s_red[2][GA_WARPS];
     const int N = p.N, T = p.T, H = p.H;
-    const int c = blockIdx.x, bh = blockIdx.y, b = bh / H, h = bh % H;
+    const int bh = blockIdx.x, c = blockIdx.y, b = bh / H, h = bh % H;    // chunks on grid.y: T / 32 <= 65535
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (!gather_sequence(tfirst + (size_t)bh * N, N, T)) return;          // uniform per CTA
     const int nc = (T + GC - 1) / GC, t0 = c * GC, tc = min(GC, T - t0);

@@ -151,6 +151,9 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (addr_fwd_smem_bytes(p->N, p->DK, 4) + 1024 > SMEM_CAP || addr_bwd_smem_bytes(p->N, p->DK) + 1024 > SMEM_CAP)
         return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
+    /* token chunks ride on grid.y (<= 65535) and the partial-sum table is indexed with ints */
+    if (((long long)p->T + GATHER_CHUNK - 1) / GATHER_CHUNK > 65535) return SLOTSCAN_E_SHAPE;
+    if ((long long)p->B * p->H * (((long long)p->T + GATHER_CHUNK - 1) / GATHER_CHUNK + 1) > 2147483647LL / 2) return SLOTSCAN_E_SHAPE;
     if (p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
     if (p->snap_dtype != SLOTSCAN_F32 && p->snap_dtype != SLOTSCAN_BF16) return SLOTSCAN_E_DTYPE;
     return SLOTSCAN_OK;
@@ -283,6 +286,12 @@ extern "C" int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= MAX_DEVICES) return SLOTSCAN_E_SHAPE;
+    // The array handed to the kernels is the CURRENT device's: the inputs (and so the stream) must live there too.
+    if (k != nullptr) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, k) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device != dev)
+            return SLOTSCAN_E_MODE;
+    }
     void* scratch;
     {
         std::lock_guard<std::mutex> l(g_fixed_scratch_mu);

@@ -4,8 +4,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# SLOTSCAN_LIB points at another build of the same library (e.g. one compiled with extra instrumentation)
-LIB_PATH = os.environ.get("SLOTSCAN_LIB") or os.path.join(_HERE, "libslotscan.so")
+LIB_PATH = os.path.join(_HERE, "libslotscan.so")
 
 F32, BF16 = 0, 1
 

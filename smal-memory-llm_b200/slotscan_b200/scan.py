@@ -24,6 +24,14 @@ def _as_f32(x):
     return x.contiguous().to(torch.float32)
 
 
+def _token_streams(k, v, q):
+    """The dtype policy of the token streams: bf16 kernels only when k, v and q (if given) are ALL bfloat16; anything
+    else is cast to contiguous float32 as the reference does (slotkern_cuda.py:488-489)."""
+    bf = k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and (q is None or q.dtype == torch.bfloat16)
+    conv = (lambda x: x.contiguous()) if bf else _as_f32
+    return conv(k), conv(v), (None if q is None else conv(q))
+
+
 def kv_scan_g(k, v, gate, fr, N, temp, G=16, hard=False, hard_gate=False, eps=1e-4, detach_addr=False, q=None, nw=None,
               nwb=None, occ_bin=False, out_dtype=torch.float32):
     if not k.is_cuda:
@@ -35,10 +43,7 @@ def kv_scan_g(k, v, gate, fr, N, temp, G=16, hard=False, hard_gate=False, eps=1e
         raise ValueError("out_dtype must be float32 or bfloat16")
     B, T, H, DK = k.shape
     assert v.shape[:3] == (B, T, H) and gate.shape == (B, T, H), (k.shape, v.shape, gate.shape)
-    bf = k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and (q is None or q.dtype == torch.bfloat16)
-    conv = (lambda x: x.contiguous()) if bf else _as_f32
-    k_, v_ = conv(k), conv(v)
-    q_ = None if q is None else conv(q)
+    k_, v_, q_ = _token_streams(k, v, q)
     g_ = _as_f32(gate)
     if torch.is_tensor(fr) and fr.dim() == 3:
         assert fr.shape == gate.shape, (fr.shape, gate.shape)            # slotkern_cuda.py:493
@@ -68,13 +73,14 @@ def scan_with_log(k, v, gate, fr, N, temp, G=16, hard_gate=False, eps=1e-4, q=No
     """Forward only, returning the snapshots AND the log (addresses, undo rows, final state): what a caller that
     inspects addresses or streams a long context needs.  Keys: kbuf, vbuf, addr, oold, kold, vold, kfin, vfin, ofin,
     tfirst (include/slotscan.h: slotscan_log)."""
-    bf = k.dtype == torch.bfloat16
-    conv = (lambda x: x.contiguous()) if bf else _as_f32
+    if not k.is_cuda:
+        raise RuntimeError("slotscan_b200.scan_with_log: CUDA tensors only (no CPU path in this package)")
+    k_, v_, q_ = _token_streams(k, v, q)
     fr_ = _as_f32(fr) if (torch.is_tensor(fr) and fr.dim() == 3) else \
         torch.as_tensor(fr, dtype=torch.float32, device=k.device).reshape(1)
     temp_ = torch.as_tensor(temp, dtype=torch.float32, device=k.device).reshape(1)
     with torch.no_grad():
-        out = ops.hard_fwd(conv(k), None if q is None else conv(q), conv(v), _as_f32(gate), fr_, temp_, int(N), int(G),
+        out = ops.hard_fwd(k_, q_, v_, _as_f32(gate), fr_, temp_, int(N), int(G),
                            bool(hard_gate), float(eps), bool(occ_bin), out_dtype == torch.bfloat16)
     names = ("kbuf", "vbuf", "addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")
     return dict(zip(names, out))

@@ -1,11 +1,11 @@
 """Generates the golden fixtures of this directory by RUNNING THE REFERENCE's own torch code on CPU.
 
-Needs the reference checkout (its location: $SLOTSCAN_REFERENCE, else the default in REF below); it imports, unmodified,
+Needs the reference checkout, its location given in $SLOTSCAN_REFERENCE; it imports, unmodified,
     gqa25/slotkern_kv.py   _ref_scan_kv_impl / ref_scan_kv     (the scan; gradients by torch autograd)
     gqa25/memlm_sh.py      SharedMixer._read, _fq, _quantize_mem (the read and the storage quantiser)
 and writes one compressed .npz per case.  The fixtures travel with the repository; the reference does not.
 
-    python tests/golden/make_golden.py            # rewrites tests/golden/*.npz
+    SLOTSCAN_REFERENCE=<reference checkout> python tests/golden/make_golden.py      # rewrites tests/golden/*.npz
 
 Case list follows the reference's own test protocols: gqa25/test_kvg.py:6-12 (soft, attached/detached, T % G != 0,
 separate query, G = 1), gqa25/test_frtok.py:13-36 (clustered keys, per-token fr, fr/temp in [0.2, 1.5]),
@@ -20,7 +20,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("SLOTSCAN_REFERENCE", "/root/reference")
+REF = os.environ.get("SLOTSCAN_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "gqa25")):
+    sys.exit("make_golden.py: set SLOTSCAN_REFERENCE to the reference checkout (the directory that holds gqa25/)")
 sys.path.insert(0, os.path.join(REF, "gqa25"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 

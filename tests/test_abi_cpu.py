@@ -37,6 +37,15 @@ def test_argument_validation_needs_no_gpu():
         p = _lib.Params(2, 16, 3, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
         setattr(p, field, val)
         assert L.slotscan_check(ctypes.byref(p)) < 0, field
+    # sizes whose launch grid or partial-sum table would overflow are refused before anything is launched
+    for B, T, H in ((70000, 8, 1), (1, 32 * 65536, 1), (400000, 40000, 4)):
+        p = _lib.Params(B, T, H, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
+        assert L.slotscan_check(ctypes.byref(p)) in (0, -2)
+    big = _lib.Params(1, 32 * 65536 + 1, 1, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
+    assert L.slotscan_check(ctypes.byref(big)) == -2                   # token chunks ride on grid.y
+    big = _lib.Params(400000, 40000, 4, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4)
+    assert L.slotscan_check(ctypes.byref(big)) == -2                   # partial-sum table beyond int range
+    assert L.slotscan_check(ctypes.byref(_lib.Params(70000, 8, 1, 12, 16, 16, 8, 0, 1, 1, 0, 0, 1e-4))) == 0   # B*H > 65535 is fine
     assert L.slotscan_check(None) == -1
     assert L.slotscan_hard_bwd_scratch_bytes(ctypes.byref(ok)) >= 4 * 2 * 3 * 16 * 12
     # NULL pointers are refused before any launch
@@ -55,6 +64,27 @@ def test_python_host_mirrors_reference_signatures():
     ps = list(inspect.signature(S.scan_kv).parameters)                  # gqa25/slotkern_kv.py:29
     assert ps == ["k", "v", "gate", "fr", "N", "temp", "G", "hard", "hard_gate", "eps", "detach_addr", "q"]
     assert inspect.signature(S.scan_kv).parameters["G"].default == 1
+
+
+def test_token_stream_dtype_policy():
+    """bf16 kernels only when k, v and q are all bfloat16; any mix is cast to float32 (slotkern_cuda.py:488-489) --
+    in kv_scan_g and in scan_with_log alike."""
+    from slotscan_b200 import scan
+    kb, vb = torch.zeros(1, 2, 1, 8, dtype=torch.bfloat16), torch.zeros(1, 2, 1, 8, dtype=torch.bfloat16)
+    kf = kb.float()
+    assert [t.dtype for t in scan._token_streams(kb, vb, kb)] == [torch.bfloat16] * 3
+    assert scan._token_streams(kb, vb, None)[2] is None and scan._token_streams(kb, vb, None)[0].dtype == torch.bfloat16
+    for k, v, q in ((kb, kf, kb), (kb, vb, kf), (kf, vb, None), (kb.half(), vb, kb)):
+        out = scan._token_streams(k, v, q)
+        assert all(t is None or t.dtype == torch.float32 for t in out), [None if t is None else t.dtype for t in out]
+    src = inspect.getsource(scan.scan_with_log)
+    assert "_token_streams" in src
+
+
+def test_drop_in_kernel_attrs_signature():
+    import slotkern_cuda
+    ps = inspect.signature(slotkern_cuda.kernel_attrs).parameters           # gqa25/slotkern_cuda.py:467
+    assert list(ps) == ["N", "D", "occb", "frt", "eps"]
 
 
 def test_no_cpu_fallback():

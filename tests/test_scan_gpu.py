@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.scan_cases import address_report, allclose_report, make_inputs, rel_to_max
+from tests.scan_cases import address_report, allclose_report, bf16_band_report, make_inputs, rel_to_max
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -49,6 +49,22 @@ def run_log(inp, N, G, hard_gate, occ_bin, dtype=torch.float32):
     return {n: x.cpu().numpy() for n, x in lg.items()}
 
 
+def check_addresses(name, addr, ref, B, H):
+    """Addresses against the oracle: identical wherever the oracle's top-1 / top-2 margin exceeds 1e-4; a sequence
+    whose smallest margin over all its tokens exceeds 1e-3 must not differ at all.  Prints the counts (pytest -s / -rP
+    shows them) and returns the mask of sequences whose values can be compared."""
+    ok, nflip, nbad, keep = address_report(addr, ref["addr"], ref["margin"])
+    clear = ref["margin"].min(axis=1) > 1e-3                            # (B, H): no near-tie anywhere in the sequence
+    near = int((ref["margin"] < 1e-4).sum())
+    print("%s: sequences with an address flip %d / %d (beyond the 1e-4 margin: %d); oracle near-ties (< 1e-4): %d tokens; "
+          "sequences with every margin > 1e-3: %d, flips among them: %d"
+          % (name, nflip, B * H, nbad, near, int(clear.sum()), int((~keep[clear]).sum())))
+    assert ok, "an address differs where the oracle's margin exceeds 1e-4"
+    assert keep[clear].all(), "an address flipped in a sequence whose smallest margin exceeds 1e-3"
+    assert keep.mean() >= 0.75, "too many near-tie flips to judge values"
+    return keep
+
+
 HARD_DETACHED = sorted(p for p in glob.glob(os.path.join(GOLDEN, "scan_hard_detached*.npz")) +
                        glob.glob(os.path.join(GOLDEN, "scan_hard_bench*.npz")))
 
@@ -73,6 +89,10 @@ CASES = [  # name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq 
     ("sh25_main_clustered", "clustered", 1, 512, 6, 192, 128, 128, 8, False, True, True, True),
     ("sh25_main_fill", "fill", 1, 768, 6, 192, 128, 128, 8, False, True, True, True),
     ("t1000_d64", "gates01", 1, 1000, 4, 192, 64, 64, 8, False, True, True, True),
+    # ~55 candidate rows: first-pass forward scan (64 rows resident), resident-state address backward
+    ("gates01_55rows", "gates01:3", 1, 600, 4, 192, 128, 128, 8, False, True, True, True),
+    # ~110 candidate rows: the forward scan's full-size second pass
+    ("gates01_110rows", "gates01:4", 1, 600, 4, 192, 128, 128, 8, False, True, True, True),
     ("n40_g16_scalar_fr", "gates01", 1, 300, 4, 40, 64, 64, 16, False, False, False, False),
     ("n40_g7_hardgate", "gates01", 1, 300, 4, 40, 64, 64, 7, True, True, False, True),
     ("n50_d128_no_occbin", "gates01", 1, 300, 3, 50, 128, 128, 8, False, False, False, True),
@@ -89,10 +109,7 @@ def test_fp32_mode_vs_float64_oracle(case):
     kw = dict(N=N, temp=inp["temp"], G=G, hard=True, hard_gate=hard_gate, q=inp["q"], occ_bin=occ_bin)
     ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dtype=np.float64, **kw)
     lg = run_log(inp, N, G, hard_gate, occ_bin)
-    ok, nflip, nbad, keep = address_report(lg["addr"], ref["addr"], ref["margin"])
-    print("%s: sequences with an address flip %d / %d, beyond the 1e-4 margin %d" % (name, nflip, B * H, nbad))
-    assert ok, "an address differs where the oracle's margin exceeds 1e-4"
-    assert keep.mean() >= 0.75, "too many near-tie flips to judge values"
+    keep = check_addresses(name, lg["addr"], ref, B, H)
     gen = torch.Generator().manual_seed(7)
     wk = torch.randn(ref["kbuf"].shape, generator=gen).numpy()
     wv = torch.randn(ref["vbuf"].shape, generator=gen).numpy()
@@ -116,22 +133,12 @@ def test_fp32_mode_vs_float64_oracle(case):
             assert rel_to_max(out["dfr"], gr["dfr"]) < 1e-4
 
 
-BF16_CASES = [c for c in CASES if c[0] in ("sh25_main", "sh25_enc", "sh25_main_clustered", "t1000_d64", "dk_ne_dv")]
-
-
-def _bf16(x):
-    return torch.as_tensor(np.asarray(x, np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
-
-
-def _bf16_storage_close(out, ref, scale=1.0):
-    """A bf16-typed output against the oracle: bf16 keeps 8 significant bits (unit round-off 2^-8 = 3.9e-3), so the
-    stored number cannot sit within rtol 2e-3 of the exact one.  What can be asked is that it is the oracle's value
-    in the same storage format: equal to the bf16-rounded oracle value up to one bf16 ulp (float32 round-off can
-    tip a value across a rounding boundary), plus the absolute 2e-3 (of the tensor's scale)."""
-    r = _bf16(ref)
-    ulp = np.abs(r) * 2.0 ** -7
-    err = np.abs(np.asarray(out, np.float64) - r) - (ulp + 2e-3 * scale)
-    return bool((err <= 0).all()), float(err.max())
+BF16_CASES = [c for c in CASES if c[0] in ("sh25_main", "sh25_enc", "sh25_main_clustered", "sh25_main_fill", "t1000_d64",
+                                           "gates01_55rows", "gates01_110rows", "dk_ne_dv")]
+# Largest share of elements that may differ from the bf16-rounded oracle value (see bf16_band_report): snapshots are
+# float32 state rounded once, so only values within float32 round-off of a rounding boundary differ; gradients are
+# float32 sums of many terms rounded once.
+SNAP_SHARE, GRAD_SHARE = 2e-3, 2e-2
 
 
 @pytest.mark.parametrize("case", BF16_CASES, ids=[c[0] for c in BF16_CASES])
@@ -139,7 +146,8 @@ def test_bf16_storage_mode(case):
     """bf16 token streams, bf16 snapshots and bf16 upstream gradients, float32 state and accumulation.  The oracle
     gets the same bf16-rounded inputs, so what is compared is the arithmetic.  float32-typed results (final slot
     state, dgate, dfr, dtemp) at rtol = atol = 2e-3; bf16-typed results (snapshots, dk, dq, dv) against the oracle
-    value in the same storage format (see _bf16_storage_close)."""
+    value in the same storage format (scan_cases.bf16_band_report): inside the one-ulp band AND bit-identical to the
+    rounded oracle value in all but a small share of the elements."""
     name, dist, B, T, H, N, DK, DV, G, hard_gate, occ_bin, frtok, sepq = case
     inp = make_inputs(dist, B, T, H, DK, DV, seed=300 + len(name), frtok=frtok, sepq=sepq)
     for n in ("k", "q", "v"):
@@ -148,9 +156,7 @@ def test_bf16_storage_mode(case):
     kw = dict(N=N, temp=inp["temp"], G=G, hard=True, hard_gate=hard_gate, q=inp["q"], occ_bin=occ_bin)
     ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dtype=np.float64, **kw)
     lg = run_log(inp, N, G, hard_gate, occ_bin, dtype=torch.bfloat16)
-    ok, nflip, nbad, keep = address_report(lg["addr"], ref["addr"], ref["margin"])
-    print("%s (bf16): sequences with an address flip %d / %d, beyond the margin %d" % (name, nflip, B * H, nbad))
-    assert ok and keep.mean() >= 0.75
+    keep = check_addresses(name + " (bf16)", lg["addr"], ref, B, H)
     gen = torch.Generator().manual_seed(7)
     wk = torch.randn(ref["kbuf"].shape, generator=gen).to(torch.bfloat16).float().numpy()
     wv = torch.randn(ref["vbuf"].shape, generator=gen).to(torch.bfloat16).float().numpy()
@@ -162,13 +168,17 @@ def test_bf16_storage_mode(case):
         okc, worst = allclose_report(lg[n].reshape(ref[n].shape)[keep], ref[n][keep], 2e-3, 2e-3)
         assert okc, (n, worst)
     for n, m in (("kbuf", m5), ("vbuf", m5)):
-        okc, worst = _bf16_storage_close(out[n] * m, ref[n] * m)
+        okc, worst, share = bf16_band_report(out[n] * m, ref[n] * m)
+        print("%s (bf16) %s: share of elements not equal to the bf16-rounded oracle value %.2e" % (name, n, share))
         assert okc, (n, worst)
+        assert share <= SNAP_SHARE, (n, share)
     for n, m in (("dk", m4), ("dv", m4), ("dq", m4)):
         if n in out:
             scale = max(np.abs(gr[n]).max(), 1e-30)
-            okc, worst = _bf16_storage_close(out[n] * m, gr[n] * m, scale)
+            okc, worst, share = bf16_band_report(out[n] * m, gr[n] * m, scale)
+            print("%s (bf16) %s: share of elements not equal to the bf16-rounded oracle value %.2e" % (name, n, share))
             assert okc, (n, worst / scale)
+            assert share <= GRAD_SHARE, (n, share)
     for n in ("dgate", "dfr"):
         if out[n].shape == gr[n].shape:
             scale = max(np.abs(gr[n]).max(), 1e-30)          # gradients are compared relative to their own max
