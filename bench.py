@@ -2,19 +2,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W]            this build's CUDA path
     python bench.py --impl reference [...]                          the CPU implementation timed on the host cores
-    torchrun ... bench.py --gpus N ...                              one rank per GPU, batch-sharded (weak scaling)
+    torchrun ... bench.py --gpus N ...                              one rank per GPU, the batch sharded over the ranks
 
-One step = one forward + backward pass of the scan over one batch (B=64 sequences x T=1024 tokens x 6 heads per GPU,
-N=192 slots, dk=dv=128, snapshot stride 8, bf16 token streams and snapshots, float32 state and accumulation), on
-seeded synthetic inputs with the benchmark's distributions.  Prints ONE JSON line:
+One step = one forward + backward pass of the scan over one batch of T=1024-token sequences x 6 heads (N=192 slots,
+dk=dv=128, snapshot stride 8, bf16 token streams and snapshots, float32 state and accumulation), on seeded synthetic
+inputs with the benchmark's distributions.  The global batch is 64 sequences at every GPU count (strong scaling:
+64 / N sequences per rank, no data-path collective); `--scaling weak` keeps 64 sequences per GPU instead.
+Prints ONE JSON line:
   value      tokens/s, whole job, inputs resident in HBM, device-timed (CUDA events, max over ranks)
   e2e        the same through the public Python API with HOST (pinned) inputs: H2D of k,q,v,gate,fr and D2H of every
              input gradient inside the timed region
-  roofline   the dominant kernel's algorithmic bytes / its event-timed duration against the measured HBM peak
+  roofline   the dominant kernel's algorithmic bytes / its event-timed duration against the measured HBM peak;
+             .step the same for the whole step, .touched_* with the bytes the kernels are obliged to move on THESE
+             inputs (snapshot-gradient rows of slots that never were candidates reach no input and are skipped),
+             .fill the step on inputs that use every slot
+  extra      one GPU only: the writer epilogue and one reader layer's cosine read over the snapshots of the same scan
   cpu_baseline  the CPU oracle (C, OpenMP) on a bounded sample of the same workload, on this box's host cores
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -126,8 +133,18 @@ def max_over_ranks(values, device):
 
 
 def whole_job_tokens_per_s(B_per_rank, T, world, steps, ms):
-    """Weak scaling: every rank scans its own B_per_rank sequences; the job's throughput counts all of them."""
+    """Every rank scans its own B_per_rank sequences; the job's throughput counts all of them."""
     return B_per_rank * T * world * steps / (ms * 1e-3)
+
+
+def shard_of_batch(global_B, world, rank, scaling):
+    """(first sequence, number of sequences) of this rank.  strong: the global batch is split evenly (the remainder
+    goes to the first ranks); weak: every rank holds `global_B` sequences of its own."""
+    if scaling == "weak" or world == 1:
+        return rank * global_B, global_B
+    base, rem = divmod(global_B, world)
+    n = base + (1 if rank < rem else 0)
+    return rank * base + min(rank, rem), n
 
 
 def make_host_inputs(B, T, H, DK, DV, seed, dist="bench"):
@@ -136,19 +153,30 @@ def make_host_inputs(B, T, H, DK, DV, seed, dist="bench"):
 
 
 # ------------------------------------------------------------------------------------------------------------------
-def cpu_leg(steps, warmup, sample_B=2, threads=None, budget_s=90.0):
+def host_threads():
+    """All host cores the process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its children)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_sample_batch(threads, H):
+    """Sequences of the CPU sample: the oracle runs one (sequence, head) scan per OpenMP task, so the sample holds at
+    least two tasks per core (dynamic schedule) -- every core has work for the whole step."""
+    return max(2, math.ceil(2 * threads / H))
+
+
+def cpu_leg(steps, warmup, threads=None, budget_s=60.0):
     """The CPU implementation of the same path: the C oracle (float32, OpenMP over (sequence, head)), forward + backward,
-    on a bounded sample: `sample_B` sequences of the full T / H / N / D."""
+    on a bounded sample: `sample_B` sequences of the full T / H / N / D, every host core busy."""
     import numpy as np
     from oracle import oracle as O
-    # all host cores the process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1 for its children)
-    if not threads:
-        try:
-            threads = len(os.sched_getaffinity(0))
-        except AttributeError:
-            threads = os.cpu_count() or 1
+    threads = threads or host_threads()
+    flags = O.use_timed_build()
     O.set_threads(threads)
     s = SHAPE
+    sample_B = min(cpu_sample_batch(threads, s["H"]), s["B"])
     inp = make_host_inputs(sample_B, s["T"], s["H"], s["DK"], s["DV"], seed=0)
     kw = dict(N=s["N"], temp=16.0, G=s["G"], hard=True, q=inp["q"], occ_bin=True, dtype=np.float32)
     NB = (s["T"] + s["G"] - 1) // s["G"]
@@ -170,35 +198,143 @@ def cpu_leg(steps, warmup, sample_B=2, threads=None, budget_s=90.0):
         if time.perf_counter() - t0 > budget_s:          # keep the whole run within minutes on a slow host
             break
     dt = time.perf_counter() - t0
-    steps = done
-    toks = sample_B * s["T"] * steps
-    return dict(value=toks / dt, ms_per_step=1e3 * dt / steps, cores=O.threads(), steps=steps,
-                sample="%d of %d sequences, full T=%d H=%d N=%d D=%d G=%d, float32, fwd+bwd" %
-                       (sample_B, s["B"], s["T"], s["H"], s["N"], s["DK"], s["G"]))
+    toks = sample_B * s["T"] * done
+    out = dict(value=toks / dt, ms_per_step=1e3 * dt / done, cores=O.threads(), steps=done, sample_B=sample_B, build=flags,
+               sample="%d of %d sequences (%d OpenMP tasks on %d threads), full T=%d H=%d N=%d D=%d G=%d, float32, fwd+bwd"
+                      % (sample_B, s["B"], sample_B * s["H"], O.threads(), s["T"], s["H"], s["N"], s["DK"], s["G"]))
+    # config 0 as specified: B=2, T=256, forward only, float32 (scan -> epilogue -> read), the whole case, not a sample
+    c0 = make_host_inputs(2, 256, s["H"], s["DK"], s["DV"], seed=0)
+    rq = np.random.default_rng(1)
+    qr = rq.standard_normal((2, 256, s["H"], 1, s["DK"])).astype(np.float32)
+    sharp = (np.log1p(np.exp(rq.standard_normal((2, 256, s["H"], 1)))) + 1).astype(np.float32)
+
+    def cfg0():
+        r = O.scan_fwd(c0["k"], c0["v"], c0["gate"], c0["fr"], N=s["N"], temp=16.0, G=s["G"], hard=True, q=c0["q"],
+                       occ_bin=True, dtype=np.float32)
+        ki, va = O.epilogue(r["kbuf"], dtype=np.float32)
+        O.read_fwd(qr, sharp, r["kbuf"], r["vbuf"], ki, va, s["G"], dtype=np.float32)
+
+    cfg0()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        cfg0()
+    out["config0"] = {"tokens_per_s": 3 * 2 * 256 / (time.perf_counter() - t0), "workload": "config0: B=2 T=256 H=6 N=192 "
+                      "D=128 G=8, float32, forward scan + epilogue + read, whole case (12 OpenMP tasks)"}
+    return out
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    warmup = min(args.warmup, 1)
-    r = cpu_leg(max(1, args.steps), warmup)
-    steps = r["steps"]
+    r = cpu_leg(max(1, args.steps), args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "config1: slot-scan fwd+bwd, B=64 T=1024 H=6 N=192 dk=dv=128 G=8 (CPU sample: see cpu_baseline.sample)",
-                       "l2": "n/a (host)"},
-            "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                       "global_batch": SHAPE["B"], "seq_len": SHAPE["T"], "l2": "n/a (host)"},
+            "cpu_baseline": {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"],
+                             "build": r["build"], "config0": r["config0"]},
             "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     emit(line)
 
 
 # ------------------------------------------------------------------------------------------------------------------
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under profiles/
+# (each taken at B = 8 sequences; traffic is proportional to the batch, so a launch over B sequences moves B / 8 of it).
+# A kernel that changed since its capture is taken out of this table until it is captured again.
+NCU_TRAFFIC_B8 = {
+    "replay_rows_k": (13.03e6 + 274.17e6, "profiles/replay_rows_128_bf16_small_case.md"),
+    "replay_rows_v": (13.03e6 + 274.17e6, "profiles/replay_rows_128_bf16_small_case.md"),
+    "addr_fwd": (25.6e6, "profiles/addr_fwd_128_bf16_small_case.md"),
+    "rows_bwd_k": (107.8e6 + 16.7e6, "profiles/rows_bwd_128_bf16_small_case.md"),
+    "addr_bwd": (52.34e6 + 0.96e6, "profiles/addr_bwd_gather_128_bf16_small_case.md"),
+}
+
+
+class ScanJob:
+    """One rank's share of the workload: inputs on the host (pinned) and on the device, upstream gradients, the step."""
+
+    def __init__(self, S, dev, B, T, H, N, DK, DV, G, seed, dist):
+        import torch
+        self.S, self.dev, self.dims = S, dev, (B, T, H, N, DK, DV, G)
+        NB = (T + G - 1) // G
+        inp = make_host_inputs(B, T, H, DK, DV, seed=seed, dist=dist)
+        bf = torch.bfloat16
+        self.host = {n: inp[n].to(bf).contiguous().pin_memory() for n in ("k", "q", "v")}
+        self.host.update({n: inp[n].float().contiguous().pin_memory() for n in ("gate", "fr")})
+        self.devin = {n: t.to(dev) for n, t in self.host.items()}
+        self.temp = torch.tensor([16.0], device=dev)
+        gen = torch.Generator(device=dev).manual_seed(7 + seed)
+        self.dkb = torch.randn(B, NB, H, N, DK, device=dev, dtype=bf, generator=gen)
+        self.dvb = torch.randn(B, NB, H, N, DV, device=dev, dtype=bf, generator=gen)
+
+    def scan(self, x, sl=slice(None)):
+        import torch
+        B, T, H, N, DK, DV, G = self.dims
+        k, q, v = (x[n].detach().requires_grad_() for n in ("k", "q", "v"))
+        g, fr = x["gate"].detach().requires_grad_(), x["fr"].detach().requires_grad_()
+        tp = self.temp.detach().requires_grad_()
+        kb, vb = self.S.kv_scan_g(k, v, g, fr, N, tp, G=G, hard=True, hard_gate=False, detach_addr=True, q=q, occ_bin=True,
+                                  out_dtype=torch.bfloat16)
+        torch.autograd.backward([kb, vb], [self.dkb[sl], self.dvb[sl]])
+        return k.grad, q.grad, v.grad, g.grad, fr.grad, tp.grad
+
+    def step(self):
+        return self.scan(self.devin)
+
+    def touched_bytes(self):
+        """Bytes the kernels are obliged to move on these inputs: as the algorithmic figure, but of the snapshot
+        gradients only the rows that can reach an input -- row n from the block in which it first became a candidate
+        (tfirst of the forward log).  The forward has to write every snapshot row, zeros included."""
+        import torch
+        B, T, H, N, DK, DV, G = self.dims
+        NB = (T + G - 1) // G
+        x = self.devin
+        with torch.no_grad():
+            lg = self.S.scan_with_log(x["k"], x["v"], x["gate"], x["fr"], N, 16.0, G=G, q=x["q"], occ_bin=True,
+                                      out_dtype=torch.bfloat16)
+        tf = lg["tfirst"].long()                                         # (B*H, N): first token at which row n is a candidate
+        blocks = torch.where(tf < T, NB - tf // G, torch.zeros_like(tf))  # snapshots taken at or after the block that holds tfirst
+        rows_read = int(blocks.sum())
+        used = float((tf < T).float().sum(1).mean())
+        ab = algorithmic_bytes_per_token_head(N, DK, DV, G, 2, 2)
+        tok_heads = B * T * H
+        full = ab["total"] * tok_heads
+        snap_grad_full = ab["snap"] * tok_heads
+        snap_grad_touched = rows_read * (DK + DV) * 2
+        del lg
+        return dict(step=full - snap_grad_full + snap_grad_touched, rows_bwd=snap_grad_touched + 2 * (DK + DV) * 2 * tok_heads,
+                    slots_used_mean=used)
+
+
+def timed(job, steps, barrier, clock_index=None):
+    """`steps` calls of job.step() between two events on the current stream, barrier + synchronize on both sides;
+    per-kernel event times from the library."""
+    import torch
+    from slotscan_b200 import _lib
+    _lib.profile_enable(True)
+    _lib.profile_read()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clk = ClockSampler(clock_index) if clock_index is not None else None
+    if clk:
+        clk.__enter__()
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        job.step()
+    e1.record()
+    barrier()
+    if clk:
+        clk.__exit__()
+    prof = _lib.profile_read()
+    _lib.profile_enable(False)
+    return e0.elapsed_time(e1), prof, (clk.summary() if clk else None)
+
+
 def run_gpu(args, rank, local_rank, world):
     import torch
     import slotscan_b200 as S
-    from slotscan_b200 import _lib
 
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: this build has no CPU path for the scan")
@@ -214,26 +350,14 @@ def run_gpu(args, rank, local_rank, world):
         s["B"] = args.B
     if args.T:
         s["T"] = args.T
-    B, T, H, N, DK, DV, G = (s[n] for n in ("B", "T", "H", "N", "DK", "DV", "G"))
-    NB = (T + G - 1) // G
-    inp = make_host_inputs(B, T, H, DK, DV, seed=rank, dist=args.dist)       # each rank its own shard of the batch
-    bf = torch.bfloat16
-    host = {n: inp[n].to(bf).contiguous().pin_memory() for n in ("k", "q", "v")}
-    host.update({n: inp[n].float().contiguous().pin_memory() for n in ("gate", "fr")})
-    devin = {n: t.to(dev) for n, t in host.items()}
-    temp = torch.tensor([16.0], device=dev)
-    gen = torch.Generator(device=dev).manual_seed(7 + rank)
-    dkb = torch.randn(B, NB, H, N, DK, device=dev, dtype=bf, generator=gen)
-    dvb = torch.randn(B, NB, H, N, DV, device=dev, dtype=bf, generator=gen)
-
-    def step(x):
-        k, q, v = (x[n].detach().requires_grad_() for n in ("k", "q", "v"))
-        g, fr = x["gate"].detach().requires_grad_(), x["fr"].detach().requires_grad_()
-        tp = temp.detach().requires_grad_()
-        kb, vb = S.kv_scan_g(k, v, g, fr, N, tp, G=G, hard=True, hard_gate=False, detach_addr=True, q=q, occ_bin=True,
-                             out_dtype=bf)
-        torch.autograd.backward([kb, vb], [dkb, dvb])
-        return k.grad, q.grad, v.grad, g.grad, fr.grad, tp.grad
+    GB, T, H, N, DK, DV, G = (s[n] for n in ("B", "T", "H", "N", "DK", "DV", "G"))
+    scaling = args.scaling
+    first, B = shard_of_batch(GB, world, rank, scaling)
+    global_B = GB * world if scaling == "weak" else GB
+    if B < 1:
+        raise RuntimeError("fewer sequences than ranks")
+    # every rank draws its own sequences (seeded by rank): the scan never looks across sequences
+    job = ScanJob(S, dev, B, T, H, N, DK, DV, G, seed=rank, dist=args.dist)
 
     def barrier():
         if dist_on:
@@ -241,29 +365,21 @@ def run_gpu(args, rank, local_rank, world):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step(devin)
+        job.step()
     barrier()
     # ---- device-timed leg: inputs resident in HBM ----
-    _lib.profile_enable(True)
-    _lib.profile_read()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clk:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step(devin)
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
-    prof = _lib.profile_read()
-    _lib.profile_enable(False)
+    ms, prof, clocks = timed(job, args.steps, barrier, clock_index=local_rank)
+
     # ---- end-to-end leg: host inputs in, input gradients out, every step ----
     # The batch goes through in P chunks on P streams, so that the host->device copy of one chunk, the kernels of
     # another and the device->host copy of a third overlap (sequences are independent; the copies use both directions
     # of the link).  All through the public call, kv_scan_g, as a user would write it.
-    P = args.e2e_chunks if B % args.e2e_chunks == 0 and B >= 2 * args.e2e_chunks else 1
+    P = args.e2e_chunks
+    while P > 1 and (B % P or B < 2 * P):
+        P //= 2
     bs = B // P
     streams = [torch.cuda.Stream(device=dev) for _ in range(P)]
+    host = job.host
     hout = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (host["k"], host["q"], host["v"], host["gate"], host["fr"])]
     htemp = torch.empty(P, dtype=torch.float32).pin_memory()
 
@@ -276,15 +392,10 @@ def run_gpu(args, rank, local_rank, world):
             st.wait_event(start)
             with torch.cuda.stream(st):
                 x = {n: t[sl].to(dev, non_blocking=True) for n, t in host.items()}
-                k, q, v = (x[n].requires_grad_() for n in ("k", "q", "v"))
-                g, fr = x["gate"].requires_grad_(), x["fr"].requires_grad_()
-                tp = temp.detach().requires_grad_()
-                kb, vb = S.kv_scan_g(k, v, g, fr, N, tp, G=G, hard=True, hard_gate=False, detach_addr=True, q=q,
-                                     occ_bin=True, out_dtype=bf)
-                torch.autograd.backward([kb, vb], [dkb[sl], dvb[sl]])
-                for h_, g_ in zip(hout, (k.grad, q.grad, v.grad, g.grad, fr.grad)):
+                grads = job.scan(x, sl)
+                for h_, g_ in zip(hout, grads[:5]):
                     h_[sl].copy_(g_, non_blocking=True)
-                htemp[i:i + 1].copy_(tp.grad, non_blocking=True)
+                htemp[i:i + 1].copy_(grads[5], non_blocking=True)
         for st in streams:
             cur.wait_stream(st)
         cur.synchronize()                                  # the caller holds the gradients on the host
@@ -300,9 +411,46 @@ def run_gpu(args, rank, local_rank, world):
     ms_e2e = f0.elapsed_time(f1)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = sum(t.numel() * t.element_size() for t in hout) + 4 * P
-    ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev)
+
+    # copies alone, both directions at once on two streams: the link's share of the end-to-end step on this host
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    dsrc = {n: torch.empty_like(t) for n, t in job.devin.items()}
+
+    def copies_only():
+        with torch.cuda.stream(up):
+            for n, t in host.items():
+                job.devin[n].copy_(t, non_blocking=True)
+        with torch.cuda.stream(down):
+            for h_, n in zip(hout, ("k", "q", "v", "gate", "fr")):
+                h_.copy_(dsrc[n], non_blocking=True)
+        up.synchronize(); down.synchronize()
+    copies_only()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        copies_only()
+    ms_copy = (time.perf_counter() - t0) / 3 * 1e3
+    del dsrc
+
+    # strong scaling is the headline; the weak figure (64 sequences on every GPU) rides along when ranks > 1
+    weak = None
+    if dist_on and scaling == "strong" and not args.no_weak:
+        del job
+        torch.cuda.empty_cache()
+        wjob = ScanJob(S, dev, GB, T, H, N, DK, DV, G, seed=rank, dist=args.dist)
+        for _ in range(args.warmup):
+            wjob.step()
+        wms, _, _ = timed(wjob, args.steps, barrier)
+        wms = max_over_ranks([wms], dev)[0]
+        weak = {"value": whole_job_tokens_per_s(GB, T, world, args.steps, wms), "unit": "tokens/s",
+                "ms_per_step": wms / args.steps, "global_batch": GB * world, "scaling": "weak"}
+        del wjob
+        torch.cuda.empty_cache()
+
+    nseq = max_over_ranks([float(B)], dev)[0]
+    ms, ms_e2e, ms_copy = max_over_ranks([ms, ms_e2e, ms_copy], dev)
     if rank == 0:
-        toks = B * T * world * args.steps
+        toks = global_B * T * args.steps
         ab = algorithmic_bytes_per_token_head(N, DK, DV, G, 2, 2)
         peak, peak_kind = hbm_peak()
         # bytes each kernel is responsible for, per token and head (sums to ab["total"])
@@ -319,49 +467,82 @@ def run_gpu(args, rank, local_rank, world):
             if not c:
                 continue
             ms_l = t / c
-            gbs = kb_bytes[n] * B * T * H / (ms_l * 1e-3) / 1e9
+            gbs = kb_bytes.get(n, 0) * B * T * H / (ms_l * 1e-3) / 1e9
             kern[n] = {"launches": c, "ms_per_launch": ms_l, "share": t / tot_ms,
                        "algorithmic_gbs": gbs, "frac_of_hbm_peak": gbs / peak}
         top = max(prof, key=lambda n: prof[n][1])
         top_ms = prof[top][1] / max(prof[top][0], 1)
-        top_bytes = kb_bytes[top] * B * T * H
+        top_bytes = kb_bytes.get(top, 0) * B * T * H
         achieved = top_bytes / (top_ms * 1e-3) / 1e9
-        step_gbs = ab["total"] * H * B * T / (ms / args.steps * 1e-3) / 1e9
+        step_ms = ms / args.steps
+        step_bytes = ab["total"] * H * B * T                              # per rank: ranks run side by side
+        step_gbs = step_bytes / (step_ms * 1e-3) / 1e9
+        traffic = None
+        if top in NCU_TRAFFIC_B8 and T == SHAPE["T"] and args.dist == "bench":
+            traffic = NCU_TRAFFIC_B8[top][0] * B / 8
         line = {"metric": METRIC, "value": toks / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": scaling,
                 "vs_baseline": None, "dtype": "f32 state/accumulate, bf16 streams+snapshots", "data": "synthetic",
-                "config": {"workload": "config1: slot-scan fwd+bwd, B=%d/GPU T=%d H=%d N=%d dk=dv=%d G=%d, hard+detached, "
-                                       "occ_bin, per-token fr, separate write query, dist=%s" % (B, T, H, N, DK, G, args.dist),
-                           "global_batch": B * world, "seq_len": T, "sharding": "batch, no collective",
-                           "l2": "working set %.1f GB per step >> 126 MB L2 (no flush needed)" % (ab["total"] * H * B * T / 1e9)},
+                "config": {"workload": "config1: slot-scan fwd+bwd, global B=%d (%d per GPU) T=%d H=%d N=%d dk=dv=%d G=%d, "
+                                       "hard+detached, occ_bin, per-token fr, separate write query, dist=%s"
+                                       % (global_B, int(nseq), T, H, N, DK, G, args.dist),
+                           "global_batch": global_B, "seq_len": T, "sharding": "batch, no collective",
+                           "l2": "working set %.1f GB per step and GPU >> 126 MB L2 (no flush needed)" % (step_bytes / 1e9)},
                 "e2e": {"value": toks / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e / args.steps, "pipeline": "%d batch chunks on %d streams" % (P, P)},
+                        "ms_per_step": ms_e2e / args.steps, "pipeline": "%d batch chunks on %d streams" % (P, P),
+                        "copies_only_ms": ms_copy, "copies_only_gbs_each_way": h2d / (ms_copy * 1e-3) / 1e9},
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                             "frac": achieved / peak, "peak_kind": peak_kind, "traffic": TRAFFIC.get(top) if (B == SHAPE["B"] and T == SHAPE["T"] and args.dist == "bench") else None,
+                             "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+                             "traffic_source": NCU_TRAFFIC_B8[top][1] + " (B=8 capture scaled by B/8)" if traffic else None,
                              "algorithmic_bytes_per_launch": top_bytes,
-                             "step": {"algorithmic_bytes": ab["total"] * H * B * T, "achieved": step_gbs, "frac": step_gbs / peak}},
+                             "step": {"algorithmic_bytes": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak}},
                 "kernels": kern,
-                "clocks": clk.summary()}
-        if world == 1 and not args.no_cpu:
-            r = cpu_leg(1, 0)
-            line["cpu_baseline"] = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+                "clocks": clocks}
+        if weak is not None:
+            line["weak"] = weak
+        if world == 1:
+            tb = job.touched_bytes()
+            rf = line["roofline"]
+            rf["touched_bytes_step"] = tb["step"]
+            rf["touched_frac_step"] = tb["step"] / (step_ms * 1e-3) / 1e9 / peak
+            rf["slots_used_mean"] = tb["slots_used_mean"]
+            if top.startswith("rows_bwd"):
+                rf["touched_bytes_per_launch"] = tb["rows_bwd"]
+                rf["touched_frac"] = tb["rows_bwd"] / (top_ms * 1e-3) / 1e9 / peak
+            if not args.no_extra:
+                del job
+                torch.cuda.empty_cache()
+                if args.dist != "fill":
+                    fjob = ScanJob(S, dev, B, T, H, N, DK, DV, G, seed=rank, dist="fill")
+                    for _ in range(3):
+                        fjob.step()
+                    fms, fprof, _ = timed(fjob, max(3, args.steps // 2), barrier)
+                    fsteps = max(3, args.steps // 2)
+                    ftb = fjob.touched_bytes()
+                    rf["fill"] = {"workload": "same shape, inputs that use every slot (dist=fill)", "ms_per_step": fms / fsteps,
+                                  "value": B * T * fsteps / (fms * 1e-3), "unit": "tokens/s",
+                                  "frac_step": step_bytes / (fms / fsteps * 1e-3) / 1e9 / peak,
+                                  "touched_frac_step": ftb["step"] / (fms / fsteps * 1e-3) / 1e9 / peak,
+                                  "slots_used_mean": ftb["slots_used_mean"],
+                                  "kernels_ms": {n: t / c for n, (c, t) in fprof.items() if c}}
+                    del fjob
+                    torch.cuda.empty_cache()
+                line["extra"] = {"read_bench": read_workload(args, local_rank, "bench"),
+                                 "read_fill": read_workload(args, local_rank, "fill"),
+                                 "epilogue": epilogue_workload(args, local_rank)}
+            if not args.no_cpu:
+                r = cpu_leg(3, 1, budget_s=30.0)
+                line["cpu_baseline"] = {"value": r["value"], "unit": "tokens/s", "cores": r["cores"], "kind": "port",
+                                        "sample": r["sample"], "build": r["build"], "config0": r["config0"]}
         emit(line)
     if dist_on:
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at the benchmark size, from the ncu captures
-# summarised under profiles/ (taken at B = 8 and scaled by 8: traffic is proportional to the batch)
-# rows_bwd reads far fewer bytes than its algorithmic figure with the benchmark's inputs: snapshot-gradient rows of
-# slots that were never candidates have no path to any input gradient and are skipped
-TRAFFIC = {"replay_rows_k": 8 * (13.03e6 + 274.17e6), "replay_rows_v": 8 * (13.03e6 + 274.17e6), "addr_fwd": 8 * 25.6e6,
-           "rows_bwd_k": 8 * (107.8e6 + 16.7e6), "addr_bwd": 8 * (52.34e6 + 0.96e6)}
-
-
-def run_epilogue(args, local_rank):
-    """Secondary line (`--workload epilogue`): the writer epilogue + 3-bit storage quantiser over the snapshots of the
-    config-1 scan (keys with kinv / valid, then values), bf16 in, bf16 out.  One GPU; HBM-bound streaming."""
+def epilogue_workload(args, local_rank):
+    """The writer epilogue + 3-bit storage quantiser over the snapshot tensors of the config-1 scan (keys with
+    kinv / valid, then values), bf16 in, bf16 out.  One GPU; HBM-bound streaming."""
     import torch
     import slotscan_b200 as S
     torch.cuda.set_device(local_rank)
@@ -372,96 +553,95 @@ def run_epilogue(args, local_rank):
     vbuf = torch.randn(B, NB, H, N, D, generator=g, device="cuda", dtype=torch.bfloat16)
     rows = kbuf.numel() // D
     out = {}
-    with ClockSampler(local_rank) as clk:
-        for bits in (0, 3):
-            for _ in range(max(args.warmup, 3)):
-                S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(args.steps):
-                S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
-            b.record()
-            torch.cuda.synchronize()
-            out[bits] = a.elapsed_time(b) / args.steps
+    for bits in (0, 3):
+        for _ in range(3):
+            S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            S.writer_epilogue(kbuf, vbuf, torch.bfloat16, qbits=bits, qgroup=16)
+        b.record()
+        torch.cuda.synchronize()
+        out[bits] = a.elapsed_time(b) / args.steps
     peak, which = hbm_peak()
     # bits 0: keys are read, written and normed by the kernel; the values' cast bf16 -> bf16 is the identity (no pass)
     alg0 = rows * (2 * D * 2 + 5)
     alg3 = 2 * rows * 2 * D * 2 + rows * 5
-    line = {"metric": "writer epilogue GB/s (config-1 snapshots, bf16)", "value": alg3 / out[3] / 1e6, "unit": "GB/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": out[3],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16 storage",
-            "data": "synthetic", "gpu_launches": 2 * args.steps,
-            "config": {"workload": "writer epilogue + _fq(3 bits, group 16) over (%d,%d,%d,%d,%d) keys and values"
-                                   % (B, NB, H, N, D), "l2": "inputs (2 x %.1f GB) larger than L2" % (rows * D * 2 / 1e9)},
-            "roofline": {"bound": "hbm", "achieved": alg3 / out[3] / 1e6, "peak": peak, "unit": "GB/s",
-                         "frac": alg3 / out[3] / 1e6 / peak, "traffic": None, "peak_source": which},
-            "unquantised": {"ms_per_step": out[0], "achieved": alg0 / out[0] / 1e6, "frac": alg0 / out[0] / 1e6 / peak},
-            "clocks": clk.summary()}
-    emit(line)
+    del kbuf, vbuf
+    torch.cuda.empty_cache()
+    return {"workload": "writer epilogue over (%d,%d,%d,%d,%d) bf16 keys and values" % (B, NB, H, N, D),
+            "fq3_group16": {"ms": out[3], "achieved_gbs": alg3 / out[3] / 1e6, "frac": alg3 / out[3] / 1e6 / peak},
+            "unquantised": {"ms": out[0], "achieved_gbs": alg0 / out[0] / 1e6, "frac": alg0 / out[0] / 1e6 / peak},
+            "peak_source": which}
 
 
-def run_read(args, local_rank):
-    """Secondary line (`--workload read`): one reader layer's cosine read (NQ = 2 queries per head) over the snapshots of
-    the config-1 scan: scan -> writer epilogue once (untimed), then the read is timed.  One GPU."""
+def read_workload(args, local_rank, dist):
+    """One reader layer's cosine read (NQ = 2 queries per head) over the snapshots of the config-1 scan: scan -> writer
+    epilogue once (untimed), then the read is timed, forward and backward, and beside it the reference's own read
+    math (torch einsum + softmax, gqa25/memlm_sh.py:379-397) on the same device tensors."""
     import torch
     import slotscan_b200 as S
     torch.cuda.set_device(local_rank)
     s = SHAPE
     B, T, H, N, D, G, NQ = (args.B or s["B"]), (args.T or s["T"]), s["H"], s["N"], s["DK"], s["G"], 2
-    inp = make_host_inputs(B, T, H, D, D, seed=0, dist=args.dist)
+    inp = make_host_inputs(B, T, H, D, D, seed=0, dist=dist)
     k, q, v = (inp[n].cuda().to(torch.bfloat16) for n in ("k", "q", "v"))
+    steps = max(3, args.steps // 2)
+
+    def time_it(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
     with torch.no_grad():
         kbuf, vbuf = S.kv_scan_g(k, v, inp["gate"].cuda(), inp["fr"].cuda(), N, 16.0, G=G, hard=True, detach_addr=True,
                                  q=q, occ_bin=True, out_dtype=torch.bfloat16)
         kq, vq, kinv, valid = S.writer_epilogue(kbuf, vbuf, torch.bfloat16)
+        del kbuf, vbuf, k, q, v
         g = torch.Generator(device="cuda").manual_seed(1)
         qr = torch.randn(B, T, H, NQ, D, generator=g, device="cuda", dtype=torch.bfloat16)
         sharp = torch.nn.functional.softplus(torch.randn(B, T, H, NQ, generator=g, device="cuda")) + 1
-        with ClockSampler(local_rank) as clk:
-            for _ in range(max(args.warmup, 3)):
-                S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(args.steps):
-                S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G)
-            b.record()
-            torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / args.steps
+        ms = time_it(lambda: S.read_snapshots(qr, sharp, kq, vq, kinv, valid, G))
         drd = torch.randn(B, T, H, NQ, D, generator=g, device="cuda", dtype=torch.bfloat16)
-        for _ in range(3):
-            torch.ops.slotscan.read_bwd(qr, sharp, kq, vq, kinv, valid.to(torch.uint8), drd, G)
-        torch.cuda.synchronize()
-        a.record()
-        for _ in range(args.steps):
-            torch.ops.slotscan.read_bwd(qr, sharp, kq, vq, kinv, valid.to(torch.uint8), drd, G)
-        b.record()
-        torch.cuda.synchronize()
-        ms_bwd = a.elapsed_time(b) / args.steps
+        v8 = valid.to(torch.uint8)
+        ms_bwd = time_it(lambda: torch.ops.slotscan.read_bwd(qr, sharp, kq, vq, kinv, v8, drd, G))
+
+        # the reference's read on the same tensors (library GEMMs + eager softmax), forward only
+        NB = T // G
+
+        def torch_read():
+            qn = torch.nn.functional.normalize(qr.float(), dim=-1, eps=1e-6).to(qr.dtype)
+            qb = qn.view(B, NB, G, H, NQ, D).permute(0, 1, 3, 2, 4, 5).reshape(B, NB, H, G * NQ, D)
+            sc = torch.einsum("bjhmd,bjhnd->bjhmn", qb, kq).float() * kinv.unsqueeze(-2)
+            sc = sc * sharp.view(B, NB, G, H, NQ).permute(0, 1, 3, 2, 4).reshape(B, NB, H, G * NQ, 1)
+            att = torch.softmax(sc.masked_fill(~valid.unsqueeze(-2), float("-inf")), dim=-1).nan_to_num(0.0)
+            return torch.einsum("bjhmn,bjhnd->bjhmd", att.to(vq.dtype), vq)
+        ms_torch = time_it(torch_read) if T % G == 0 else None
     peak, which = hbm_peak()
     rows = kq.numel() // D
     alg = qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 5      # q, rd, sharp, both snapshots, kinv+valid
     touched = qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * int(valid.sum()) * D * 2 + rows * 5
-    line = {"metric": "snapshot read tokens/s per reader layer (config-1 shape, NQ=2, bf16)", "value": B * T / (ms * 1e-3),
-            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16 storage",
-            "data": "synthetic", "gpu_launches": args.steps,
-            "config": {"workload": "cosine read, forward: B=%d T=%d H=%d NQ=%d N=%d dk=dv=%d G=%d over the snapshots of the "
-                                   "config-1 scan (dist=%s), valid rows per snapshot %.1f of %d"
-                                   % (B, T, H, NQ, N, D, G, args.dist, float(valid.sum()) / (rows / N), N)},
-            # invalid rows are masked out of the softmax and never loaded: the bytes that count are those of the valid
-            # rows; the all-rows figure (what a dense batched GEMM reads) is given beside it
-            "roofline": {"bound": "hbm", "achieved": touched / ms / 1e6, "peak": peak, "unit": "GB/s",
-                         "frac": touched / ms / 1e6 / peak, "traffic": None, "peak_source": which,
-                         "algorithmic_bytes": touched, "bytes_all_rows": alg, "achieved_all_rows": alg / ms / 1e6},
-            # backward: re-reads what the forward read plus drd, writes dqr, dsharp and BOTH snapshot gradients in full
-            # (exact zeros in the rows that are not valid) and dkinv
-            "backward": {"ms_per_step": ms_bwd, "algorithmic_bytes": touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4,
-                         "achieved": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6,
-                         "frac": (touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4) / ms_bwd / 1e6 / peak},
-            "clocks": clk.summary()}
-    emit(line)
+    bwd_bytes = touched + qr.numel() * 2 * 2 + sharp.numel() * 4 + 2 * rows * D * 2 + rows * 4
+    out = {"workload": "cosine read of one reader layer: B=%d T=%d H=%d NQ=%d N=%d dk=dv=%d G=%d, dist=%s, valid rows per "
+                       "snapshot %.1f of %d" % (B, T, H, NQ, N, D, G, dist, float(valid.sum()) / (rows / N), N),
+           "fwd_ms": ms, "fwd_tokens_per_s": B * T / (ms * 1e-3),
+           # invalid rows are masked out of the softmax and never loaded: the bytes that count are those of the valid
+           # rows; the all-rows figure (what a dense batched GEMM reads) is given beside it
+           "fwd_touched_gbs": touched / ms / 1e6, "fwd_touched_frac": touched / ms / 1e6 / peak,
+           "fwd_all_rows_gbs": alg / ms / 1e6, "fwd_all_rows_frac": alg / ms / 1e6 / peak,
+           "bwd_ms": ms_bwd, "bwd_gbs": bwd_bytes / ms_bwd / 1e6, "bwd_frac": bwd_bytes / ms_bwd / 1e6 / peak,
+           "torch_reference_math_fwd_ms": ms_torch, "peak_source": which}
+    del kq, vq, kinv, valid, qr, sharp, drd
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -470,28 +650,32 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--B", type=int, default=0, help="sequences per GPU (default 64)")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong: the global batch (64 sequences) is split over the GPUs; weak: 64 sequences per GPU")
+    ap.add_argument("--B", type=int, default=0, help="sequences of the global batch (default 64)")
     ap.add_argument("--T", type=int, default=0, help="tokens per sequence (default 1024)")
     ap.add_argument("--dist", default="bench", help="input distribution: bench (the benchmark's) | fill (every slot used) | clustered")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the fill-distribution step and the read / epilogue figures")
+    ap.add_argument("--no-weak", action="store_true", help="ranks > 1: skip the secondary weak-scaling figure")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks (= streams) of the end-to-end leg")
     ap.add_argument("--workload", default="scan", choices=["scan", "epilogue", "read"],
-                    help="scan: the headline fwd+bwd slot scan; epilogue: the writer epilogue + quantiser pass; "
-                         "read: one reader layer's cosine read of the snapshots (secondary lines, 1 GPU)")
+                    help="scan: the headline fwd+bwd slot scan; epilogue / read: only that secondary figure (1 GPU)")
     args = ap.parse_args()
     claim_stdout()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args, rank, world)
-    elif args.workload == "epilogue":
+        return
+    args.warmup = max(args.warmup, 3)
+    if args.workload == "epilogue":
         if rank == 0:
-            run_epilogue(args, local_rank)
+            emit(epilogue_workload(args, local_rank))
     elif args.workload == "read":
         if rank == 0:
-            run_read(args, local_rank)
+            emit(read_workload(args, local_rank, args.dist))
     else:
         run_gpu(args, rank, local_rank, world)
 

@@ -38,6 +38,24 @@ def lib():
     return _LIB
 
 
+def use_timed_build():
+    """For the TIMED CPU-baseline legs of bench.py only: switch to a build of the same source compiled for speed on
+    the host it runs on (-O3 -march=native, contraction allowed), so the baseline is not handicapped by the flags the
+    parity build needs (no FMA contraction, to match the reference's torch arithmetic bit for bit where it can).
+    Falls back to the parity build if the compiler refuses.  Returns the flags in use."""
+    global _LIB
+    path = os.path.join(_HERE, "liboracle_timed.so")
+    flags = ["-O3", "-march=native", "-fPIC", "-fopenmp"]
+    try:
+        subprocess.run(["gcc"] + flags + ["-shared", "-o", path, os.path.join(_HERE, "slotscan_oracle.c"), "-lm"],
+                       check=True, capture_output=True)
+        _LIB = ctypes.CDLL(path)
+        return " ".join(flags)
+    except Exception:
+        lib()
+        return "-O2 -ffp-contract=off (parity build)"
+
+
 def threads():
     return lib().slotscan_oracle_threads()
 

@@ -96,11 +96,11 @@ def _compare_sequences(tag, out, inp, dkb, dvb, N, G, H, seqs):
         m5, m4, m3 = keep[:, None, :, None, None], keep[:, None, :, None], keep[:, None, :]
         for n in ("kbuf", "vbuf"):
             okc, worst, share = bf16_band_report(out[n][sl].float().cpu().numpy() * m5, ref[n] * m5)
-            assert okc and share <= 2e-3, (tag, b, n, worst, share)
+            assert okc and share <= 5e-4, (tag, b, n, worst, share)
         for n in ("dk", "dq", "dv"):
             scale = max(np.abs(gr[n]).max(), 1e-30)
             okc, worst, share = bf16_band_report(out[n][sl].float().cpu().numpy() * m4, gr[n] * m4, scale)
-            assert okc and share <= 2e-2, (tag, b, n, worst / scale, share)
+            assert okc and share <= 5e-3, (tag, b, n, worst / scale, share)
         for n in ("dgate", "dfr"):
             scale = max(np.abs(gr[n]).max(), 1e-30)
             okc, worst = allclose_report(out[n][sl].cpu().numpy() * m3 / scale, gr[n] * m3 / scale, 2e-3, 2e-3)

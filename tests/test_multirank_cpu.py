@@ -37,3 +37,17 @@ def test_two_gloo_ranks_shard_and_reduce():
     assert a0 == a1 == 11.0 and b0 == b1 == 5.0      # max over ranks, identical on every rank
     import bench
     assert bench.whole_job_tokens_per_s(64, 1024, 2, 10, 50.0) == 2 * 64 * 1024 * 10 / 0.05
+
+
+def test_strong_scaling_shards_cover_the_global_batch():
+    import bench
+    for world in (1, 2, 4, 8, 3):
+        parts = [bench.shard_of_batch(64, world, r, "strong") for r in range(world)]
+        assert sum(n for _, n in parts) == 64
+        assert [f for f, _ in parts] == [sum(n for _, n in parts[:r]) for r in range(world)]     # contiguous, in rank order
+        assert max(n for _, n in parts) - min(n for _, n in parts) <= 1
+    assert bench.shard_of_batch(64, 8, 3, "strong") == (24, 8)
+    assert bench.shard_of_batch(64, 8, 3, "weak") == (192, 64)
+    # CPU sample of the reference arm: at least two OpenMP tasks per host thread
+    for cores in (8, 16, 32, 64):
+        assert bench.cpu_sample_batch(cores, 6) * 6 >= 2 * cores

@@ -137,8 +137,8 @@ BF16_CASES = [c for c in CASES if c[0] in ("sh25_main", "sh25_enc", "sh25_main_c
                                            "gates01_55rows", "gates01_110rows", "dk_ne_dv")]
 # Largest share of elements that may differ from the bf16-rounded oracle value (see bf16_band_report): snapshots are
 # float32 state rounded once, so only values within float32 round-off of a rounding boundary differ; gradients are
-# float32 sums of many terms rounded once.
-SNAP_SHARE, GRAD_SHARE = 2e-3, 2e-2
+# float32 sums of many terms rounded once (measured: below 1e-3).
+SNAP_SHARE, GRAD_SHARE = 5e-4, 5e-3
 
 
 @pytest.mark.parametrize("case", BF16_CASES, ids=[c[0] for c in BF16_CASES])
