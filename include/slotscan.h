@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define SLOTSCAN_ABI_VERSION 1
+#define SLOTSCAN_ABI_VERSION 2
 
 enum { SLOTSCAN_F32 = 0, SLOTSCAN_BF16 = 1 };
 
@@ -82,6 +82,36 @@ int slotscan_hard_fwd(const slotscan_params* p, const void* k, const void* q, co
                       const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log* log,
                       void* stream);
 
+/* Extras of a forward call; every pointer may be NULL (a NULL `ex` is slotscan_hard_fwd).
+ * [The reference carries no state across calls (gqa25/memlm_sh.py:676 asserts it) and forms kinv / valid in a separate
+ * eager pass over the emitted keys (memlm_sh.py:474-475); its kernels hold the final state internally
+ * (slotkern_cuda.py:504).]
+ *   K0, V0, o0   (B*H,N,DK) (B*H,N,DV) (B*H,N) f32: the state the scan starts from -- kfin, vfin, ofin of the call that
+ *                scanned the preceding tokens.  All three or none (none = the empty memory).  Snapshot 0 is then this
+ *                state.  A long context is streamed chunk by chunk this way with memory constant in T.
+ *   nsq0         (B*H,N) f64: squared key norms carried with the state (nsqfin of the preceding call).  NULL: they are
+ *                summed again from K0, which may move a score by one float32 ulp against the unchunked scan.
+ *   nsqfin       (B*H,N) f64 out: squared key norms of the final state as the scan carried them.
+ *   kinv, valid  (B,NB,H,N) f32 / bytes out, both or neither: rsqrt(max(|K_n|^2, 1e-12)) and [|K_n|^2 > 1e-12] of every
+ *                emitted key row, taken from the float32 state while the row is in registers (what memlm_sh.py:474-475
+ *                computes from the float32 kbuf before casting it): no separate pass over the snapshots.
+ *   no_undo_log  non-zero: the rows before each write (log->kold, log->vold, which may then be NULL) are not stored.
+ *                For forward-only callers; the backward needs them.
+ * The backward of a call that was given K0 / V0 / o0 produces no gradient for that carried-in state. */
+typedef struct {
+    const float* K0;
+    const float* V0;
+    const float* o0;
+    const double* nsq0;
+    double* nsqfin;
+    float* kinv;
+    uint8_t* valid;
+    int32_t no_undo_log;
+} slotscan_fwd_extra;
+int slotscan_hard_fwd_ex(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
+                         const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log* log,
+                         const slotscan_fwd_extra* ex, void* stream);
+
 /* Bytes of scratch the backward needs (the per-token, per-row table D[t,n] plus per-sequence partial sums). */
 size_t slotscan_hard_bwd_scratch_bytes(const slotscan_params* p);
 
@@ -95,6 +125,15 @@ int slotscan_hard_bwd(const slotscan_params* p, const void* k, const void* q, co
                       const float* fr, const float* temp, const slotscan_log* log, const void* dkbuf,
                       const void* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq, void* dv,
                       float* dgate, float* dfr, float* dtemp, void* stream);
+
+/* slotscan_hard_bwd with one more upstream gradient: dkinv (B,NB,H,N) f32, the gradient that reached the kinv output
+ * of slotscan_hard_fwd_ex (NULL = none).  It enters the key rows where the snapshot was taken,
+ * d kbuf[j,n] += -kinv^3 * dkinv[j,n] * K_n for valid rows, with K_n the float32 state -- the adjoint of
+ * rsqrt(clamp_min(nsq, 1e-12)) that the reference gets from autograd (memlm_sh.py:474-475). */
+int slotscan_hard_bwd_ex(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
+                         const float* fr, const float* temp, const slotscan_log* log, const void* dkbuf,
+                         const void* dvbuf, const float* dkinv, void* scratch, size_t scratch_bytes, void* dk, void* dq,
+                         void* dv, float* dgate, float* dfr, float* dtemp, void* stream);
 
 /* The same backward for callers that cannot supply scratch memory.  [No counterpart in the reference: its host side
  * always allocates through torch.]  Meant for hosts whose device memory is already fully assigned (a server that

@@ -111,13 +111,14 @@ __device__ __forceinline__ void af_token_consts(const Ts* __restrict__ qrow, con
     }
 }
 
-// RPL = row slots per lane (N <= 32 * RPL)
-template <int DK, int RPL, bool OCCB, typename Tin>
+// RPL = row slots per lane (N <= 32 * RPL); CARRY: the scan starts from a state carried in from a preceding chunk
+template <int DK, int RPL, bool OCCB, bool CARRY, typename Tin>
 __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, int* __restrict__ am_out,
     float* __restrict__ oold_out, float* __restrict__ kiold_out, float* __restrict__ ofin, int* __restrict__ tfirst,
-    const int ncap, const int second_pass) {
+    const float* __restrict__ K0, const float* __restrict__ o0, const double* __restrict__ nsq0,
+    double* __restrict__ nsqfin, const int ncap, const int second_pass) {
     // Two-pass protocol.  Most sequences touch few rows, and a CTA that holds only `ncap` rows is small enough for every
     // (sequence, head) of a large batch to be resident at once.  Pass 1 (ncap < N) runs every sequence; one that
     // needs row ncap gives up, marks itself by tfirst[bh][0] = -1 and leaves.  Pass 2 (ncap = N, second_pass = 1)
@@ -162,7 +163,39 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     __syncthreads();
     for (int i = tid; i < ncap * KS; i += AF_THREADS) K[i] = 0.f;
     for (int i = tid; i < DK; i += AF_THREADS) Ks[(RING - 1) * DK + i] = (Ts)0.f;    // "the key before token 0"
-    for (int i = tid; i < N; i += AF_THREADS) tfirst[(size_t)bh * N + i] = (i == 0) ? 0 : T;
+    // State carried in from a preceding chunk (K0 / o0, optionally the squared key norms as that scan carried them).
+    // hw0 = the highest row it has touched: rows above it are exactly zero, as in a scan from the empty memory.
+    int hw0 = -1;
+    double* s_nsq = reinterpret_cast<double*>(smem + L.part);         // N doubles, before `part` is first written
+    if (CARRY) {
+        for (int n = warp; n < N; n += AF_WARPS) {
+            double a = 0.0;
+            if (nsq0 != nullptr) {
+                a = nsq0[(size_t)bh * N + n];
+            } else {
+                for (int c = lane; c < DK; c += 32) {
+                    const double xk = (double)K0[((size_t)bh * N + n) * DK + c];
+                    a = fma(xk, xk, a);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(FULL, a, off);
+            }
+            if (lane == 0) s_nsq[n] = a;
+        }
+        __syncthreads();
+        for (int n = 0; n < N; n++)
+            if (s_nsq[n] > 0.0 || o0[(size_t)bh * N + n] != 0.f) hw0 = n;             // same in every thread
+        for (int i = tid; i < ncap * DK; i += AF_THREADS) {
+            const int n = i / DK, c = i - n * DK;
+            K[(size_t)n * KS + c] = K0[((size_t)bh * N + n) * DK + c];
+        }
+    }
+    const int lim0 = CARRY ? min(hw0 + 1, N - 1) : 0;                 // candidate limit of token 0
+    for (int i = tid; i < N; i += AF_THREADS) tfirst[(size_t)bh * N + i] = (i <= hw0 + 1) ? 0 : T;
+    if (CARRY && lim0 >= ncap) {                                      // the carried-in state already needs more rows
+        if (tid == 0) tfirst[(size_t)bh * N] = -1;
+        return;
+    }
 
     // ---- chunk loader (warps 1..4): 8-element items of q (first IPS) and k (next IPS); gate / fr on 2 C threads ----
     Pre8<Tin> pre[NIT];
@@ -364,7 +397,22 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
     float kinv_r[RPL], o_r[RPL];
 #pragma unroll
     for (int s = 0; s < RPL; s++) { nsq_r[s] = 0.0; kinv_r[s] = 1e6f; o_r[s] = 0.f; }
-    int hw = -1, fe = 0, lim = 0;                         // highest row touched; lowest free row (N if none)
+    int hw = hw0, fe = 0, lim = lim0;                     // highest row touched; lowest free row (N if none)
+    if (CARRY && warp == 0) {
+        int m = BIGI;
+#pragma unroll
+        for (int s = RPL - 1; s >= 0; s--) {
+            const int n = lane + 32 * s;
+            if (n < N) {
+                nsq_r[s] = s_nsq[n];
+                kinv_r[s] = fminf(rsqrtf((float)nsq_r[s]), 1e6f);
+                o_r[s] = o0[(size_t)bh * N + n];
+                if (o_r[s] < eps) m = n;
+            }
+        }
+        m = (int)__reduce_min_sync(FULL, (unsigned)m);
+        fe = (m == BIGI) ? N : m;
+    }
     int am_prev = -1, pslot = 0;                          // the token whose bookkeeping is still open
     float Rb_prev = 0.f;
     TokC cc = {}, pc = {}, nc = {};                       // constants of the current, previous and next token
@@ -381,7 +429,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         for (int r = 0; r < C / 8; r++) AF_TOKEN_CONSTS(0, r);
     }
     __syncthreads();
-    if (wact) { AF_DOTS_SPLIT(4, 0, 0) }
+    if (wact) {
+        if (CARRY) { AF_DOTS_DISPATCH(lim0, 0, 0) }
+        else { AF_DOTS_SPLIT(4, 0, 0) }
+    }
     if (warp == 0) AF_LOAD_CONSTS(cc, 0);
     __syncthreads();
 
@@ -419,7 +470,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
 #pragma unroll
         for (int s = 0; s < RPL; s++) {
             const int n = lane + 32 * s;
-            if (n < N) ofin[(size_t)bh * N + n] = o_r[s];
+            if (n < N) {
+                ofin[(size_t)bh * N + n] = o_r[s];
+                if (nsqfin != nullptr) nsqfin[(size_t)bh * N + n] = nsq_r[s];
+            }
         }
     } else {
         for (int t = 0; t < T; t++) {
@@ -454,7 +508,10 @@ __global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
         }
     }
 #undef AF_PHASE_BARRIER
-    for (int n = 32 * RPL + tid; n < N; n += AF_THREADS) ofin[(size_t)bh * N + n] = 0.f;   // rows this pass never held
+    for (int n = 32 * RPL + tid; n < N; n += AF_THREADS) {                                // rows this pass never held
+        ofin[(size_t)bh * N + n] = 0.f;
+        if (nsqfin != nullptr) nsqfin[(size_t)bh * N + n] = 0.0;
+    }
     __syncthreads();
     {   // the log entries not written out yet: the last chunk, and the one before it if the last stopped before phase 1
         const int cl = (T - 1) / C;

@@ -68,30 +68,33 @@ constexpr size_t SMEM_CAP = 227 * 1024;
 
 static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
                            const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
-                           cudaStream_t st) {
+                           const slotscan_fwd_extra& ex, cudaStream_t st) {
     cudaError_t e;
     {
         ProfScope ps(K_ADDR_FWD, st);
-        e = (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, st)
-                                         : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, st);
+        const AddrFwdState S0{ex.K0, ex.o0, ex.nsq0, ex.nsqfin};
+        e = (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, S0, st)
+                                         : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, S0, st);
     }
     if (e != cudaSuccess) return e;
     {
         ProfScope ps(K_REPLAY_K, st);
-        e = run_replay(p, p.DK, k, gate, L.addr, L.tfirst, kbuf, L.kold, L.kfin, st);
+        e = run_replay(p, p.DK, k, gate, L.addr, L.tfirst, ex.K0, kbuf, ex.no_undo_log ? nullptr : L.kold, L.kfin, ex.kinv,
+                       ex.valid, st);
     }
     if (e != cudaSuccess) return e;
     {
         ProfScope ps(K_REPLAY_V, st);
-        e = run_replay(p, p.DV, v, gate, L.addr, L.tfirst, vbuf, L.vold, L.vfin, st);
+        e = run_replay(p, p.DV, v, gate, L.addr, L.tfirst, ex.V0, vbuf, ex.no_undo_log ? nullptr : L.vold, L.vfin, nullptr,
+                       nullptr, st);
     }
     return e;
 }
 
 static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
                            const float* fr, const float* temp, const slotscan_log& L, const void* dkbuf, const void* dvbuf,
-                           float* Dn, float* part, int* vend, void* dk, void* dq, void* dv, float* dgate, float* dfr,
-                           float* dtemp, cudaStream_t st) {
+                           const float* dkinv, float* Dn, float* part, int* vend, void* dk, void* dq, void* dv,
+                           float* dgate, float* dfr, float* dtemp, cudaStream_t st) {
     cudaError_t e;
     // partial sums of dtemp / scalar dfr: one slot per (sequence, 32-token chunk) + one per sequence; slots that no
     // kernel fills must read as zero
@@ -100,8 +103,8 @@ static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* 
     if ((e = cudaMemsetAsync(part, 0, 2 * part_n * sizeof(float), st)) != cudaSuccess) return e;
     // keys and values are independent given the log: one launch (blockIdx.z) when dk == dv, each into its own D table
     float* DnV = Dn + (size_t)p.B * p.H * p.T * p.N;
-    const RowsBwdPtrs ak{k, L.kold, L.kfin, dkbuf, dk, Dn};
-    const RowsBwdPtrs av{v, L.vold, L.vfin, dvbuf, dv, DnV};
+    const RowsBwdPtrs ak{k, L.kold, L.kfin, dkbuf, dk, Dn, dkinv};
+    const RowsBwdPtrs av{v, L.vold, L.vfin, dvbuf, dv, DnV, nullptr};
     if (p.DK == p.DV) {
         ProfScope ps(K_ROWS_BWD_K, st);
         e = run_rows_bwd(p, p.DK, 2, ak, av, gate, L.addr, L.tfirst, st);
@@ -159,21 +162,32 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     return SLOTSCAN_OK;
 }
 
+extern "C" int slotscan_hard_fwd_ex(const slotscan_params* p, const void* k, const void* q, const void* v,
+                                    const float* gate, const float* fr, const float* temp, void* kbuf, void* vbuf,
+                                    const slotscan_log* log, const slotscan_fwd_extra* ex_, void* stream) {
+    int rc = slotscan_check(p);
+    if (rc) return rc;
+    slotscan_fwd_extra ex = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+    if (ex_) ex = *ex_;
+    if (!k || !v || !gate || !fr || !temp || !kbuf || !vbuf || !log) return SLOTSCAN_E_NULL;
+    if (!log->addr || !log->oold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst || !log->kiold)
+        return SLOTSCAN_E_NULL;
+    if (!ex.no_undo_log && (!log->kold || !log->vold)) return SLOTSCAN_E_NULL;
+    if ((ex.K0 != nullptr) != (ex.V0 != nullptr) || (ex.K0 != nullptr) != (ex.o0 != nullptr)) return SLOTSCAN_E_NULL;
+    if (ex.nsq0 != nullptr && ex.K0 == nullptr) return SLOTSCAN_E_NULL;
+    if ((ex.kinv != nullptr) != (ex.valid != nullptr)) return SLOTSCAN_E_NULL;
+    if (misaligned(k) || misaligned(q) || misaligned(v) || misaligned(kbuf) || misaligned(vbuf) || misaligned(log->kold) ||
+        misaligned(log->vold) || misaligned(log->kfin) || misaligned(log->vfin) || misaligned(ex.K0) || misaligned(ex.V0))
+        return SLOTSCAN_E_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const cudaError_t e = fwd_run(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, ex, st);
+    return (int)e;
+}
+
 extern "C" int slotscan_hard_fwd(const slotscan_params* p, const void* k, const void* q, const void* v, const float* gate,
                                  const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log* log,
                                  void* stream) {
-    int rc = slotscan_check(p);
-    if (rc) return rc;
-    if (!k || !v || !gate || !fr || !temp || !kbuf || !vbuf || !log) return SLOTSCAN_E_NULL;
-    if (!log->addr || !log->oold || !log->kold || !log->vold || !log->kfin || !log->vfin || !log->ofin || !log->tfirst ||
-        !log->kiold)
-        return SLOTSCAN_E_NULL;
-    if (misaligned(k) || misaligned(q) || misaligned(v) || misaligned(kbuf) || misaligned(vbuf) || misaligned(log->kold) ||
-        misaligned(log->vold) || misaligned(log->kfin) || misaligned(log->vfin))
-        return SLOTSCAN_E_ALIGN;
-    cudaStream_t st = (cudaStream_t)stream;
-    const cudaError_t e = fwd_run(*p, k, q, v, gate, fr, temp, kbuf, vbuf, *log, st);
-    return (int)e;
+    return slotscan_hard_fwd_ex(p, k, q, v, gate, fr, temp, kbuf, vbuf, log, nullptr, stream);
 }
 
 // scratch layout: [D table keys | D table values] [partial sums 2 x B*H x (chunks + 1) f32] [next-write table B*H x chunks x 32 i32]
@@ -200,6 +214,15 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
                                  const float* fr, const float* temp, const slotscan_log* log, const void* dkbuf,
                                  const void* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq, void* dv,
                                  float* dgate, float* dfr, float* dtemp, void* stream) {
+    return slotscan_hard_bwd_ex(p, k, q, v, gate, fr, temp, log, dkbuf, dvbuf, nullptr, scratch, scratch_bytes, dk, dq, dv,
+                                dgate, dfr, dtemp, stream);
+}
+
+extern "C" int slotscan_hard_bwd_ex(const slotscan_params* p, const void* k, const void* q, const void* v,
+                                    const float* gate, const float* fr, const float* temp, const slotscan_log* log,
+                                    const void* dkbuf, const void* dvbuf, const float* dkinv, void* scratch,
+                                    size_t scratch_bytes, void* dk, void* dq, void* dv, float* dgate, float* dfr,
+                                    float* dtemp, void* stream) {
     int rc = slotscan_check(p);
     if (rc) return rc;
     if (!k || !v || !gate || !fr || !temp || !log || !scratch || !dk || !dq || !dv || !dgate || !dfr || !dtemp)
@@ -218,7 +241,8 @@ extern "C" int slotscan_hard_bwd(const slotscan_params* p, const void* k, const 
     float* part = (float*)((char*)scratch + off_part);
     int* vend = (int*)((char*)scratch + off_vend);
     cudaStream_t st = (cudaStream_t)stream;
-    const cudaError_t e = bwd_run(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, Dn, part, vend, dk, dq, dv, dgate, dfr, dtemp, st);
+    const cudaError_t e = bwd_run(*p, k, q, v, gate, fr, temp, *log, dkbuf, dvbuf, dkinv, Dn, part, vend, dk, dq, dv, dgate,
+                                  dfr, dtemp, st);
     return (int)e;
 }
 

@@ -17,10 +17,12 @@ static inline cudaError_t opt_in_smem(F f, size_t bytes) {
 }
 
 // in_dtype / snap_dtype of p select the instantiation
+// initial state of the address scan (all NULL: the empty memory) and where its carried squared key norms go
+struct AddrFwdState { const float* K0; const float* o0; const double* nsq0; double* nsqfin; };
 cudaError_t run_addr_fwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
-                             const float* temp, const slotscan_log& L, cudaStream_t st);
+                             const float* temp, const slotscan_log& L, const AddrFwdState& S0, cudaStream_t st);
 cudaError_t run_addr_fwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
-                              const float* temp, const slotscan_log& L, cudaStream_t st);
+                              const float* temp, const slotscan_log& L, const AddrFwdState& S0, cudaStream_t st);
 cudaError_t run_addr_bwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                              const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
                              float* part, int* vend, int part_stride, cudaStream_t st);
@@ -30,11 +32,13 @@ cudaError_t run_addr_bwd_bf16(const slotscan_params& p, const void* q, const voi
 // tokens per CTA of the token-parallel address backward: the partial-sum table has one slot per such chunk (+ 1)
 constexpr int GATHER_CHUNK = 32;
 constexpr int GATHER_ROWS_MAX = 32;
-// one tensor (keys: D = DK, values: D = DV) through the forward row replay
+// one tensor (keys: D = DK, values: D = DV) through the forward row replay.  x0: the rows the replay starts from
+// (NULL = zeros); xold NULL: no undo log; kinv / valid: per emitted row, from the float32 state (keys only, or NULL)
 cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
-                       void* xbuf, float* xold, float* xfin, cudaStream_t st);
+                       const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid, cudaStream_t st);
 // reverse row scan; ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs the first set only
-struct RowsBwdPtrs { const void* x; const float* xold; const float* xfin; const void* dxbuf; void* dx; float* Dn; };
+// dkinv: upstream gradient of the kinv output (keys only, NULL otherwise)
+struct RowsBwdPtrs { const void* x; const float* xold; const float* xfin; const void* dxbuf; void* dx; float* Dn; const float* dkinv; };
 cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
                          const float* gate, const int* am, const int* tfirst, cudaStream_t st);
 

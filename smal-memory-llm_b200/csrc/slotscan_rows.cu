@@ -8,10 +8,16 @@ namespace slotscan {
 
 template <int D, typename Tin, typename Tsn>
 static cudaError_t replay_one(const slotscan_params& p, const void* x, const float* gate, const int* am, const int* tfirst,
-                              void* xbuf, float* xold, float* xfin, cudaStream_t st) {
+                              const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid,
+                              cudaStream_t st) {
     constexpr int RPB = ROW_THREADS / (D / 8);
     dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB);
-    replay_rows_kernel<D, Tin, Tsn><<<grid, ROW_THREADS, 0, st>>>(p, (const Tin*)x, gate, am, tfirst, (Tsn*)xbuf, xold, xfin);
+    if (kinv != nullptr)
+        replay_rows_kernel<D, Tin, Tsn, true><<<grid, ROW_THREADS, 0, st>>>(p, (const Tin*)x, gate, am, tfirst, x0, (Tsn*)xbuf,
+                                                                            xold, xfin, kinv, valid);
+    else
+        replay_rows_kernel<D, Tin, Tsn, false><<<grid, ROW_THREADS, 0, st>>>(p, (const Tin*)x, gate, am, tfirst, x0, (Tsn*)xbuf,
+                                                                             xold, xfin, nullptr, nullptr);
     return cudaGetLastError();
 }
 
@@ -24,8 +30,8 @@ static cudaError_t rows_bwd_one(const slotscan_params& p, int ntensors, const Ro
     auto kern = rows_bwd_kernel<D, Tin, Tsn>;
     cudaError_t e = opt_in_smem(kern, sm);
     if (e != cudaSuccess) return e;
-    const RowsBwdArgs<Tin, Tsn> b0{(const Tin*)a0.x, a0.xold, a0.xfin, (const Tsn*)a0.dxbuf, (Tin*)a0.dx, a0.Dn};
-    const RowsBwdArgs<Tin, Tsn> b1{(const Tin*)a1.x, a1.xold, a1.xfin, (const Tsn*)a1.dxbuf, (Tin*)a1.dx, a1.Dn};
+    const RowsBwdArgs<Tin, Tsn> b0{(const Tin*)a0.x, a0.xold, a0.xfin, (const Tsn*)a0.dxbuf, (Tin*)a0.dx, a0.Dn, a0.dkinv};
+    const RowsBwdArgs<Tin, Tsn> b1{(const Tin*)a1.x, a1.xold, a1.xfin, (const Tsn*)a1.dxbuf, (Tin*)a1.dx, a1.Dn, a1.dkinv};
     kern<<<grid, ROW_THREADS, sm, st>>>(p, b0, b1, gate, am, tfirst);
     return cudaGetLastError();
 }
@@ -39,12 +45,13 @@ static cudaError_t rows_bwd_one(const slotscan_params& p, int ntensors, const Ro
 
 template <int D>
 static cudaError_t replay_d(const slotscan_params& p, const void* x, const float* gate, const int* am, const int* tfirst,
-                            void* xbuf, float* xold, float* xfin, cudaStream_t st) {
+                            const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid,
+                            cudaStream_t st) {
     typedef __nv_bfloat16 bf;
-    ROWS_TYPES(return (replay_one<D, float, float>(p, x, gate, am, tfirst, xbuf, xold, xfin, st)),
-               return (replay_one<D, float, bf>(p, x, gate, am, tfirst, xbuf, xold, xfin, st)),
-               return (replay_one<D, bf, float>(p, x, gate, am, tfirst, xbuf, xold, xfin, st)),
-               return (replay_one<D, bf, bf>(p, x, gate, am, tfirst, xbuf, xold, xfin, st)))
+    ROWS_TYPES(return (replay_one<D, float, float>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)),
+               return (replay_one<D, float, bf>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)),
+               return (replay_one<D, bf, float>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)),
+               return (replay_one<D, bf, bf>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)))
 }
 
 template <int D>
@@ -58,9 +65,9 @@ static cudaError_t rows_bwd_d(const slotscan_params& p, int nt, const RowsBwdPtr
 }
 
 cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
-                       void* xbuf, float* xold, float* xfin, cudaStream_t st) {
+                       const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
-    SLOTSCAN_DISPATCH_D(D, e = (replay_d<DD>(p, x, gate, am, tfirst, xbuf, xold, xfin, st)));
+    SLOTSCAN_DISPATCH_D(D, e = (replay_d<DD>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)));
     return e;
 }
 
@@ -72,8 +79,9 @@ cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const Ro
 }
 
 void attrs_rows(slotscan_kernel_attr* out, int cap, int& n) {
-    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16>);
-    fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float>);
+    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);
+    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16,kinv>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, true>);
+    fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float, false>);
     fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16>);
     fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float>);
 }

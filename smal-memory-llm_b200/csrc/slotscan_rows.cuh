@@ -62,10 +62,29 @@ __device__ __forceinline__ void stage_chunk(const slotscan_params& p, int b, int
 }
 
 // ======================================================================================================
-template <int D, typename Tin, typename Tsn>
+// kinv / valid of a row from its float32 state: rsqrt(max(|X|^2, 1e-12)) and [|X|^2 > 1e-12]  [memlm_sh.py:474-475]
+// The rows of one warp walk their events independently, so the sum runs over the row's own LPR lanes only (`gmask`).
+template <int LPR>
+__device__ __forceinline__ float row_nsq(const float* X, unsigned gmask) {
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) a = fmaf(X[j], X[j], a);
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) a += __shfl_xor_sync(gmask, a, off);
+    return a;
+}
+template <int LPR>
+__device__ __forceinline__ unsigned row_group_mask() {
+    const unsigned lane = threadIdx.x & 31u;
+    return (LPR >= 32) ? FULL : (((1u << LPR) - 1u) << (LPR * (lane / LPR)));
+}
+
+// NORM: also emit kinv / valid of every snapshot row (keys only).  x0 (may be NULL): the rows the replay starts from.
+template <int D, typename Tin, typename Tsn, bool NORM>
 __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     const slotscan_params p, const Tin* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ am,
-    const int* __restrict__ tfirst, Tsn* __restrict__ xbuf, float* __restrict__ xold, float* __restrict__ xfin) {
+    const int* __restrict__ tfirst, const float* __restrict__ x0, Tsn* __restrict__ xbuf, float* __restrict__ xold,
+    float* __restrict__ xfin, float* __restrict__ kinv_out, uint8_t* __restrict__ valid_out) {
     constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
     __shared__ float s_g[RC];
     __shared__ unsigned long long s_mask[RPB];
@@ -81,14 +100,22 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     for (int j = 0; j < 8; j++) X[j] = 0.f;
     const size_t snap_stride = (size_t)H * N * D;                   // between consecutive snapshots of one sequence
     Tsn* snap = xbuf + (((size_t)b * NB) * H + h) * N * D + (size_t)n * D + c * 8;
+    // kinv / valid of snapshot j of this row live at norm_base + j * norm_stride (one lane per row writes them)
+    const size_t norm_stride = (size_t)H * N;
+    size_t norm_ix = (((size_t)b * NB) * H + h) * N + n;
 
     if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) {
-        if (live) {                                                  // never addressed: every snapshot is zero
+        if (live) {                                                  // never a candidate: the row stays zero
             for (int j = 0; j < NB; j++) st8(snap + j * snap_stride, X);
             st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+            if (NORM && c == 0) {
+                for (int j = 0; j < NB; j++) { kinv_out[norm_ix + j * norm_stride] = 1e6f; valid_out[norm_ix + j * norm_stride] = 0; }
+            }
         }
         return;
     }
+    if (x0 != nullptr && live) ld8(X, x0 + ((size_t)bh * N + n) * D + c * 8);   // state carried in from the preceding chunk
+    const unsigned gmask = row_group_mask<LPR>();
     int tsnap = 0;                                                   // next snapshot time (multiple of G)
     for (int t0 = 0; t0 < T; t0 += RC) {
         const int tc = min(RC, T - t0);
@@ -102,13 +129,27 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
             const unsigned long long mm = m >> i;                    // i < tc <= 64 here
             const int ih = mm ? i + __ffsll((long long)mm) - 1 : tc; // next token that writes this row
             const int tlast = t0 + min(ih, tc - 1);
-            for (; tsnap <= tlast; tsnap += G) { st8(snap, X); snap += snap_stride; }   // pre-write copies
+            if (NORM) {
+                if (tsnap <= tlast) {                                // the state is the same for every snapshot of this stretch
+                    const float nsq = row_nsq<LPR>(X, gmask);
+                    if (c == 0) {
+                        const float ki = rsqrtf(fmaxf(nsq, 1e-12f));
+                        const uint8_t va = nsq > 1e-12f ? 1 : 0;
+                        size_t o = norm_ix;
+                        for (int ts = tsnap; ts <= tlast; ts += G) { kinv_out[o] = ki; valid_out[o] = va; o += norm_stride; }
+                    }
+                }
+            }
+            for (; tsnap <= tlast; tsnap += G) {                     // pre-write copies
+                st8(snap, X);
+                snap += snap_stride; norm_ix += norm_stride;
+            }
             if (ih >= tc) break;
             const size_t ix = ((size_t)b * T + t0 + ih) * H + h;
             const float g = s_g[ih], omw = 1.f - g;
             float xv[8];
             ld8(xv, s_x + ih * D + c * 8);
-            st8(xold + ix * D + c * 8, X);
+            if (xold != nullptr) st8(xold + ix * D + c * 8, X);
 #pragma unroll
             for (int j = 0; j < 8; j++) X[j] = blend(X[j], xv[j], g, omw);
             i = ih + 1;
@@ -138,6 +179,7 @@ struct RowsBwdArgs {
     const Tsn* dxbuf;
     Tin* dx;
     float* Dn;       // this tensor's own D table: the address backward adds the two
+    const float* dkinv;   // (B,NB,H,N) gradient of the kinv output, or NULL: enters dX where the snapshot was taken
 };
 
 template <int D, typename Tin, typename Tsn>
@@ -152,6 +194,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
     const Tsn* __restrict__ dxbuf = A.dxbuf;
     Tin* __restrict__ dx = A.dx;
     float* __restrict__ Dn = A.Dn;
+    const float* __restrict__ dkinv = A.dkinv;
     constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
     extern __shared__ __align__(16) unsigned char dsm[];
     float* s_xo = reinterpret_cast<float*>(dsm);                                   // [RC][D] undo rows
@@ -181,10 +224,34 @@ __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
     const Tsn* dsnap0 = (dxbuf == nullptr) ? nullptr : dxbuf + (((size_t)b * NB) * H + h) * N * D + (size_t)n * D + c * 8;
     // the snapshot gradient of block jb is added when the walk passes t = jb * G; it is fetched one block ahead
     int jb = NB - 1;
-    float nxt[8];
+    float nxt[8], nxt_w = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++) nxt[j] = 0.f;
-    if (dsnap0 != nullptr && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+    const float* dki0 = (dkinv == nullptr) ? nullptr : dkinv + (((size_t)b * NB) * H + h) * N + n;
+    const size_t dki_stride = (size_t)H * N;
+    // snapshot gradient of block JB into nxt (and the kinv gradient of that snapshot row into nxt_w)
+#define RB_FETCH(JB)                                                                        \
+    if ((JB) >= 0 && (JB) * G >= tstop) {                                                   \
+        if (dsnap0 != nullptr) ld8(nxt, dsnap0 + (size_t)(JB) * snap_stride);               \
+        if (dki0 != nullptr) nxt_w = dki0[(size_t)(JB) * dki_stride];                       \
+    }
+    // dX += the gradients that arrive at the snapshot taken at this token (X is the pre-write state here): the snapshot
+    // gradient itself and, through kinv = rsqrt(max(|X|^2, 1e-12)), -kinv^3 dkinv X.  All lanes of the warp call.
+#define RB_ADD_SNAPSHOT(ON)                                                                 \
+    {                                                                                       \
+        float w_ = 0.f;                                                                     \
+        if (dki0 != nullptr) {                                                              \
+            float nsq_ = 0.f;                                                               \
+            _Pragma("unroll") for (int j = 0; j < 8; j++) nsq_ = fmaf(X[j], X[j], nsq_);    \
+            nsq_ = group_sum<LPR>(nsq_);                                                    \
+            const float ki_ = rsqrtf(fmaxf(nsq_, 1e-12f));                                  \
+            w_ = nsq_ > 1e-12f ? -(ki_ * ki_ * ki_) * nxt_w : 0.f;                          \
+        }                                                                                   \
+        if (ON) {                                                                           \
+            _Pragma("unroll") for (int j = 0; j < 8; j++) dX[j] += nxt[j] + w_ * X[j];      \
+        }                                                                                   \
+    }
+    RB_FETCH(jb)
 
     const int nchunk = (T + RC - 1) / RC;
     for (int ck = nchunk - 1; ck >= 0; ck--) {
@@ -240,12 +307,9 @@ __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
                         if (ACCUM) *dst += w; else *dst = w;
                     }
                     if (jb >= 0 && jb * G == t - 3) {                              // the group ended on a snapshot time
-                        if (t - 3 >= tstop) {
-#pragma unroll
-                            for (int j = 0; j < 8; j++) dX[j] += nxt[j];
-                        }
+                        RB_ADD_SNAPSHOT(t - 3 >= tstop)
                         jb--;
-                        if (dsnap0 != nullptr && jb >= 0 && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+                        RB_FETCH(jb)
                     }
                     i -= 4;
                     t -= 4;
@@ -273,15 +337,14 @@ __global__ void __launch_bounds__(ROW_THREADS) rows_bwd_kernel(
                 st8(dx + (((size_t)b * T + t) * H + h) * D + c * 8, a);
             }
             if (t == jb * G) {                                                     // pre-write state of block jb
-                if (on) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) dX[j] += nxt[j];
-                }
+                RB_ADD_SNAPSHOT(on)
                 jb--;
-                if (dsnap0 != nullptr && jb >= 0 && jb * G >= tstop) ld8(nxt, dsnap0 + (size_t)jb * snap_stride);
+                RB_FETCH(jb)
             }
         }
     }
+#undef RB_FETCH
+#undef RB_ADD_SNAPSHOT
 }
 
 }  // namespace slotscan

@@ -7,6 +7,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libslotscan.so")
 
 F32, BF16 = 0, 1
+ABI_VERSION = 2
 
 ERRORS = {-1: "a required pointer is NULL", -2: "unsupported shape", -3: "unknown dtype code",
           -4: "a pointer is not 16-byte aligned", -5: "mode not implemented by this entry point",
@@ -22,6 +23,12 @@ class Params(ctypes.Structure):
 class Log(ctypes.Structure):
     """slotscan_log of include/slotscan.h."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")]
+
+
+class FwdExtra(ctypes.Structure):
+    """slotscan_fwd_extra of include/slotscan.h."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("K0", "V0", "o0", "nsq0", "nsqfin", "kinv", "valid")] + \
+               [("no_undo_log", ctypes.c_int32)]
 
 
 class EpilogueParams(ctypes.Structure):
@@ -61,6 +68,10 @@ def lib():
         L.slotscan_abi_version.restype = ci
         L.slotscan_check.argtypes = [PP]
         L.slotscan_hard_fwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, vp, vp, LP, vp]
+        L.slotscan_hard_fwd_ex.argtypes = [PP, vp, vp, vp, vp, vp, vp, vp, vp, LP, ctypes.POINTER(FwdExtra), vp]
+        L.slotscan_hard_fwd_ex.restype = ci
+        L.slotscan_hard_bwd_ex.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
+        L.slotscan_hard_bwd_ex.restype = ci
         L.slotscan_hard_bwd_scratch_bytes.argtypes = [PP]
         L.slotscan_hard_bwd_scratch_bytes.restype = sz
         L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
@@ -82,7 +93,7 @@ def lib():
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]
         for f in ("slotscan_profile_enable", "slotscan_profile_read", "slotscan_check", "slotscan_hard_fwd", "slotscan_hard_bwd", "slotscan_query_attrs"):
             getattr(L, f).restype = ci
-        assert L.slotscan_abi_version() == 1, "libslotscan.so / Python host ABI mismatch"
+        assert L.slotscan_abi_version() == ABI_VERSION, "libslotscan.so / Python host ABI mismatch"
         _lib = L
     return _lib
 

@@ -12,10 +12,12 @@ import torch
 from . import _lib
 
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+# position of each output of hard_fwd
+OUT = ("kbuf", "vbuf", "addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold", "nsqfin", "kinv", "valid")
 
 
 def _ptr(t):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+    return None if t is None or t.numel() == 0 else ctypes.c_void_p(t.data_ptr())
 
 
 def _stream(dev):
@@ -35,58 +37,70 @@ def _require_cuda(*ts):
                                "(the CPU oracle lives in the test tree)")
 
 
-@torch.library.custom_op("slotscan::hard_fwd", mutates_args=())
-def hard_fwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
-             temp: torch.Tensor, N: int, G: int, hard_gate: bool, eps: float, occ_bin: bool,
-             snap_bf16: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
-                                       torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
-                                       torch.Tensor]:
-    """k, q, v: contiguous f32 or bf16 (same dtype); gate, fr, temp: contiguous f32.
-    Returns kbuf, vbuf, then the log: addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold (include/slotscan.h)."""
-    _require_cuda(k, q, v, gate, fr, temp)
+def _addr(t):
+    return 0 if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _fwd_shapes(k, v, N, G, snap_bf16, want_norm, undo_log, new):
+    """The output tensors of hard_fwd; `new(shape, dtype)` allocates (real or fake).  Outputs that were not asked
+    for have zero elements."""
     B, T, H, DK = k.shape
     DV = v.shape[-1]
     NB = (T + G - 1) // G
-    dev = k.device
     sdt = torch.bfloat16 if snap_bf16 else torch.float32
-    e = lambda *s, dt=torch.float32: torch.empty(*s, device=dev, dtype=dt)
-    kbuf, vbuf = e(B, NB, H, N, DK, dt=sdt), e(B, NB, H, N, DV, dt=sdt)
-    addr, oold = e(B, T, H, dt=torch.int32), e(B, T, H)
-    kold, vold = e(B, T, H, DK), e(B, T, H, DV)
-    kfin, vfin, ofin = e(B * H, N, DK), e(B * H, N, DV), e(B * H, N)
-    tfirst = e(B * H, N, dt=torch.int32)
-    kiold = e(B, T, H)
-    p = _params(k, v, gate, fr, N, G, hard_gate, eps, occ_bin, sdt)
-    log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold)))
+    f32, i32 = torch.float32, torch.int32
+    return (new((B, NB, H, N, DK), sdt), new((B, NB, H, N, DV), sdt), new((B, T, H), i32), new((B, T, H), f32),
+            new((B, T, H, DK) if undo_log else (0,), f32), new((B, T, H, DV) if undo_log else (0,), f32),
+            new((B * H, N, DK), f32), new((B * H, N, DV), f32), new((B * H, N), f32), new((B * H, N), i32),
+            new((B, T, H), f32), new((B * H, N), torch.float64),
+            new((B, NB, H, N) if want_norm else (0,), f32), new((B, NB, H, N) if want_norm else (0,), torch.uint8))
+
+
+@torch.library.custom_op("slotscan::hard_fwd", mutates_args=())
+def hard_fwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
+             temp: torch.Tensor, K0: Optional[torch.Tensor], V0: Optional[torch.Tensor], o0: Optional[torch.Tensor],
+             nsq0: Optional[torch.Tensor], N: int, G: int, hard_gate: bool, eps: float, occ_bin: bool,
+             snap_bf16: bool, want_norm: bool, undo_log: bool
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                        torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """k, q, v: contiguous f32 or bf16 (same dtype); gate, fr, temp: contiguous f32.  K0, V0, o0 (f32), nsq0 (f64):
+    the state carried in from the preceding chunk, or None.  Returns, in the order of `OUT`: kbuf, vbuf, the log
+    (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold; include/slotscan.h), nsqfin, kinv, valid."""
+    _require_cuda(k, q, v, gate, fr, temp, K0, V0, o0, nsq0)
+    dev = k.device
+    out = _fwd_shapes(k, v, N, G, snap_bf16, want_norm, undo_log, lambda s, dt: torch.empty(s, device=dev, dtype=dt))
+    kbuf, vbuf, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold, nsqfin, kinv, valid = out
+    p = _params(k, v, gate, fr, N, G, hard_gate, eps, occ_bin, kbuf.dtype)
+    log = _lib.Log(*(_addr(t) for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold)))
+    c = lambda t, dt: None if t is None else t.contiguous().to(dt)
+    K0, V0, o0, nsq0 = c(K0, torch.float32), c(V0, torch.float32), c(o0, torch.float32), c(nsq0, torch.float64)
+    ex = _lib.FwdExtra(_addr(K0), _addr(V0), _addr(o0), _addr(nsq0), _addr(nsqfin), _addr(kinv), _addr(valid),
+                       0 if undo_log else 1)
     with torch.cuda.device(dev):
-        rc = _lib.lib().slotscan_hard_fwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
-                                          _ptr(kbuf), _ptr(vbuf), ctypes.byref(log), _stream(dev))
-    _lib.check(rc, "slotscan_hard_fwd")
-    return kbuf, vbuf, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold
+        rc = _lib.lib().slotscan_hard_fwd_ex(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
+                                             _ptr(kbuf), _ptr(vbuf), ctypes.byref(log), ctypes.byref(ex), _stream(dev))
+    _lib.check(rc, "slotscan_hard_fwd_ex")
+    return out
 
 
 @hard_fwd.register_fake
-def _(k, q, v, gate, fr, temp, N, G, hard_gate, eps, occ_bin, snap_bf16):
-    B, T, H, DK = k.shape
-    DV = v.shape[-1]
-    NB = (T + G - 1) // G
-    sdt = torch.bfloat16 if snap_bf16 else torch.float32
-    e = lambda *s, dt=torch.float32: k.new_empty(s, dtype=dt)
-    return (e(B, NB, H, N, DK, dt=sdt), e(B, NB, H, N, DV, dt=sdt), e(B, T, H, dt=torch.int32), e(B, T, H),
-            e(B, T, H, DK), e(B, T, H, DV), e(B * H, N, DK), e(B * H, N, DV), e(B * H, N), e(B * H, N, dt=torch.int32),
-            e(B, T, H))
+def _(k, q, v, gate, fr, temp, K0, V0, o0, nsq0, N, G, hard_gate, eps, occ_bin, snap_bf16, want_norm, undo_log):
+    return _fwd_shapes(k, v, N, G, snap_bf16, want_norm, undo_log, lambda s, dt: k.new_empty(s, dtype=dt))
 
 
 @torch.library.custom_op("slotscan::hard_bwd", mutates_args=())
 def hard_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
              temp: torch.Tensor, addr: torch.Tensor, oold: torch.Tensor, kold: torch.Tensor, vold: torch.Tensor,
              kfin: torch.Tensor, vfin: torch.Tensor, ofin: torch.Tensor, tfirst: torch.Tensor, kiold: torch.Tensor,
-             dkbuf: Optional[torch.Tensor], dvbuf: Optional[torch.Tensor], N: int, G: int, hard_gate: bool,
-             eps: float, occ_bin: bool, snap_bf16: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor,
-                                                                   torch.Tensor, torch.Tensor, torch.Tensor]:
+             dkbuf: Optional[torch.Tensor], dvbuf: Optional[torch.Tensor], dkinv: Optional[torch.Tensor], N: int, G: int,
+             hard_gate: bool, eps: float, occ_bin: bool, snap_bf16: bool
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns dk, dq, dv (dtype of k), dgate (B,T,H) f32, dfr (shape of fr) f32, dtemp (1,) f32.
-    With q None, dq holds the search-path part, which the kernel has already added into dk."""
+    With q None, dq holds the search-path part, which the kernel has already added into dk.
+    dkinv: the gradient that reached the kinv output of the forward (B,NB,H,N) f32, or None."""
     _require_cuda(k, v)
+    if kold.numel() == 0 or vold.numel() == 0:
+        raise RuntimeError("slotscan: this forward was run without its undo log (forward-only mode); it has no backward")
     dev = k.device
     sdt = torch.bfloat16 if snap_bf16 else torch.float32
     p = _params(k, v, gate, fr, N, G, hard_gate, eps, occ_bin, sdt)
@@ -99,35 +113,38 @@ def hard_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: 
     dtemp = torch.empty(1, device=dev, dtype=torch.float32)
     log = _lib.Log(*(t.data_ptr() for t in (addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold)))
     with torch.cuda.device(dev):
-        rc = L.slotscan_hard_bwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
-                                 ctypes.byref(log), _ptr(dkbuf), _ptr(dvbuf), _ptr(scratch), nbytes, _ptr(dk), _ptr(dq),
-                                 _ptr(dv), _ptr(dgate), _ptr(dfr), _ptr(dtemp), _stream(dev))
-    _lib.check(rc, "slotscan_hard_bwd")
+        rc = L.slotscan_hard_bwd_ex(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
+                                    ctypes.byref(log), _ptr(dkbuf), _ptr(dvbuf), _ptr(dkinv), _ptr(scratch), nbytes,
+                                    _ptr(dk), _ptr(dq), _ptr(dv), _ptr(dgate), _ptr(dfr), _ptr(dtemp), _stream(dev))
+    _lib.check(rc, "slotscan_hard_bwd_ex")
     return dk, dq, dv, dgate, dfr, dtemp
 
 
 @hard_bwd.register_fake
-def _(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold, dkbuf, dvbuf, N, G, hard_gate,
-      eps, occ_bin, snap_bf16):
+def _(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold, dkbuf, dvbuf, dkinv, N, G,
+      hard_gate, eps, occ_bin, snap_bf16):
     f = lambda t: t.new_empty(t.shape, dtype=torch.float32)
     return torch.empty_like(k), torch.empty_like(k), torch.empty_like(v), f(gate), f(fr), gate.new_empty(1)
 
 
 def _setup(ctx, inputs, output):
-    k, q, v, gate, fr, temp, N, G, hard_gate, eps, occ_bin, snap_bf16 = inputs
-    ctx.save_for_backward(k, q, v, gate, fr, temp, *output[2:])
+    k, q, v, gate, fr, temp, K0, V0, o0, nsq0, N, G, hard_gate, eps, occ_bin, snap_bf16, want_norm, undo_log = inputs
+    ctx.save_for_backward(k, q, v, gate, fr, temp, *output[2:11])
     ctx.meta = (N, G, hard_gate, eps, occ_bin, snap_bf16)
     ctx.set_materialize_grads(False)
 
 
-def _backward(ctx, dkbuf, dvbuf, *unused):
+def _backward(ctx, *grads):
+    dkbuf, dvbuf, dkinv = grads[0], grads[1], grads[12]
     k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst, kiold = ctx.saved_tensors
     N, G, hard_gate, eps, occ_bin, snap_bf16 = ctx.meta
     sdt = torch.bfloat16 if snap_bf16 else torch.float32
-    c = lambda g: None if g is None else g.contiguous().to(sdt)
+    c = lambda g, dt: None if g is None else g.contiguous().to(dt)
     dk, dq, dv, dgate, dfr, dtemp = hard_bwd(k, q, v, gate, fr, temp, addr, oold, kold, vold, kfin, vfin, ofin, tfirst,
-                                             kiold, c(dkbuf), c(dvbuf), N, G, hard_gate, eps, occ_bin, snap_bf16)
-    return dk, (None if q is None else dq), dv, dgate, dfr, dtemp, None, None, None, None, None, None
+                                             kiold, c(dkbuf, sdt), c(dvbuf, sdt), c(dkinv, torch.float32), N, G, hard_gate,
+                                             eps, occ_bin, snap_bf16)
+    # no gradient for the carried-in state (K0, V0, o0, nsq0) nor for the integer / flag arguments
+    return (dk, (None if q is None else dq), dv, dgate, dfr, dtemp) + (None,) * 12
 
 
 hard_fwd.register_autograd(_backward, setup_context=_setup)

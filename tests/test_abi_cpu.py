@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     assert len(names) >= 10, names
     for n in names:
         assert hasattr(L, n), "libslotscan.so does not export %s" % n
-    assert L.slotscan_abi_version() == 1
+    assert L.slotscan_abi_version() == 2
 
 
 def test_argument_validation_needs_no_gpu():
@@ -50,6 +50,7 @@ def test_argument_validation_needs_no_gpu():
     assert L.slotscan_hard_bwd_scratch_bytes(ctypes.byref(ok)) >= 4 * 2 * 3 * 16 * 12
     # NULL pointers are refused before any launch
     assert L.slotscan_hard_fwd(ctypes.byref(ok), None, None, None, None, None, None, None, None, None, None) == -1
+    assert L.slotscan_hard_fwd_ex(ctypes.byref(ok), None, None, None, None, None, None, None, None, None, None, None) == -1
 
 
 def test_python_host_mirrors_reference_signatures():
@@ -112,10 +113,15 @@ def test_custom_op_has_fake_kernel_for_compiled_callers():
     k = torch.empty(2, 16, 3, 32, device="meta")
     g = torch.empty(2, 16, 3, device="meta")
     t1 = torch.empty(1, device="meta")
-    out = torch.ops.slotscan.hard_fwd(k, k, k, g, g, t1, 24, 8, False, 1e-4, True, True)
+    out = torch.ops.slotscan.hard_fwd(k, k, k, g, g, t1, None, None, None, None, 24, 8, False, 1e-4, True, True, True, True)
     assert out[0].shape == (2, 2, 3, 24, 32) and out[0].dtype == torch.bfloat16 and out[2].dtype == torch.int32
-    gr = torch.ops.slotscan.hard_bwd(k, k, k, g, g, t1, *out[2:], out[0], out[1], 24, 8, False, 1e-4, True, True)
+    assert out[11].dtype == torch.float64 and out[12].shape == (2, 2, 3, 24) and out[13].dtype == torch.uint8
+    gr = torch.ops.slotscan.hard_bwd(k, k, k, g, g, t1, *out[2:11], out[0], out[1], out[12], 24, 8, False, 1e-4, True, True)
     assert gr[0].shape == k.shape and gr[5].shape == (1,)
+    # forward-only form: no undo log, no norms -> those outputs are empty
+    out = torch.ops.slotscan.hard_fwd(k, None, k, g, g, t1, out[6], out[7], out[8], out[11], 24, 8, False, 1e-4, True,
+                                      False, False, False)
+    assert out[4].numel() == 0 and out[5].numel() == 0 and out[12].numel() == 0 and out[0].dtype == torch.float32
 
 
 def test_epilogue_validation_and_host_names():

@@ -1,0 +1,198 @@
+"""GPU tests of the fused writer hand-over and of state carry across calls.
+
+  write_memory      scan + kinv / valid emitted by the scan kernels (no pass over the snapshots), and its backward with
+                    the kinv gradient entering inside the reverse row scan   [memlm_sh.py:454-475]
+  state carry       a sequence scanned in chunks == the same sequence scanned in one call; oracle parity on a prefix
+  long context      B=8 sequences streamed chunk by chunk with `_fq(.,8,128)` storage ("int8 per row"): peak memory
+                    does not depend on the total length
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.scan_cases import address_report, make_inputs, rel_to_max
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _S():
+    import slotscan_b200 as S
+    return S
+
+
+@pytest.mark.parametrize("dist,N,T", [("bench", 192, 256), ("fill", 96, 400), ("gates01:3", 40, 203)],
+                         ids=["bench", "fill_n96", "gates01_TmodG"])
+def test_write_memory_fp32_values_and_gradients(dist, N, T):
+    """float32 mode: (kbuf, vbuf, kinv, valid) and every input gradient against the float64 oracle, with upstream
+    gradients on the snapshots AND on kinv."""
+    S = _S()
+    B, H, D, G = 2, 3, 64, 8
+    inp = make_inputs(dist, B, T, H, D, D, seed=21)
+    kw = dict(N=N, temp=inp["temp"], G=G, hard=True, q=inp["q"], occ_bin=True)
+    ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dtype=np.float64, **kw)
+    ki_o, va_o = O.epilogue(ref["kbuf"])
+    leaves = {n: inp[n].to(DEV).requires_grad_() for n in ("k", "q", "v", "gate", "fr")}
+    temp = torch.tensor(float(inp["temp"]), device=DEV, requires_grad=True)
+    kb, vb, kinv, valid = S.write_memory(leaves["k"], leaves["v"], leaves["gate"], leaves["fr"], N, temp, G=G,
+                                         q=leaves["q"], occ_bin=True, out_dtype=torch.float32)
+    lg = S.scan_with_log(*(inp[n].to(DEV) for n in ("k", "v", "gate", "fr")), N, inp["temp"], G=G, q=inp["q"].to(DEV),
+                         occ_bin=True)
+    ok, nflip, nbad, keep = address_report(lg["addr"].cpu().numpy(), ref["addr"], ref["margin"])
+    assert ok and keep.all(), (nflip, nbad)
+    assert np.abs(kb.detach().cpu().numpy() - ref["kbuf"]).max() < 1e-5
+    assert np.abs(vb.detach().cpu().numpy() - ref["vbuf"]).max() < 1e-5
+    assert np.array_equal(valid.cpu().numpy(), va_o)
+    kin = kinv.detach().cpu().numpy()
+    assert np.abs(kin[va_o] / ki_o[va_o] - 1).max() < 1e-5
+    # backward: loss = <kbuf, wk> + <vbuf, wv> + <kinv, wi> over the valid rows
+    gen = torch.Generator().manual_seed(3)
+    wk, wv = torch.randn(kb.shape, generator=gen), torch.randn(vb.shape, generator=gen)
+    wi = torch.randn(kinv.shape, generator=gen) * torch.from_numpy(va_o)
+    ((kb * wk.to(DEV)).sum() + (vb * wv.to(DEV)).sum() + (kinv * wi.to(DEV)).sum()).backward()
+    # oracle: d kinv / d kbuf = -kinv^3 K on the valid rows, folded into the snapshot gradient
+    wk_tot = wk.double().numpy() + (-(ki_o ** 3) * wi.double().numpy() * va_o)[..., None] * ref["kbuf"]
+    gr = O.scan_bwd(inp["k"], inp["v"], inp["gate"], inp["fr"], dkbuf=wk_tot, dvbuf=wv.numpy(), detach_addr=True,
+                    dtype=np.float64, **kw)
+    for n, t in (("dk", leaves["k"]), ("dq", leaves["q"]), ("dv", leaves["v"]), ("dgate", leaves["gate"]),
+                 ("dfr", leaves["fr"]), ("dtemp", temp)):
+        e = rel_to_max(t.grad.cpu().numpy().reshape(gr[n].shape), gr[n])
+        assert e < 1e-4, (n, e)
+
+
+def test_write_memory_bf16_matches_reference_order_of_operations():
+    """bf16 hand-over: snapshots are the float32 state rounded once, kinv / valid come from the float32 state (as
+    memlm_sh.py:474-475 takes them from the float32 kbuf before the cast), not from the rounded copy."""
+    S = _S()
+    B, T, H, N, D, G = 2, 512, 6, 192, 128, 8
+    inp = make_inputs("bench", B, T, H, D, D, seed=4)
+    for n in ("k", "q", "v"):
+        inp[n] = inp[n].to(torch.bfloat16)
+    d = lambda x: x.to(DEV)
+    with torch.no_grad():
+        kb, vb, kinv, valid = S.write_memory(d(inp["k"]), d(inp["v"]), d(inp["gate"]), d(inp["fr"]), N, 16.0, G=G,
+                                             q=d(inp["q"]), occ_bin=True, out_dtype=torch.bfloat16)
+        kb32, vb32 = S.kv_scan_g(d(inp["k"]), d(inp["v"]), d(inp["gate"]), d(inp["fr"]), N, 16.0, G=G, hard=True,
+                                 detach_addr=True, q=d(inp["q"]), occ_bin=True, out_dtype=torch.float32)
+    assert kb.dtype == torch.bfloat16 and torch.equal(kb, kb32.to(torch.bfloat16)) and torch.equal(vb, vb32.to(torch.bfloat16))
+    nsq = kb32.double().pow(2).sum(-1)
+    assert torch.equal(valid, nsq > 1e-12)
+    want = torch.rsqrt(nsq.clamp_min(1e-12))
+    assert ((kinv.double() / want - 1).abs()[valid]).max().item() < 1e-5
+    assert not valid[:, 0].any()                                       # snapshot 0 is the empty memory
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("dist,T,chunk", [("bench", 4096, 512), ("fill", 1536, 256), ("clustered", 1000, 104)],
+                         ids=["bench_T4096", "fill_T1536", "clustered_T1000"])
+def test_chunked_scan_equals_one_call(dist, T, chunk, dtype):
+    """State carry: scanning a sequence chunk by chunk, the slot state (keys, values, occupancy and the squared key
+    norms) handed from call to call, gives the addresses and the snapshots of one call over the whole sequence, bit
+    for bit.  (The first token of a chunk scores against freshly computed dot products, a token in mid-scan against
+    dot products updated by linearity: the two can differ in the last bit of a score, so a tie within float32
+    round-off could in principle resolve differently; the seeded inputs here have none.)"""
+    S = _S()
+    B, H, N, D, G = 2, 6, 192, 128, 8
+    inp = make_inputs(dist, B, T, H, D, D, seed=12)
+    dev = {n: inp[n].to(DEV, dtype if n in ("k", "q", "v") else torch.float32) for n in ("k", "q", "v", "gate", "fr")}
+    kw = dict(G=G, occ_bin=True, out_dtype=dtype)
+    one = S.scan_with_log(dev["k"], dev["v"], dev["gate"], dev["fr"], N, inp["temp"], q=dev["q"], want_norm=True, **kw)
+    state, kbs, vbs, addrs, kis = None, [], [], [], []
+    for t0 in range(0, T, chunk):
+        sl = slice(t0, min(t0 + chunk, T))
+        c = S.scan_with_log(dev["k"][:, sl], dev["v"][:, sl], dev["gate"][:, sl], dev["fr"][:, sl], N, inp["temp"],
+                            q=dev["q"][:, sl], state=state, want_norm=True, undo_log=False, **kw)
+        state = (c["kfin"], c["vfin"], c["ofin"], c["nsqfin"])
+        kbs.append(c["kbuf"]); vbs.append(c["vbuf"]); addrs.append(c["addr"]); kis.append(c["kinv"])
+        assert c["kold"].numel() == 0
+    assert torch.equal(torch.cat(addrs, 1), one["addr"])
+    assert torch.equal(torch.cat(kbs, 1), one["kbuf"]) and torch.equal(torch.cat(vbs, 1), one["vbuf"])
+    assert torch.equal(torch.cat(kis, 1), one["kinv"])
+    for n, i in (("kfin", 0), ("vfin", 1), ("ofin", 2), ("nsqfin", 3)):
+        assert torch.equal(state[i], one[n]), n
+    assert int(one["addr"].max()) >= (100 if dist != "bench" else 5)   # the carried state spans many rows
+    # without the carried norms they are summed again from the keys: same addresses here, values within float32 round-off
+    state = None
+    for t0 in range(0, T, chunk):
+        sl = slice(t0, min(t0 + chunk, T))
+        c = S.scan_with_log(dev["k"][:, sl], dev["v"][:, sl], dev["gate"][:, sl], dev["fr"][:, sl], N, inp["temp"],
+                            q=dev["q"][:, sl], state=state, undo_log=False, **kw)
+        state = (c["kfin"], c["vfin"], c["ofin"])
+    assert (state[0] - one["kfin"]).abs().max().item() < 1e-5 and (state[1] - one["vfin"]).abs().max().item() < 1e-5
+
+
+def test_chunked_scan_prefix_matches_oracle():
+    """The chunked scan against the float64 oracle run over the whole prefix in one go (float32 mode, 1e-5)."""
+    S = _S()
+    B, T, H, N, D, G, chunk = 1, 768, 4, 96, 64, 8, 128
+    inp = make_inputs("gates01:6", B, T, H, D, D, seed=33)
+    ref = O.scan_fwd(inp["k"], inp["v"], inp["gate"], inp["fr"], N=N, temp=inp["temp"], G=G, hard=True, q=inp["q"],
+                     occ_bin=True, dtype=np.float64)
+    st = S.StreamingScan(N, inp["temp"], G=G, occ_bin=True, out_dtype=torch.float32)
+    outs = [st.push(*(inp[n][:, t0:t0 + chunk].to(DEV) for n in ("k", "v", "gate", "fr")), q=inp["q"][:, t0:t0 + chunk].to(DEV))
+            for t0 in range(0, T, chunk)]
+    kb = torch.cat([o[0] for o in outs], 1).cpu().numpy()
+    vb = torch.cat([o[1] for o in outs], 1).cpu().numpy()
+    assert int(ref["addr"].max()) > 64
+    assert np.abs(kb - ref["kbuf"]).max() < 1e-5 and np.abs(vb - ref["vbuf"]).max() < 1e-5
+    assert np.abs(st.state[0].cpu().numpy().reshape(ref["kfin"].shape) - ref["kfin"]).max() < 1e-5
+    ki_o, va_o = O.epilogue(ref["kbuf"])
+    assert np.array_equal(torch.cat([o[3] for o in outs], 1).cpu().numpy(), va_o)
+
+
+def _device_chunk(gen, B, Tc, H, D):
+    """One chunk of the benchmark's seeded distributions, drawn on the device (a long context never sits in host memory)."""
+    r = lambda *s: torch.randn(*s, device=DEV, generator=gen)
+    unit = lambda x: x / x.norm(dim=-1, keepdim=True)
+    k, v = unit(r(B, Tc, H, D)), 0.5 * r(B, Tc, H, D)
+    g = torch.sigmoid(r(B, Tc, H))
+    fr = 0.1 * r(B, Tc, H)
+    q = unit(r(B, Tc, H, D))
+    return k, v, g, fr, q
+
+
+def _stream(S, T, chunk, qbits, check_prefix=0):
+    B, H, N, D, G = 8, 6, 192, 128, 8
+    gen = torch.Generator(device=DEV).manual_seed(0)
+    st = S.StreamingScan(N, 16.0, G=G, occ_bin=True, out_dtype=torch.float32 if check_prefix else torch.bfloat16,
+                         qbits=qbits, qgroup=128)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    keep, acc = [], 0.0
+    for t0 in range(0, T, chunk):
+        k, v, g, fr, q = _device_chunk(gen, B, chunk, H, D)
+        kq, vq, kinv, valid = st.push(k, v, g, fr, q=q)
+        acc += float(valid.sum())                                      # the consumer of the chunk (a reader layer) goes here
+        if t0 < check_prefix:
+            keep.append(tuple(x.cpu() for x in (k, v, g, fr, q, kq, vq, valid)))
+        del k, v, g, fr, q, kq, vq, kinv, valid
+    torch.cuda.synchronize()
+    return torch.cuda.max_memory_allocated(), keep, acc, st
+
+
+def test_config3_long_context_streams_in_constant_memory():
+    """Config 3: B=8, forward only, `_fq(., 8, group 128)` storage (one absmax scale per 128-wide row, 256 levels: the
+    reference's per-row 8-bit format), streamed in 4,096-token chunks.  Peak device memory at T = 131,072 equals the
+    peak at T = 16,384; the first 4,096 tokens are checked against the oracle at the same quantisation."""
+    S = _S()
+    chunk = 4096
+    peak_short, _, _, _ = _stream(S, 4 * chunk, chunk, qbits=8)
+    peak_long, _, acc, st = _stream(S, 131072, chunk, qbits=8)
+    print("config 3: peak device memory %.2f GB at T=16,384 and %.2f GB at T=131,072" % (peak_short / 1e9, peak_long / 1e9))
+    assert st.tokens == 131072 and acc > 0
+    assert peak_long <= peak_short * 1.01
+    # parity of the first chunk(s): float32 hand-over so the quantiser's output can be compared bit for bit
+    _, keep, _, _ = _stream(S, 2 * 1024, 1024, qbits=8, check_prefix=2048)
+    k, v, g, fr, q = (torch.cat([c[i] for c in keep], 1) for i in range(5))
+    kq, vq, valid = (torch.cat([c[i] for c in keep], 1) for i in (5, 6, 7))
+    ref = O.scan_fwd(k, v, g, fr, N=192, temp=16.0, G=8, hard=True, q=q, occ_bin=True, dtype=np.float64)
+    want_k = O.fq(ref["kbuf"].astype(np.float32), 8, 128)
+    want_v = O.fq(ref["vbuf"].astype(np.float32), 8, 128)
+    # the quantiser floors: a float32 state that differs from the oracle's in the last bit can land one level away
+    step_k = np.abs(ref["kbuf"]).max(-1, keepdims=True) / 128 + 1e-6
+    step_v = np.abs(ref["vbuf"]).max(-1, keepdims=True) / 128 + 1e-6
+    dk, dv = np.abs(kq.numpy() - want_k), np.abs(vq.numpy() - want_v)
+    assert (dk <= step_k * 1.001).all() and (dv <= step_v * 1.001).all()
+    assert (dk > 1e-6).mean() < 1e-3 and (dv > 1e-6).mean() < 1e-3     # all but a few elements are identical
+    assert np.array_equal(valid.numpy(), O.epilogue(want_k.astype(np.float64))[1])
