@@ -158,6 +158,34 @@ int slotscan_hard_bwd_noalloc(const slotscan_params* p, const void* k, const voi
                               const void* dvbuf, void* dk, void* dq, void* dv, float* dgate, float* dfr, float* dtemp,
                               void* stream);
 
+/* The general scan: every mode of kv_scan_g (gqa25/slotkern_kvg.py:257) -- soft or hard address, address gradient
+ * attached to the stored keys or detached, hard gate, either occupancy penalty, scalar or per-token fr, q or NULL.
+ * [replaces the Triton kernels _kvfwd (gqa25/slotkern_kvt.py:43-119) and _kvbwd_g (gqa25/slotkern_kvg.py:41-205), which
+ * the reference falls back to for everything but its hard + detached training mode (slotkern_cuda.py:540-542).]
+ * The hard + detached mode has its own, much faster kernels (slotscan_hard_*); this entry point exists so that no
+ * argument combination of the reference call is without a CUDA implementation.  One CTA per (sequence, head).
+ *   base.snap_dtype must be SLOTSCAN_F32: kbuf, vbuf and obuf (B,NB,H,N) are float32 -- they are the checkpoints the
+ *   backward replays from.  Any 1 <= DK, DV <= 128; N * (DK + DV + 8) floats must fit one CTA's shared memory
+ *   (N <= 192 at 128 + 128).
+ * slotscan_dense_fwd: addr (B,T,H) int32 = argmax of each token's address, kfin / vfin / ofin = the final state; each
+ * of the four may be NULL.
+ * slotscan_dense_bwd: needs the forward's kbuf, vbuf, obuf and scratch of slotscan_dense_bwd_scratch_bytes (G states
+ * per (sequence, head)); dkbuf / dvbuf float32, either may be NULL.  Outputs as slotscan_hard_bwd. */
+typedef struct {
+    slotscan_params base;
+    int32_t hard;           /* forward address: 1 = one-hot argmax, 0 = the softmax over the candidate rows */
+    int32_t detach_addr;    /* 1 = the address reads the stored keys as constants: no gradient into them from the match */
+} slotscan_dense_params;
+int slotscan_dense_check(const slotscan_dense_params* p);
+int slotscan_dense_fwd(const slotscan_dense_params* p, const void* k, const void* q, const void* v, const float* gate,
+                       const float* fr, const float* temp, float* kbuf, float* vbuf, float* obuf, int32_t* addr,
+                       float* kfin, float* vfin, float* ofin, void* stream);
+size_t slotscan_dense_bwd_scratch_bytes(const slotscan_dense_params* p);
+int slotscan_dense_bwd(const slotscan_dense_params* p, const void* k, const void* q, const void* v, const float* gate,
+                       const float* fr, const float* temp, const float* kbuf, const float* vbuf, const float* obuf,
+                       const float* dkbuf, const float* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq,
+                       void* dv, float* dgate, float* dfr, float* dtemp, void* stream);
+
 /* Writer epilogue and storage quantiser over emitted snapshot rows, one streaming pass.
  * [replaces memlm_sh.py:464-475 (nsq = sum kbuf^2 in fp32, kinv = rsqrt(max(nsq, 1e-12)), valid = nsq > 1e-12, cast of
  * the snapshots to the model dtype) and memlm_sh.py:221-234 (_fq, _quantize_mem).]
@@ -222,6 +250,12 @@ typedef struct {
 } slotscan_kernel_time;
 int slotscan_profile_enable(int on);
 int slotscan_profile_read(slotscan_kernel_time* out, int cap);
+
+/* Kernels of this library never wait without a limit: a wait on an asynchronous copy that does not complete within
+ * about 0.2 s makes the kernel return early and raises a flag.  This call synchronises the current device and returns
+ * 1 if that happened since the last call (the results of that launch are then incomplete), 0 if not, -1 on a CUDA error.
+ * [No counterpart in the reference, whose kernels use no asynchronous copies.] */
+int slotscan_device_status(void);
 
 int slotscan_abi_version(void);
 

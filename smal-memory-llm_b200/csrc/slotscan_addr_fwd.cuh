@@ -26,11 +26,6 @@ constexpr int AF_CWARPS = 4;                // column warps: each owns a quarter
 constexpr int AF_THREADS = 32 * (AF_CWARPS + 1);   // + warp 0, the resolver
 constexpr int AF_WARPS = AF_THREADS / 32;
 
-__device__ __forceinline__ unsigned ord_key(float f) {    // monotone float -> unsigned
-    const unsigned u = __float_as_uint(f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
 // 8 elements of a token stream held in registers between the global load and the shared-memory store
 template <typename T> struct Pre8;
 template <> struct Pre8<float> {
@@ -113,7 +108,7 @@ __device__ __forceinline__ void af_token_consts(const Ts* __restrict__ qrow, con
 
 // RPL = row slots per lane (N <= 32 * RPL); CARRY: the scan starts from a state carried in from a preceding chunk
 template <int DK, int RPL, bool OCCB, bool CARRY, typename Tin>
-__global__ void __launch_bounds__(AF_THREADS) addr_fwd_direct_kernel(
+__global__ void __launch_bounds__(AF_THREADS, (RPL <= 2 ? 3 : 1)) addr_fwd_direct_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const Tin* __restrict__ k, const float* __restrict__ gate,
     const float* __restrict__ fr, const float* __restrict__ temp_p, int* __restrict__ am_out,
     float* __restrict__ oold_out, float* __restrict__ kiold_out, float* __restrict__ ofin, int* __restrict__ tfirst,

@@ -79,6 +79,11 @@ __device__ __forceinline__ void best(float& z, int& i, float z2, int i2) {
     if (z2 > z || (z2 == z && i2 < i)) { z = z2; i = i2; }
 }
 
+__device__ __forceinline__ unsigned ord_key(float f) {    // monotone float -> unsigned
+    const unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 __device__ __forceinline__ float gate_eff(float g, int hard_gate) { return hard_gate ? (g > 0.5f ? 1.f : 0.f) : g; }
 
 }  // namespace slotscan

@@ -154,6 +154,12 @@ extern "C" int slotscan_check(const slotscan_params* p) {
     if (addr_fwd_smem_bytes(p->N, p->DK, 4) + 1024 > SMEM_CAP || addr_bwd_smem_bytes(p->N, p->DK) + 1024 > SMEM_CAP)
         return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H > 2147483647LL / 4) return SLOTSCAN_E_SHAPE;
+    /* the reverse row scan runs one block per (sequence, head, tile of 2048 / D rows, tensor) on grid.x */
+    {
+        const int dmax = p->DK > p->DV ? p->DK : p->DV;
+        const long long tiles = ((long long)p->N * dmax + 2047) / 2048;
+        if ((long long)p->B * p->H * tiles * 2 > 2147483647LL) return SLOTSCAN_E_SHAPE;
+    }
     /* token chunks ride on grid.y (<= 65535) and the partial-sum table is indexed with ints */
     if (((long long)p->T + GATHER_CHUNK - 1) / GATHER_CHUNK > 65535) return SLOTSCAN_E_SHAPE;
     if ((long long)p->B * p->H * (((long long)p->T + GATHER_CHUNK - 1) / GATHER_CHUNK + 1) > 2147483647LL / 2) return SLOTSCAN_E_SHAPE;
@@ -251,9 +257,17 @@ extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
     attrs_addr_fwd_f32(out, cap, n);
     attrs_addr_fwd_bf16(out, cap, n);
     attrs_rows(out, cap, n);
+    attrs_rows_bwd_f32(out, cap, n);
+    attrs_rows_bwd_bf16(out, cap, n);
     attrs_addr_bwd_f32(out, cap, n);
     attrs_addr_bwd_bf16(out, cap, n);
     return n;
+}
+
+extern "C" int slotscan_device_status(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    const int a = rows_bwd_status_f32(), b = rows_bwd_status_bf16(), c = read_mma_status();
+    return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
 }
 
 extern "C" int slotscan_profile_enable(int on) {

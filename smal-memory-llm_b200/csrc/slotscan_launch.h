@@ -39,8 +39,24 @@ cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const flo
 // reverse row scan; ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs the first set only
 // dkinv: upstream gradient of the kinv output (keys only, NULL otherwise)
 struct RowsBwdPtrs { const void* x; const float* xold; const float* xfin; const void* dxbuf; void* dx; float* Dn; const float* dkinv; };
-cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
-                         const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+cudaError_t run_rows_bwd_f32(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
+                             const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+cudaError_t run_rows_bwd_bf16(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
+                              const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+static inline cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0,
+                                       const RowsBwdPtrs& a1, const float* gate, const int* am, const int* tfirst,
+                                       cudaStream_t st) {
+    return p.in_dtype == SLOTSCAN_F32 ? run_rows_bwd_f32(p, D, ntensors, a0, a1, gate, am, tfirst, st)
+                                      : run_rows_bwd_bf16(p, D, ntensors, a0, a1, gate, am, tfirst, st);
+}
+// rows (highest valid row + 1) up to which a snapshot is read by the CUDA-core kernel even when the tensor-core one runs
+constexpr int RM_SPARSE_ROWS = 32;
+// tensor-core forward read (slotscan_read_mma.cu): returns false when the shape / dtypes are not its own
+bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
+                      const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err);
+int read_mma_status();
+int rows_bwd_status_f32();
+int rows_bwd_status_bf16();
 
 size_t addr_fwd_smem_bytes(int ncap, int DK, int in_bytes);
 size_t addr_bwd_smem_bytes(int ncap, int DK);
@@ -49,6 +65,8 @@ void attrs_addr_fwd_bf16(slotscan_kernel_attr* out, int cap, int& n);
 void attrs_addr_bwd_f32(slotscan_kernel_attr* out, int cap, int& n);
 void attrs_addr_bwd_bf16(slotscan_kernel_attr* out, int cap, int& n);
 void attrs_rows(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_rows_bwd_f32(slotscan_kernel_attr* out, int cap, int& n);
+void attrs_rows_bwd_bf16(slotscan_kernel_attr* out, int cap, int& n);
 
 template <typename F>
 static inline void fill_attr(slotscan_kernel_attr* out, int cap, int& n, const char* name, F f) {

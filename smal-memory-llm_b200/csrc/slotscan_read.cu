@@ -20,6 +20,7 @@
 
 #include "slotscan.h"
 #include "slotscan_common.cuh"
+#include "slotscan_launch.h"
 
 namespace slotscan {
 
@@ -35,20 +36,21 @@ __global__ void __launch_bounds__(RD_THREADS) read_fwd_kernel(const slotscan_rea
                                                              const float* __restrict__ sharp,
                                                              const Tsn* __restrict__ kbuf, const Tsn* __restrict__ vbuf,
                                                              const float* __restrict__ kinv,
-                                                             const uint8_t* __restrict__ valid, Tq* __restrict__ rd) {
+                                                             const uint8_t* __restrict__ valid, Tq* __restrict__ rd,
+                                                             const int sparse_only) {
     extern __shared__ __align__(16) float rsm[];
     const int N = p.N, T = p.T, H = p.H, NQ = p.NQ, DK = p.DK, DV = p.DV, G = p.G;
     const int NB = (T + G - 1) / G;
     int* s_rows = reinterpret_cast<int*>(rsm);                 // [N] indices of the valid rows
     float* s_ki = rsm + N;                                     // [N] their kinv
     float* s_sc = rsm + ((2 * N + 3) & ~3);                    // [warps][N][4] logits, then attention weights (16-byte aligned)
-    __shared__ int s_nv;
+    __shared__ int s_nv, s_hv;
     const int so = blockIdx.x;                                 // (b * NB + nb) * H + h
     const int h = so % H, nb = (so / H) % NB, b = so / (H * NB);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (warp == 0) {
-        int nv = 0;
+        int nv = 0, hv = 0;
         for (int base = 0; base < N; base += 32) {
             const int n = base + lane;
             const bool v = n < N && valid[(size_t)so * N + n] != 0;
@@ -59,11 +61,13 @@ __global__ void __launch_bounds__(RD_THREADS) read_fwd_kernel(const slotscan_rea
                 s_ki[pos] = kinv[(size_t)so * N + n];
             }
             nv += __popc(bal);
+            if (bal) hv = base + 32 - __clz(bal);              // highest valid row + 1
         }
-        if (lane == 0) s_nv = nv;
+        if (lane == 0) { s_nv = nv; s_hv = hv; }
     }
     __syncthreads();
     const int nv = s_nv;
+    if (sparse_only && s_hv > RM_SPARSE_ROWS) return;          // the tensor-core kernel reads this snapshot
     const int t0 = nb * G, tc = min(G, T - t0), M = tc * NQ;   // queries that read this snapshot
     float* sc = s_sc + (size_t)warp * N * RD_QPW;
     const Tsn* Kb = kbuf + (size_t)so * N * DK;
@@ -156,7 +160,8 @@ __global__ void __launch_bounds__(RD_THREADS) read_fwd_kernel(const slotscan_rea
 
 template <typename Tq, typename Tsn>
 static cudaError_t launch_read(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf,
-                               const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st) {
+                               const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st,
+                               int sparse_only = 0) {
     const int NB = (p.T + p.G - 1) / p.G;
     const size_t sm = sizeof(float) * ((size_t)((2 * p.N + 3) & ~3) + (size_t)p.N * RD_WARPS * RD_QPW);
     auto kern = read_fwd_kernel<Tq, Tsn>;
@@ -165,7 +170,7 @@ static cudaError_t launch_read(const slotscan_read_params& p, const void* qr, co
         if (e != cudaSuccess) return e;
     }
     kern<<<p.B * NB * p.H, RD_THREADS, sm, st>>>(p, (const Tq*)qr, sharp, (const Tsn*)kbuf, (const Tsn*)vbuf, kinv, valid,
-                                                  (Tq*)rd);
+                                                  (Tq*)rd, sparse_only);
     return cudaGetLastError();
 }
 
@@ -192,6 +197,12 @@ extern "C" int slotscan_read_fwd(const slotscan_read_params* p, const void* qr, 
     if (!qr || !sharp || !kbuf || !vbuf || !kinv || !valid || !rd) return SLOTSCAN_E_NULL;
     cudaStream_t st = (cudaStream_t)stream_;
     cudaError_t e;
+    // bf16 with dk = dv in {64, 128}: snapshots with more than RM_SPARSE_ROWS rows in use go through the tensor-core
+    // kernel, the others through the CUDA-core kernel; each kernel returns at once on the other's snapshots
+    if (read_fwd_mma_try(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st, &e)) {
+        if (e != cudaSuccess) return (int)e;
+        return (int)launch_read<__nv_bfloat16, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st, 1);
+    }
     const bool qb = p->q_dtype == SLOTSCAN_BF16, sb = p->snap_dtype == SLOTSCAN_BF16;
     if (qb && sb) e = launch_read<__nv_bfloat16, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
     else if (qb) e = launch_read<__nv_bfloat16, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);

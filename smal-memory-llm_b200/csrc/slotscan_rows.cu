@@ -1,4 +1,4 @@
-// Row-parallel kernels (slotscan_rows.cuh) instantiated for every row width and dtype pair.
+// Forward row replay (slotscan_rows.cuh) instantiated for every row width and dtype pair.
 #include <stdio.h>
 
 #include "slotscan_launch.h"
@@ -21,21 +21,6 @@ static cudaError_t replay_one(const slotscan_params& p, const void* x, const flo
     return cudaGetLastError();
 }
 
-template <int D, typename Tin, typename Tsn>
-static cudaError_t rows_bwd_one(const slotscan_params& p, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
-                                const float* gate, const int* am, const int* tfirst, cudaStream_t st) {
-    constexpr int RPB = ROW_THREADS / (D / 8);
-    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB, ntensors);
-    constexpr size_t sm = rows_bwd_smem_bytes<D, Tin>();
-    auto kern = rows_bwd_kernel<D, Tin, Tsn>;
-    cudaError_t e = opt_in_smem(kern, sm);
-    if (e != cudaSuccess) return e;
-    const RowsBwdArgs<Tin, Tsn> b0{(const Tin*)a0.x, a0.xold, a0.xfin, (const Tsn*)a0.dxbuf, (Tin*)a0.dx, a0.Dn, a0.dkinv};
-    const RowsBwdArgs<Tin, Tsn> b1{(const Tin*)a1.x, a1.xold, a1.xfin, (const Tsn*)a1.dxbuf, (Tin*)a1.dx, a1.Dn, a1.dkinv};
-    kern<<<grid, ROW_THREADS, sm, st>>>(p, b0, b1, gate, am, tfirst);
-    return cudaGetLastError();
-}
-
 #define ROWS_TYPES(CALL_F32_F32, CALL_F32_BF16, CALL_BF16_F32, CALL_BF16_BF16)            \
     if (p.in_dtype == SLOTSCAN_F32) {                                                     \
         if (p.snap_dtype == SLOTSCAN_F32) { CALL_F32_F32; } else { CALL_F32_BF16; }       \
@@ -54,16 +39,6 @@ static cudaError_t replay_d(const slotscan_params& p, const void* x, const float
                return (replay_one<D, bf, bf>(p, x, gate, am, tfirst, x0, xbuf, xold, xfin, kinv, valid, st)))
 }
 
-template <int D>
-static cudaError_t rows_bwd_d(const slotscan_params& p, int nt, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
-                              const float* gate, const int* am, const int* tfirst, cudaStream_t st) {
-    typedef __nv_bfloat16 bf;
-    ROWS_TYPES(return (rows_bwd_one<D, float, float>(p, nt, a0, a1, gate, am, tfirst, st)),
-               return (rows_bwd_one<D, float, bf>(p, nt, a0, a1, gate, am, tfirst, st)),
-               return (rows_bwd_one<D, bf, float>(p, nt, a0, a1, gate, am, tfirst, st)),
-               return (rows_bwd_one<D, bf, bf>(p, nt, a0, a1, gate, am, tfirst, st)))
-}
-
 cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
                        const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
@@ -71,19 +46,10 @@ cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const flo
     return e;
 }
 
-cudaError_t run_rows_bwd(const slotscan_params& p, int D, int ntensors, const RowsBwdPtrs& a0, const RowsBwdPtrs& a1,
-                         const float* gate, const int* am, const int* tfirst, cudaStream_t st) {
-    cudaError_t e = cudaSuccess;
-    SLOTSCAN_DISPATCH_D(D, e = (rows_bwd_d<DD>(p, ntensors, a0, a1, gate, am, tfirst, st)));
-    return e;
-}
-
 void attrs_rows(slotscan_kernel_attr* out, int cap, int& n) {
     fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);
     fill_attr(out, cap, n, "replay_rows<128,bf16,bf16,kinv>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, true>);
     fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float, false>);
-    fill_attr(out, cap, n, "rows_bwd<128,bf16,bf16>", rows_bwd_kernel<128, __nv_bfloat16, __nv_bfloat16>);
-    fill_attr(out, cap, n, "rows_bwd<128,f32,f32>", rows_bwd_kernel<128, float, float>);
 }
 
 }  // namespace slotscan

@@ -25,6 +25,11 @@ class Log(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in ("addr", "oold", "kold", "vold", "kfin", "vfin", "ofin", "tfirst", "kiold")]
 
 
+class DenseParams(ctypes.Structure):
+    """slotscan_dense_params of include/slotscan.h."""
+    _fields_ = [("base", Params), ("hard", ctypes.c_int32), ("detach_addr", ctypes.c_int32)]
+
+
 class FwdExtra(ctypes.Structure):
     """slotscan_fwd_extra of include/slotscan.h."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("K0", "V0", "o0", "nsq0", "nsqfin", "kinv", "valid")] + \
@@ -72,6 +77,15 @@ def lib():
         L.slotscan_hard_fwd_ex.restype = ci
         L.slotscan_hard_bwd_ex.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
         L.slotscan_hard_bwd_ex.restype = ci
+        DP = ctypes.POINTER(DenseParams)
+        L.slotscan_dense_check.argtypes = [DP]
+        L.slotscan_dense_check.restype = ci
+        L.slotscan_dense_fwd.argtypes = [DP] + [vp] * 14
+        L.slotscan_dense_fwd.restype = ci
+        L.slotscan_dense_bwd_scratch_bytes.argtypes = [DP]
+        L.slotscan_dense_bwd_scratch_bytes.restype = sz
+        L.slotscan_dense_bwd.argtypes = [DP] + [vp] * 12 + [sz] + [vp] * 7
+        L.slotscan_dense_bwd.restype = ci
         L.slotscan_hard_bwd_scratch_bytes.argtypes = [PP]
         L.slotscan_hard_bwd_scratch_bytes.restype = sz
         L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
@@ -88,6 +102,7 @@ def lib():
         L.slotscan_read_fwd.restype = ci
         L.slotscan_read_bwd.argtypes = [ctypes.POINTER(ReadParams)] + [vp] * 13
         L.slotscan_read_bwd.restype = ci
+        L.slotscan_device_status.restype = ci
         L.slotscan_query_attrs.argtypes = [ctypes.POINTER(KernelAttr), ci]
         L.slotscan_profile_enable.argtypes = [ci]
         L.slotscan_profile_read.argtypes = [ctypes.POINTER(KernelTime), ci]
@@ -113,6 +128,12 @@ def kernel_attrs():
     n = lib().slotscan_query_attrs(buf, 32)
     return {buf[i].name.decode(): (buf[i].regs, buf[i].local_bytes, buf[i].static_smem, buf[i].max_threads)
             for i in range(min(n, 32))}
+
+
+def device_status():
+    """Synchronises the device; 1 if a kernel gave up on a bounded wait since the last call (its results are then
+    incomplete), else 0."""
+    return lib().slotscan_device_status()
 
 
 def profile_enable(on=True):

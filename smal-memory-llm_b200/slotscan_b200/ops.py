@@ -148,3 +148,94 @@ def _backward(ctx, *grads):
 
 
 hard_fwd.register_autograd(_backward, setup_context=_setup)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The general scan (soft address, attached address gradient): slotscan_dense_fwd / slotscan_dense_bwd.
+def _dense_params(k, v, gate, fr, N, G, hard, hard_gate, eps, detach_addr, occ_bin):
+    base = _params(k, v, gate, fr, N, G, hard_gate, eps, occ_bin, torch.float32)
+    return _lib.DenseParams(base, int(hard), int(detach_addr))
+
+
+@torch.library.custom_op("slotscan::dense_fwd", mutates_args=())
+def dense_fwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
+              temp: torch.Tensor, N: int, G: int, hard: bool, hard_gate: bool, eps: float, detach_addr: bool,
+              occ_bin: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+                                      torch.Tensor]:
+    """Any mode of the scan.  Returns kbuf, vbuf (float32), obuf (B,NB,H,N), addr (B,T,H) int32, kfin, vfin, ofin."""
+    _require_cuda(k, q, v, gate, fr, temp)
+    B, T, H, DK = k.shape
+    DV = v.shape[-1]
+    NB = (T + G - 1) // G
+    dev = k.device
+    e = lambda *s, dt=torch.float32: torch.empty(*s, device=dev, dtype=dt)
+    kbuf, vbuf, obuf = e(B, NB, H, N, DK), e(B, NB, H, N, DV), e(B, NB, H, N)
+    addr = e(B, T, H, dt=torch.int32)
+    kfin, vfin, ofin = e(B * H, N, DK), e(B * H, N, DV), e(B * H, N)
+    p = _dense_params(k, v, gate, fr, N, G, hard, hard_gate, eps, detach_addr, occ_bin)
+    _lib.check(_lib.lib().slotscan_dense_check(ctypes.byref(p)), "slotscan_dense_check")
+    with torch.cuda.device(dev):
+        rc = _lib.lib().slotscan_dense_fwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp),
+                                           _ptr(kbuf), _ptr(vbuf), _ptr(obuf), _ptr(addr), _ptr(kfin), _ptr(vfin),
+                                           _ptr(ofin), _stream(dev))
+    _lib.check(rc, "slotscan_dense_fwd")
+    return kbuf, vbuf, obuf, addr, kfin, vfin, ofin
+
+
+@dense_fwd.register_fake
+def _(k, q, v, gate, fr, temp, N, G, hard, hard_gate, eps, detach_addr, occ_bin):
+    B, T, H, DK = k.shape
+    DV = v.shape[-1]
+    NB = (T + G - 1) // G
+    e = lambda *s, dt=torch.float32: k.new_empty(s, dtype=dt)
+    return (e(B, NB, H, N, DK), e(B, NB, H, N, DV), e(B, NB, H, N), e(B, T, H, dt=torch.int32), e(B * H, N, DK),
+            e(B * H, N, DV), e(B * H, N))
+
+
+@torch.library.custom_op("slotscan::dense_bwd", mutates_args=())
+def dense_bwd(k: torch.Tensor, q: Optional[torch.Tensor], v: torch.Tensor, gate: torch.Tensor, fr: torch.Tensor,
+              temp: torch.Tensor, kbuf: torch.Tensor, vbuf: torch.Tensor, obuf: torch.Tensor,
+              dkbuf: Optional[torch.Tensor], dvbuf: Optional[torch.Tensor], N: int, G: int, hard: bool, hard_gate: bool,
+              eps: float, detach_addr: bool, occ_bin: bool
+              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """dk, dq, dv (dtype of k), dgate, dfr (shape of fr), dtemp (1,).  With q None the search-path part in dq has
+    already been added into dk."""
+    _require_cuda(k, v, kbuf)
+    dev = k.device
+    p = _dense_params(k, v, gate, fr, N, G, hard, hard_gate, eps, detach_addr, occ_bin)
+    L = _lib.lib()
+    nbytes = L.slotscan_dense_bwd_scratch_bytes(ctypes.byref(p))
+    scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    dk, dq, dv = torch.empty_like(k), torch.empty_like(k), torch.empty_like(v)
+    dgate = torch.empty(gate.shape, device=dev, dtype=torch.float32)
+    dfr = torch.empty(fr.shape, device=dev, dtype=torch.float32)
+    dtemp = torch.empty(1, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        rc = L.slotscan_dense_bwd(ctypes.byref(p), _ptr(k), _ptr(q), _ptr(v), _ptr(gate), _ptr(fr), _ptr(temp), _ptr(kbuf),
+                                  _ptr(vbuf), _ptr(obuf), _ptr(dkbuf), _ptr(dvbuf), _ptr(scratch), nbytes, _ptr(dk),
+                                  _ptr(dq), _ptr(dv), _ptr(dgate), _ptr(dfr), _ptr(dtemp), _stream(dev))
+    _lib.check(rc, "slotscan_dense_bwd")
+    return dk, dq, dv, dgate, dfr, dtemp
+
+
+@dense_bwd.register_fake
+def _(k, q, v, gate, fr, temp, kbuf, vbuf, obuf, dkbuf, dvbuf, N, G, hard, hard_gate, eps, detach_addr, occ_bin):
+    f = lambda t: t.new_empty(t.shape, dtype=torch.float32)
+    return torch.empty_like(k), torch.empty_like(k), torch.empty_like(v), f(gate), f(fr), gate.new_empty(1)
+
+
+def _dense_setup(ctx, inputs, output):
+    k, q, v, gate, fr, temp, N, G, hard, hard_gate, eps, detach_addr, occ_bin = inputs
+    ctx.save_for_backward(k, q, v, gate, fr, temp, output[0], output[1], output[2])
+    ctx.meta = (N, G, hard, hard_gate, eps, detach_addr, occ_bin)
+    ctx.set_materialize_grads(False)
+
+
+def _dense_backward(ctx, dkbuf, dvbuf, *unused):
+    k, q, v, gate, fr, temp, kbuf, vbuf, obuf = ctx.saved_tensors
+    c = lambda g: None if g is None else g.contiguous().to(torch.float32)
+    dk, dq, dv, dgate, dfr, dtemp = dense_bwd(k, q, v, gate, fr, temp, kbuf, vbuf, obuf, c(dkbuf), c(dvbuf), *ctx.meta)
+    return (dk, (None if q is None else dq), dv, dgate, dfr, dtemp) + (None,) * 7
+
+
+dense_fwd.register_autograd(_dense_backward, setup_context=_dense_setup)

@@ -13,6 +13,8 @@ at t = 0, G, 2G, ...; gradients for k, q (if given), v, gate, fr, temp.  Differe
   * out_dtype=torch.bfloat16 makes the kernels emit bf16 snapshots directly (the reference emits float32 and the
     model casts, memlm_sh.py:475).  Default float32 = the reference contract.
   * nw / nwb (Triton warp hints) are accepted and ignored.
+  * hard=True with detach_addr=True (the training mode of the reference run) takes the specialised kernels; every other
+    combination (soft address, attached address gradient) the general ones (csrc/slotscan_dense.cu).
   * write_memory(...) is the writer layer's whole hand-over in one call: scan + the epilogue of memlm_sh.py:464-475
     (kinv, valid, storage quantisation); StreamingScan carries the slot state from one chunk of a long context to
     the next (the reference keeps no state across calls, memlm_sh.py:676).
@@ -39,9 +41,6 @@ def kv_scan_g(k, v, gate, fr, N, temp, G=16, hard=False, hard_gate=False, eps=1e
               nwb=None, occ_bin=False, out_dtype=torch.float32):
     if not k.is_cuda:
         raise RuntimeError("slotscan_b200.kv_scan_g: CUDA tensors only (no CPU path in this package)")
-    if not (hard and detach_addr):
-        raise NotImplementedError("slotscan_b200: only the hard-address scan with a detached address gradient "
-                                  "(hard=True, detach_addr=True, the training mode of the reference run) is built")
     if out_dtype not in (torch.float32, torch.bfloat16):
         raise ValueError("out_dtype must be float32 or bfloat16")
     B, T, H, DK = k.shape
@@ -54,6 +53,12 @@ def kv_scan_g(k, v, gate, fr, N, temp, G=16, hard=False, hard_gate=False, eps=1e
     else:
         fr_ = torch.as_tensor(fr, dtype=torch.float32, device=k.device).reshape(1)
     temp_ = torch.as_tensor(temp, dtype=torch.float32, device=k.device).reshape(1)   # slotkern_cuda.py:497
+    if not (hard and detach_addr):
+        # soft address and / or address gradient attached to the stored keys: the general kernels (float32 snapshots,
+        # which are also the checkpoints of their backward; a bf16 hand-over is a cast of the result)
+        out = ops.dense_fwd(k_, q_, v_, g_, fr_, temp_, int(N), int(G), bool(hard), bool(hard_gate), float(eps),
+                            bool(detach_addr), bool(occ_bin))
+        return out[0].to(out_dtype), out[1].to(out_dtype)
     out = ops.hard_fwd(k_, q_, v_, g_, fr_, temp_, None, None, None, None, int(N), int(G), bool(hard_gate), float(eps),
                        bool(occ_bin), out_dtype == torch.bfloat16, False, True)
     return out[0], out[1]

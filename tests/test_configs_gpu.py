@@ -123,6 +123,8 @@ def test_config1_full_size_sequences_vs_oracle():
     dvb = torch.randn(B, T // G, H, N, D, device=DEV, dtype=torch.bfloat16, generator=gen)
     out = _run_bf16(S, inp, N, G, dkb, dvb)
     _compare_sequences("config 1", out, inp, dkb, dvb, N, G, H, (0, 31, 63))
+    from slotscan_b200 import _lib
+    assert _lib.device_status() == 0                                   # no kernel gave up on a bounded wait
     del out, dkb, dvb
     torch.cuda.empty_cache()
 

@@ -85,6 +85,33 @@ def test_read_after_scan_and_epilogue_bf16():
     assert rd.dtype == torch.bfloat16 and rd[:, :G].abs().max() == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 3, 2, 192, 128, 128, 8, 192), (2, 40, 2, 2, 192, 128, 128, 8, 13),
+                                   (1, 50, 2, 4, 96, 64, 64, 16, 96), (1, 21, 2, 1, 40, 128, 128, 8, 37)],
+                         ids=["sh25_dense", "sh25_sparse", "d64_M64_T%G", "M8_n40"])
+def test_read_tensor_core_path_bf16(shape):
+    """bf16 queries and snapshots with dk = dv in {64, 128}: the read runs on the tensor cores (Q K^T and P V as
+    m16n8k16 MMAs with float32 accumulation, P in bf16 as the reference's att.to(bf16)).  Against the float64 oracle on
+    the same bf16-rounded inputs, within the bf16 band: one bf16 ulp of the value plus 2e-3 of the tensor's scale."""
+    S = _S()
+    B, T, H, NQ, N, DK, DV, G, nvalid = shape
+    qr, sharp, kbuf, vbuf = _case(*shape, seed=15)
+    qr, kbuf, vbuf = (x.to(torch.bfloat16) for x in (qr, kbuf, vbuf))
+    kinv, valid = O.epilogue(kbuf.float().numpy(), dtype=np.float32)
+    want = O.read_fwd(qr.float().numpy(), sharp.numpy(), kbuf.float().numpy(), vbuf.float().numpy(), kinv, valid, G,
+                      dtype=np.float64)
+    with torch.no_grad():
+        rd = S.read_snapshots(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).cuda(),
+                              torch.from_numpy(valid).cuda(), G)
+    got = rd.float().cpu().numpy()
+    assert rd.dtype == torch.bfloat16 and rd[:, :G].abs().max() == 0
+    assert np.all(np.abs(got - want) <= 2e-3 * np.abs(want).max() + np.abs(want) * 2.0 ** -7), \
+        float((np.abs(got - want) - np.abs(want) * 2.0 ** -7).max() / np.abs(want).max())
+    # mean error far inside the band: the kernel is not merely "within an ulp" everywhere
+    assert np.abs(got - want).mean() < 2e-3 * np.abs(want).max()
+    from slotscan_b200 import _lib
+    assert _lib.device_status() == 0
+
+
 def test_read_contract():
     S = _S()
     qr, sharp, kbuf, vbuf = _case(1, 8, 1, 1, 4, 16, 16, 4, 4, seed=1)
