@@ -173,6 +173,33 @@ def fq(x, bits, group, dtype=np.float32):
     return y
 
 
+def scan_v_fwd(v, wa, gate, fr, N, G=1, hard=False, hard_gate=False, dtype=np.float64):
+    """Keyless scan (gqa25/slotkern_v.py:242-261).  v (B,T,H,DV), wa (B,T,H,N), gate (B,T,H), fr scalar.
+    Returns dict(buf (B,NB,H,N,DV), addr (B,T,H))."""
+    v, wa, gate = _np(v, dtype), _np(wa, dtype), _np(gate, dtype)
+    fr = _np(fr, dtype).reshape(1)
+    B, T, H, DV = v.shape
+    NB = (T + G - 1) // G
+    out = dict(buf=np.empty((B, NB, H, N, DV), dtype), addr=np.empty((B, T, H), np.int32))
+    rc = getattr(lib(), "slotscan_oracle_v_fwd" + _suffix(dtype))(B, T, H, int(N), DV, int(G), int(hard), int(hard_gate),
+                                                                  _p(v), _p(wa), _p(gate), _p(fr), _p(out["buf"]), _p(out["addr"]))
+    assert rc == 0
+    return out
+
+
+def scan_v_bwd(v, wa, gate, fr, N, dbuf, G=1, hard=False, hard_gate=False, dtype=np.float64):
+    """Gradients of sum(buf * dbuf): dict(dv, dwa, dgate, dfr (1,))."""
+    v, wa, gate, dbuf = _np(v, dtype), _np(wa, dtype), _np(gate, dtype), _np(dbuf, dtype)
+    fr = _np(fr, dtype).reshape(1)
+    B, T, H, DV = v.shape
+    out = dict(dv=np.zeros_like(v), dwa=np.zeros_like(wa), dgate=np.zeros_like(gate), dfr=np.zeros(1, dtype))
+    rc = getattr(lib(), "slotscan_oracle_v_bwd" + _suffix(dtype))(B, T, H, int(N), DV, int(G), int(hard), int(hard_gate),
+                                                                  _p(v), _p(wa), _p(gate), _p(fr), _p(dbuf), _p(out["dv"]),
+                                                                  _p(out["dwa"]), _p(out["dgate"]), _p(out["dfr"]))
+    assert rc == 0
+    return out
+
+
 def fp8_e4m3_rows(x):
     """Per-row fp8-e4m3 storage: s = absmax/448 per row, y = e4m3(x/s) * s.  The reference has no fp8 format
     (only a comment, memlm_sh.py:217-218), so this restatement is PARITY-UNPINNED by any reference test."""

@@ -9,6 +9,7 @@
  *   slotscan_oracle_epilogue_*           kinv / valid              gqa25/memlm_sh.py:474-475
  *   slotscan_oracle_read_{fwd,bwd}_*     cosine read               gqa25/memlm_sh.py:362-397
  *   slotscan_oracle_fq_*                 midrise quantiser         gqa25/memlm_sh.py:221-229
+ *   slotscan_oracle_v_{fwd,bwd}_*        keyless scan + adjoint    gqa25/slotkern_v.py:242-261, :14-19
  *
  * Pinned by tests/test_oracle_golden.py against fixtures that tests/golden/make_golden.py produced by running the
  * reference's own torch code (forward in float64 and float32, gradients by torch autograd).

@@ -470,6 +470,134 @@ int FN(slotscan_oracle_fq)(const REAL* x, long n_groups, int group, int bits, RE
     return 0;
 }
 
+/* ---- keyless scan: address logits given from outside, value-only state ----
+ * gqa25/slotkern_v.py:242-261 (ref_scan_v) and the adjoint stated in its module docstring (:14-19):
+ *   z = wa_t - fr o over ALL N rows (no free-row mask),  a_s = softmax(z),  a = onehot(argmax z) if hard else a_s,
+ *   g_h = [g > 0.5] if hard_gate else g,  w = g_h a,  V <- (1-w) V + w v_t,  o <- (1-w) o + w.
+ * buf (B,NB,H,N,DV): pre-write V at t = 0, G, 2G, ...  fr: 1 element. */
+static void FN(v_step)(int N, int hard, int hard_gate, const REAL* wa, const REAL* o, REAL fr, REAL gate_t, REAL* asoft,
+                       REAL* afwd, REAL* g_eff) {
+    REAL zmax = -INFINITY;
+    int am = 0;
+    for (int n = 0; n < N; n++) {
+        const REAL z = wa[n] - fr * o[n];
+        asoft[n] = z;
+        if (z > zmax) { zmax = z; am = n; }                       /* first maximum */
+    }
+    REAL se = 0;
+    for (int n = 0; n < N; n++) { asoft[n] = EXP(asoft[n] - zmax); se += asoft[n]; }
+    for (int n = 0; n < N; n++) {
+        asoft[n] /= se;
+        afwd[n] = hard ? (n == am ? (REAL)1 : (REAL)0) : asoft[n];
+    }
+    *g_eff = hard_gate ? (gate_t > (REAL)0.5 ? (REAL)1 : (REAL)0) : gate_t;
+}
+
+int FN(slotscan_oracle_v_fwd)(int B, int T, int H, int N, int DV, int G, int hard, int hard_gate, const REAL* v,
+                              const REAL* wa, const REAL* gate, const REAL* fr, REAL* buf, int* addr) {
+    const int NB = (T + G - 1) / G;
+#pragma omp parallel for schedule(dynamic)
+    for (int bh = 0; bh < B * H; bh++) {
+        const int b = bh / H, h = bh % H;
+        REAL* V = (REAL*)calloc((size_t)N * DV, sizeof(REAL));
+        REAL* o = (REAL*)calloc(N, sizeof(REAL));
+        REAL* as = (REAL*)malloc(sizeof(REAL) * N);
+        REAL* af = (REAL*)malloc(sizeof(REAL) * N);
+        for (int t = 0; t < T; t++) {
+            const size_t ix = ((size_t)b * T + t) * H + h;
+            if (t % G == 0) memcpy(buf + (((size_t)b * NB + t / G) * H + h) * N * DV, V, sizeof(REAL) * N * DV);
+            REAL g;
+            FN(v_step)(N, hard, hard_gate, wa + ix * N, o, fr[0], gate[ix], as, af, &g);
+            if (addr) { int am = 0; for (int n = 1; n < N; n++) if (af[n] > af[am]) am = n; addr[ix] = am; }
+            for (int n = 0; n < N; n++) {
+                const REAL w = g * af[n];
+                if (af[n] == (REAL)0) continue;
+                for (int d = 0; d < DV; d++) V[(size_t)n * DV + d] = ((REAL)1 - w) * V[(size_t)n * DV + d] + w * v[ix * DV + d];
+                o[n] = ((REAL)1 - w) * o[n] + w;
+            }
+        }
+        free(V); free(o); free(as); free(af);
+    }
+    return 0;
+}
+
+/* gradients of sum(buf * dbuf) w.r.t. v, wa, gate, fr (1 element) */
+int FN(slotscan_oracle_v_bwd)(int B, int T, int H, int N, int DV, int G, int hard, int hard_gate, const REAL* v,
+                              const REAL* wa, const REAL* gate, const REAL* fr, const REAL* dbuf, REAL* dv, REAL* dwa,
+                              REAL* dgate, REAL* dfr) {
+    const int NB = (T + G - 1) / G;
+    REAL* part = (REAL*)calloc((size_t)B * H, sizeof(REAL));
+#pragma omp parallel for schedule(dynamic)
+    for (int bh = 0; bh < B * H; bh++) {
+        const int b = bh / H, h = bh % H;
+        const size_t SV = (size_t)N * DV;
+        REAL* sV = (REAL*)malloc(sizeof(REAL) * SV * T);           /* every pre-write state: tests are small */
+        REAL* sO = (REAL*)malloc(sizeof(REAL) * N * T);
+        REAL* V = (REAL*)calloc(SV, sizeof(REAL));
+        REAL* o = (REAL*)calloc(N, sizeof(REAL));
+        REAL* as = (REAL*)malloc(sizeof(REAL) * N);
+        REAL* af = (REAL*)malloc(sizeof(REAL) * N);
+        REAL* dV = (REAL*)calloc(SV, sizeof(REAL));
+        REAL* dO = (REAL*)calloc(N, sizeof(REAL));
+        REAL* dw = (REAL*)malloc(sizeof(REAL) * N);
+        for (int t = 0; t < T; t++) {
+            const size_t ix = ((size_t)b * T + t) * H + h;
+            memcpy(sV + SV * t, V, sizeof(REAL) * SV);
+            memcpy(sO + (size_t)N * t, o, sizeof(REAL) * N);
+            REAL g;
+            FN(v_step)(N, hard, hard_gate, wa + ix * N, o, fr[0], gate[ix], as, af, &g);
+            for (int n = 0; n < N; n++) {
+                const REAL w = g * af[n];
+                if (af[n] == (REAL)0) continue;
+                for (int d = 0; d < DV; d++) V[(size_t)n * DV + d] = ((REAL)1 - w) * V[(size_t)n * DV + d] + w * v[ix * DV + d];
+                o[n] = ((REAL)1 - w) * o[n] + w;
+            }
+        }
+        REAL acc_fr = 0;
+        for (int t = T - 1; t >= 0; t--) {
+            const size_t ix = ((size_t)b * T + t) * H + h;
+            const REAL *Vp = sV + SV * t, *op = sO + (size_t)N * t;
+            REAL g;
+            FN(v_step)(N, hard, hard_gate, wa + ix * N, op, fr[0], gate[ix], as, af, &g);
+            REAL dg = 0, sa = 0;
+            for (int n = 0; n < N; n++) {
+                REAL a1 = 0;
+                for (int d = 0; d < DV; d++) a1 += (v[ix * DV + d] - Vp[(size_t)n * DV + d]) * dV[(size_t)n * DV + d];
+                dw[n] = a1 + ((REAL)1 - op[n]) * dO[n];
+                dg += af[n] * dw[n];
+                sa += as[n] * (g * dw[n]);
+            }
+            for (int d = 0; d < DV; d++) {
+                REAL a1 = 0;
+                for (int n = 0; n < N; n++) a1 += (g * af[n]) * dV[(size_t)n * DV + d];
+                dv[ix * DV + d] = a1;
+            }
+            dgate[ix] = dg;
+            const int emit = (t % G == 0);
+            const size_t so = ((size_t)b * NB + t / G) * H + h;
+            for (int n = 0; n < N; n++) {
+                const REAL dz = as[n] * (g * dw[n] - sa);
+                dwa[ix * N + n] = dz;
+                acc_fr -= op[n] * dz;
+                const REAL om = (REAL)1 - g * af[n];
+                for (int d = 0; d < DV; d++) {
+                    REAL x = om * dV[(size_t)n * DV + d];
+                    if (emit) x += dbuf[so * SV + (size_t)n * DV + d];
+                    dV[(size_t)n * DV + d] = x;
+                }
+                dO[n] = om * dO[n] - fr[0] * dz;
+            }
+        }
+        part[bh] = acc_fr;
+        free(sV); free(sO); free(V); free(o); free(as); free(af); free(dV); free(dO); free(dw);
+    }
+    REAL sfr = 0;
+    for (int i = 0; i < B * H; i++) sfr += part[i];
+    dfr[0] = sfr;
+    free(part);
+    return 0;
+}
+
 #undef NEG_MASK
 #undef CKPT
 #undef FN

@@ -3,6 +3,7 @@
 // library builds in parallel.
 #pragma once
 #include <cuda_runtime.h>
+#include <stdio.h>
 
 #include "slotscan.h"
 

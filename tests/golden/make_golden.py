@@ -3,6 +3,7 @@
 Needs the reference checkout, its location given in $SLOTSCAN_REFERENCE; it imports, unmodified,
     gqa25/slotkern_kv.py   _ref_scan_kv_impl / ref_scan_kv     (the scan; gradients by torch autograd)
     gqa25/memlm_sh.py      SharedMixer._read, _fq, _quantize_mem (the read and the storage quantiser)
+    gqa25/slotkern_v.py    ref_scan_v                          (the keyless scan)
 and writes one compressed .npz per case.  The fixtures travel with the repository; the reference does not.
 
     SLOTSCAN_REFERENCE=<reference checkout> python tests/golden/make_golden.py      # rewrites tests/golden/*.npz
@@ -195,9 +196,41 @@ def make_quant_case(seed=3):
     print("quant_fq.npz")
 
 
+KEYLESS_CASES = [   # name, B, T, H, N, DV, G, hard, hard_gate      (the self-test of gqa25/slotkern_v.py:283-289)
+    ("soft_g1", 2, 40, 2, 12, 8, 1, 0, 0),
+    ("hard_g4", 2, 50, 2, 16, 16, 4, 1, 0),
+    ("hard_hardgate_n48", 1, 60, 3, 48, 16, 1, 1, 1),
+]
+
+
+def make_keyless_case(name, B, T, H, N, DV, G, hard, hard_gate, seed):
+    """ref_scan_v in float64 (gqa25/slotkern_v.py:242-261), gradients by autograd; inputs as in its self-test (:275-279)."""
+    import slotkern_v as SV
+    gen = torch.Generator().manual_seed(seed)
+    v = torch.randn(B, T, H, DV, generator=gen).double()
+    wa = (1.5 * torch.randn(B, T, H, N, generator=gen)).double()
+    gate = torch.sigmoid(torch.randn(B, T, H, generator=gen)).double()
+    fr = torch.tensor([3.0], dtype=torch.float64)
+    leaves = [x.clone().requires_grad_() for x in (v, wa, gate, fr)]
+    buf = SV.ref_scan_v(*leaves, N, G=G, hard=bool(hard), hard_gate=bool(hard_gate))
+    w = torch.randn(buf.shape, generator=gen).double()
+    (buf * w).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "keyless_%s.npz" % name), v=v.float().numpy(), wa=wa.float().numpy(),
+                        gate=gate.float().numpy(), fr=fr.float().numpy(), buf=buf.detach().numpy(), w=w.float().numpy(),
+                        dv=leaves[0].grad.numpy(), dwa=leaves[1].grad.numpy(), dgate=leaves[2].grad.numpy(),
+                        dfr=leaves[3].grad.numpy(), meta=np.array([B, T, H, N, DV, G, hard, hard_gate], np.int64))
+    print("keyless_%s.npz  buf %s" % (name, tuple(buf.shape)))
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
+    if "--keyless-only" in sys.argv:
+        for i, case in enumerate(KEYLESS_CASES):
+            make_keyless_case(*case, seed=400 + i)
+        sys.exit(0)
     for i, case in enumerate(SCAN_CASES):
         make_scan_case(*case, seed=100 + i)
+    for i, case in enumerate(KEYLESS_CASES):
+        make_keyless_case(*case, seed=400 + i)
     make_read_case()
     make_quant_case()

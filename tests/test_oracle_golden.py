@@ -94,3 +94,23 @@ def test_quantiser_matches_reference():
     kq = O.fq(z["x"], 3, 16)
     kinv, valid = O.epilogue(kq, dtype=np.float32)
     assert np.array_equal(valid, z["qm_valid"]) and rel(kinv[valid], z["qm_kinv"][valid]) < 1e-6
+
+
+KEYLESS = sorted(glob.glob(os.path.join(GOLDEN, "keyless_*.npz")))
+
+
+@pytest.mark.parametrize("path", KEYLESS, ids=[os.path.basename(p)[8:-4] for p in KEYLESS])
+def test_keyless_scan_matches_reference(path):
+    """The keyless scan (gqa25/slotkern_v.py: ref_scan_v) and its adjoint against the reference's float64 run + autograd."""
+    z = np.load(path)
+    B, T, H, N, DV, G, hard, hard_gate = (int(x) for x in z["meta"])
+    kw = dict(N=N, G=G, hard=bool(hard), hard_gate=bool(hard_gate))
+    out = O.scan_v_fwd(z["v"], z["wa"], z["gate"], z["fr"], dtype=np.float64, **kw)
+    assert rel(out["buf"], z["buf"]) < 1e-9
+    g = O.scan_v_bwd(z["v"], z["wa"], z["gate"], z["fr"], dbuf=z["w"], dtype=np.float64, **kw)
+    for n in ("dv", "dwa", "dgate", "dfr"):
+        assert rel(g[n].reshape(z[n].shape), z[n]) < 1e-7, n
+
+
+def test_keyless_fixture_list_complete():
+    assert len(KEYLESS) == 3, KEYLESS
