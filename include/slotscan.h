@@ -186,6 +186,28 @@ int slotscan_dense_bwd(const slotscan_dense_params* p, const void* k, const void
                        const float* dkbuf, const float* dvbuf, void* scratch, size_t scratch_bytes, void* dk, void* dq,
                        void* dv, float* dgate, float* dfr, float* dtemp, void* stream);
 
+/* The keyless scan: address logits given from outside, value-only state.
+ * [replaces the Triton kernels of gqa25/slotkern_v.py (_vfwd :25, _vrecompute :75, _vadjoint :120; entry slot_scan_v :232;
+ * definition ref_scan_v :242-261).]  z = wa_t - fr o over all N rows, softmax or argmax (hard, straight-through), gate or
+ * [gate > 0.5] (hard_gate, straight-through), V <- (1 - w) V + w v_t, o <- (1 - w) o + w.
+ *   v (B,T,H,DV) in_dtype, wa (B,T,H,N) f32, gate (B,T,H) f32, fr 1 float (device)
+ *   buf (B,NB,H,N,DV) f32: the pre-write values at t = 0, G, 2G, ...; obuf (B,NB,H,N) f32: the occupancies at the same
+ *   times (the backward's checkpoints); addr (B,T,H) int32 or NULL.
+ * Backward: dv (in_dtype), dwa (B,T,H,N), dgate (B,T,H), dfr 1 float, from dbuf (f32, or NULL = zeros); scratch of
+ * slotscan_v_bwd_scratch_bytes.  N * DV + 10 N floats must fit one CTA's shared memory. */
+typedef struct {
+    int32_t B, T, H, N, DV, G;
+    int32_t hard, hard_gate;
+    int32_t in_dtype;       /* SLOTSCAN_F32 / SLOTSCAN_BF16: v and dv */
+} slotscan_v_params;
+int slotscan_v_check(const slotscan_v_params* p);
+int slotscan_v_fwd(const slotscan_v_params* p, const void* v, const float* wa, const float* gate, const float* fr,
+                   float* buf, float* obuf, int32_t* addr, void* stream);
+size_t slotscan_v_bwd_scratch_bytes(const slotscan_v_params* p);
+int slotscan_v_bwd(const slotscan_v_params* p, const void* v, const float* wa, const float* gate, const float* fr,
+                   const float* buf, const float* obuf, const float* dbuf, void* scratch, size_t scratch_bytes, void* dv,
+                   float* dwa, float* dgate, float* dfr, void* stream);
+
 /* Writer epilogue and storage quantiser over emitted snapshot rows, one streaming pass.
  * [replaces memlm_sh.py:464-475 (nsq = sum kbuf^2 in fp32, kinv = rsqrt(max(nsq, 1e-12)), valid = nsq > 1e-12, cast of
  * the snapshots to the model dtype) and memlm_sh.py:221-234 (_fq, _quantize_mem).]

@@ -81,6 +81,14 @@ cudaError_t SS_CAT(run_addr_bwd_, SLOTSCAN_SUFFIX)(const slotscan_params& p, con
     return e;
 }
 
+// 1 when a bounded wait of this translation unit's kernels gave up since the last call (clears the flag)
+int SS_CAT(gather_status_, SLOTSCAN_SUFFIX)() {
+    int v = 0, z = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gather_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_gather_status, &z, sizeof(int));
+    return v;
+}
+
 void SS_CAT(attrs_addr_bwd_, SLOTSCAN_SUFFIX)(slotscan_kernel_attr* out, int cap, int& n) {
     fill_attr(out, cap, n, "addr_bwd<128,rows<=64>", addr_bwd_chunked_kernel<128, 2, true, 2, Tin>);
     fill_attr(out, cap, n, "addr_bwd<128,rows<=192>", addr_bwd_chunked_kernel<128, 6, true, 2, Tin>);

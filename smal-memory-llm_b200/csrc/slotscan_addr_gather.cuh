@@ -9,12 +9,15 @@
 // occupancy adjoint) and the work spreads over (sequence, head) x (32-token chunk) CTAs:
 //   next_write_kernel    one warp per (sequence, head) walks the address log backwards once and stores, per chunk,
 //                        the next write of each of the 32 rows at the chunk's END;
-//   addr_bwd_gather_kernel  per CTA: warp 0 expands that to a per-token table; then each warp takes 4 tokens:
-//                        scores by 8 lanes per row (4 rows at a time, 3 shuffle stages), softmax adjoint with
-//                        lane = row, dq accumulated with lane = 4 columns over the rows (no reduction).
+//   addr_bwd_gather_kernel  per CTA: every row version the chunk's tokens can see (<= 32 rows after the chunk + the 32
+//                        undo rows of the chunk) comes into shared memory by bulk asynchronous copies; warp 0 expands
+//                        the next-write table to a per-token table; then each warp takes 4 tokens: scores by 8 lanes
+//                        per row (4 rows at a time, 3 shuffle stages), softmax adjoint with lane = row, dq accumulated
+//                        with lane = 4 columns over the rows (no reduction).
 // A sequence that ever made row 32 a candidate is left to the chunked kernel.  [reference addr_bwd, slotkern_cuda.py:264-443]
 #pragma once
 #include "slotscan_addr_fwd.cuh"
+#include "slotscan_async.cuh"
 
 namespace slotscan {
 
@@ -47,8 +50,11 @@ static __global__ void __launch_bounds__(32) next_write_kernel(const slotscan_pa
     }
 }
 
+// Set when a bounded wait gave up (slotscan_device_status reads it through the translation unit's accessor).
+static __device__ int g_gather_status = 0;
+
 template <int DK, typename Tin>
-__global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
+__global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
     const slotscan_params p, const Tin* __restrict__ q, const float* __restrict__ gate, const float* __restrict__ fr,
     const float* __restrict__ temp_p, const int* __restrict__ am, const float* __restrict__ kold,
     const float* __restrict__ oold, const float* __restrict__ kiold, const float* __restrict__ kfin,
@@ -56,14 +62,20 @@ __global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
     const float* __restrict__ Din, Tin* __restrict__ dq, float* __restrict__ dg, float* __restrict__ dfr,
     float* __restrict__ part, const int part_stride) {
     static_assert(DK >= 32, "8 lanes x float4 per row");
-    constexpr int CPL = DK / 8;                   // columns per lane in the score pass (8 lanes per row)
-    constexpr int NF = CPL / 4;
+    constexpr int NF = DK / 32;                   // float4 per lane and row in the score pass (8 lanes per row)
+    // Every key-row version a token of this chunk can see, staged once per CTA by bulk asynchronous copies:
+    //   slot n        (n < 32)   row n as it is AFTER the chunk: the undo row of its next write, or the final row
+    //   slot 32 + i              the undo row of token t0 + i: the row it writes, as it was before that write
+    // Token i sees row n in slot 32 + (t' - t0) if some token t' >= t0 + i of this chunk writes n, else in slot n.
+    // The per-token work then reads shared memory only (before: ~11 KB of gathered rows per token out of L2).
+    __shared__ __align__(128) float s_rows[2 * GATHER_ROWS * DK];
+    __shared__ float s_kiv[2 * GATHER_ROWS], s_ov[2 * GATHER_ROWS];    // 1 / |row| (clamped) and occupancy per slot
     __shared__ int s_ver[GC][GATHER_ROWS];        // next write of row n as token i sees it
     __shared__ int s_am[GC];
-    __shared__ int s_tf[GATHER_ROWS];
-    __shared__ float s_kfinv[GATHER_ROWS], s_ofin[GATHER_ROWS];
+    __shared__ int s_tf[GATHER_ROWS], s_vend[GATHER_ROWS];
     __shared__ float s_S[GA_WARPS][GATHER_ROWS];
     __shared__ float s_red[2][GA_WARPS];
+    __shared__ __align__(8) uint64_t s_bar;
     const int N = p.N, T = p.T, H = p.H;
     const int bh = blockIdx.x, c = blockIdx.y, b = bh / H, h = bh % H;    // chunks on grid.y: T / 32 <= 65535
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -77,20 +89,57 @@ __global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
     if (tid >= 32 && tid < 32 + GATHER_ROWS) {
         const int n = tid - 32;
         s_tf[n] = (n < N) ? tfirst[(size_t)bh * N + n] : T;
-        s_ofin[n] = (n < N) ? ofin[(size_t)bh * N + n] : 0.f;
     }
-    for (int n = warp; n < NR; n += GA_WARPS) {   // norms of the final rows
-        const int col = lane * 4;
-        const float4 Kn = (col < DK) ? ld4(kfin + ((size_t)bh * N + n) * DK + col) : zero4;
-        const float nsq = warp_sum(dot4(Kn, Kn));
-        if (lane == 0) s_kfinv[n] = fminf(rsqrtf(nsq), 1e6f);
+    if (tid >= 64 && tid < 64 + GC) {             // norm and occupancy of the row each token of the chunk overwrote
+        const int i = tid - 64;
+        const size_t ix = ((size_t)b * T + t0 + i) * H + h;
+        s_kiv[GATHER_ROWS + i] = (i < tc) ? kiold[ix] : 0.f;
+        s_ov[GATHER_ROWS + i] = (i < tc) ? oold[ix] : 0.f;
+    }
+    if (tid == 0) {
+        mbar_init(&s_bar, 1);
+        mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 0) {                              // per-token versions, walking the chunk backwards
-        int ver = vend[((size_t)bh * nc + c) * GATHER_ROWS + lane];
+    if (warp == 0) {
+        const int ve = (lane < NR) ? vend[((size_t)bh * nc + c) * GATHER_ROWS + lane] : -1;
+        const bool r_in = lane < NR, t_in = lane < tc;
+        const unsigned nrow = __popc(__ballot_sync(FULL, r_in)) + __popc(__ballot_sync(FULL, t_in));
+        if (lane == 0) mbar_arrive_expect_tx(&s_bar, nrow * (unsigned)(DK * 4));
+        __syncwarp();
+        if (r_in)
+            bulk_g2s(s_rows + lane * DK, ve < 0 ? kfin + ((size_t)bh * N + lane) * DK : kold + (((size_t)b * T + ve) * H + h) * DK,
+                     DK * 4, &s_bar);
+        if (t_in) bulk_g2s(s_rows + (GATHER_ROWS + lane) * DK, kold + (((size_t)b * T + t0 + lane) * H + h) * DK, DK * 4, &s_bar);
+        s_vend[lane] = ve;
+        if (r_in) {
+            if (ve >= 0) {
+                const size_t vix = ((size_t)b * T + ve) * H + h;
+                s_kiv[lane] = kiold[vix];
+                s_ov[lane] = oold[vix];
+            } else {
+                s_ov[lane] = ofin[(size_t)bh * N + lane];                 // the norm follows once the row has landed
+            }
+        }
+        int ver = ve;                                                      // per-token versions, walking the chunk backwards
         for (int i = GC - 1; i >= 0; i--) {
             if (s_am[i] == lane) ver = t0 + i;
             s_ver[i][lane] = ver;
+        }
+    }
+    {
+        const bool landed = mbar_wait_bounded(&s_bar, 0u);
+        if (!__syncthreads_and(landed ? 1 : 0)) {
+            if (tid == 0) atomicExch(&g_gather_status, 1);
+            return;
+        }
+    }
+    for (int n = warp; n < NR; n += GA_WARPS) {   // norms of the rows that are final rows (never written again)
+        if (s_vend[n] < 0) {
+            const int col = lane * 4;
+            const float4 Kn = (col < DK) ? ld4(s_rows + n * DK + col) : zero4;
+            const float nsq = warp_sum(dot4(Kn, Kn));
+            if (lane == 0) s_kiv[n] = fminf(rsqrtf(nsq), 1e6f);
         }
     }
     __syncthreads();
@@ -100,31 +149,34 @@ __global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
         const size_t ix = ((size_t)b * T + t) * H + h;
         int lim = NR - 1;
         while (lim > 0 && s_tf[lim] > t) lim--;
-        // ---- scores: 8 lanes per row, 4 rows per pass ----
-        const int r = lane >> 3, cp = (lane & 7) * CPL;
+        // slot of row n as this token sees it
+        auto slot_of = [&](int n) {
+            const int ver = s_ver[i][n];
+            return (ver >= t0 && ver < t0 + GC) ? GATHER_ROWS + (ver - t0) : n;
+        };
+        // ---- scores: 8 lanes per row (lane l of the 8 takes float4 chunks l, l + 8, ...: conflict-free), 4 rows per pass ----
+        const int r = lane >> 3, l8 = lane & 7;
         float4 q4[NF];
         float qq = 0.f;
 #pragma unroll
-        for (int f = 0; f < NF; f++) { q4[f] = ld4(q + ix * DK + cp + 4 * f); qq += dot4(q4[f], q4[f]); }
+        for (int f = 0; f < NF; f++) { q4[f] = ld4(q + ix * DK + (l8 + 8 * f) * 4); qq += dot4(q4[f], q4[f]); }
         qq += __shfl_xor_sync(FULL, qq, 1); qq += __shfl_xor_sync(FULL, qq, 2); qq += __shfl_xor_sync(FULL, qq, 4);
         const float qinv = fminf(rsqrtf(qq), 1e6f);
         for (int base = 0; base <= lim; base += 4) {
             const int n = min(base + r, lim);
-            const int ver = s_ver[i][n];
-            const float* row = (ver < 0) ? kfin + ((size_t)bh * N + n) * DK : kold + (((size_t)b * T + ver) * H + h) * DK;
+            const float* row = s_rows + slot_of(n) * DK;
             float a = 0.f;
 #pragma unroll
-            for (int f = 0; f < NF; f++) a += dot4(ld4(row + cp + 4 * f), q4[f]);
+            for (int f = 0; f < NF; f++) a += dot4(ld4(row + (l8 + 8 * f) * 4), q4[f]);
             a += __shfl_xor_sync(FULL, a, 1); a += __shfl_xor_sync(FULL, a, 2); a += __shfl_xor_sync(FULL, a, 4);
-            if ((lane & 7) == 0 && base + r <= lim) s_S[warp][base + r] = a;
+            if (l8 == 0 && base + r <= lim) s_S[warp][base + r] = a;
         }
         __syncwarp();
         // ---- softmax adjoint: lane = row ----
         const bool in = lane <= lim;
-        const int ver = in ? s_ver[i][lane] : -1;
-        const size_t vix = ((size_t)b * T + (ver < 0 ? 0 : ver)) * H + h;
-        const float ki = !in ? 0.f : (ver < 0 ? s_kfinv[lane] : kiold[vix]);
-        const float oc = !in ? 0.f : (ver < 0 ? s_ofin[lane] : oold[vix]);
+        const int sl = in ? slot_of(lane) : 0;
+        const float ki = in ? s_kiv[sl] : 0.f;
+        const float oc = in ? s_ov[sl] : 0.f;
         const float g = gate_eff(gate[ix], p.hard_gate), frv = p.fr_per_token ? fr[ix] : fr[0];
         const float s = in ? temp * qinv * (ki * s_S[warp][lane]) : 0.f;
         const float occ = oc >= eps ? 1.f : 0.f;
@@ -167,9 +219,7 @@ __global__ void __launch_bounds__(GA_THREADS) addr_bwd_gather_kernel(
         float4 acc = zero4;
         for (int n = 0; n <= lim; n++) {
             const float cn = s_S[warp][n];
-            const int vn = s_ver[i][n];
-            const float* row = (vn < 0) ? kfin + ((size_t)bh * N + n) * DK : kold + (((size_t)b * T + vn) * H + h) * DK;
-            const float4 K4 = act ? ld4(row + col) : zero4;
+            const float4 K4 = act ? ld4(s_rows + slot_of(n) * DK + col) : zero4;
             acc.x += cn * K4.x; acc.y += cn * K4.y; acc.z += cn * K4.z; acc.w += cn * K4.w;
         }
         const float4 qv = act ? ld4(q + ix * DK + col) : zero4;

@@ -267,7 +267,8 @@ extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
 extern "C" int slotscan_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     const int a = rows_bwd_status_f32(), b = rows_bwd_status_bf16(), c = read_mma_status();
-    return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
+    const int d = gather_status_f32(), e = gather_status_bf16();
+    return (a < 0 || b < 0 || c < 0 || d < 0 || e < 0) ? -1 : (a | b | c | d | e);
 }
 
 extern "C" int slotscan_profile_enable(int on) {

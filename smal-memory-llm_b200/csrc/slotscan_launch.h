@@ -56,6 +56,8 @@ constexpr int RM_SPARSE_ROWS = 32;
 bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
                       const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err);
 int read_mma_status();
+int gather_status_f32();
+int gather_status_bf16();
 int rows_bwd_status_f32();
 int rows_bwd_status_bf16();
 

@@ -5,3 +5,4 @@ from .scan import StreamingScan, kv_scan_c, kv_scan_g, scan_kv, scan_with_log, w
 from ._lib import kernel_attrs  # noqa: F401
 from .epilogue import fq, quantize_mem, writer_epilogue  # noqa: F401
 from .read import read_snapshots  # noqa: F401
+from .keyless import slot_scan_v  # noqa: F401

@@ -30,6 +30,11 @@ class DenseParams(ctypes.Structure):
     _fields_ = [("base", Params), ("hard", ctypes.c_int32), ("detach_addr", ctypes.c_int32)]
 
 
+class KeylessParams(ctypes.Structure):
+    """slotscan_v_params of include/slotscan.h."""
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "T", "H", "N", "DV", "G", "hard", "hard_gate", "in_dtype")]
+
+
 class FwdExtra(ctypes.Structure):
     """slotscan_fwd_extra of include/slotscan.h."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("K0", "V0", "o0", "nsq0", "nsqfin", "kinv", "valid")] + \
@@ -86,6 +91,15 @@ def lib():
         L.slotscan_dense_bwd_scratch_bytes.restype = sz
         L.slotscan_dense_bwd.argtypes = [DP] + [vp] * 12 + [sz] + [vp] * 7
         L.slotscan_dense_bwd.restype = ci
+        KP = ctypes.POINTER(KeylessParams)
+        L.slotscan_v_check.argtypes = [KP]
+        L.slotscan_v_check.restype = ci
+        L.slotscan_v_fwd.argtypes = [KP] + [vp] * 8
+        L.slotscan_v_fwd.restype = ci
+        L.slotscan_v_bwd_scratch_bytes.argtypes = [KP]
+        L.slotscan_v_bwd_scratch_bytes.restype = sz
+        L.slotscan_v_bwd.argtypes = [KP] + [vp] * 8 + [sz] + [vp] * 5
+        L.slotscan_v_bwd.restype = ci
         L.slotscan_hard_bwd_scratch_bytes.argtypes = [PP]
         L.slotscan_hard_bwd_scratch_bytes.restype = sz
         L.slotscan_hard_bwd.argtypes = [PP, vp, vp, vp, vp, vp, vp, LP, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, vp]
