@@ -16,7 +16,8 @@ Prints ONE JSON line:
              .step the same for the whole step, .touched_* with the bytes the kernels are obliged to move on THESE
              inputs (snapshot-gradient rows of slots that never were candidates reach no input and are skipped),
              .fill the step on inputs that use every slot
-  extra      one GPU only: the writer epilogue and one reader layer's cosine read over the snapshots of the same scan
+  extra      one GPU only: the reference's own CUDA scan timed on this GPU (when staged under baseline/_ref/), the
+             writer epilogue and one reader layer's cosine read over the snapshots of the same scan
   cpu_baseline  the CPU oracle (C, OpenMP) on a bounded sample of the same workload, on this box's host cores
 """
 import argparse
@@ -223,6 +224,24 @@ def cpu_leg(steps, warmup, threads=None, budget_s=60.0):
     return out
 
 
+def reference_kernel_leg(B, T, H, N, D, G, steps, warmup, dist="bench", seed=0, timeout_s=600):
+    """The reference's own CUDA scan (runtime-compiled, float32 streams and snapshots) on this GPU, in a process of its
+    own: baseline/time_reference_kernel.py over the modules staged under baseline/_ref/ (git-ignored).  A secondary
+    baseline beside the CPU arm; returns {"unavailable": why} when the staging is absent or the run fails."""
+    script = os.path.join(ROOT, "baseline", "time_reference_kernel.py")
+    if not os.path.isfile(os.path.join(ROOT, "baseline", "_ref", "gqa25", "slotkern_cuda.py")):
+        return {"unavailable": "baseline/_ref/gqa25 is not staged (baseline/stage_reference.py needs a reference checkout)"}
+    cmd = [sys.executable, script] + [str(x) for x in (B, T, H, N, D, G, steps, warmup, dist, seed)]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+        for ln in reversed(out.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"unavailable": "rc=%d: %s" % (out.returncode, (out.stderr.strip().splitlines() or ["no output"])[-1][:300])}
+    except Exception as e:                                             # noqa: BLE001 -- a baseline must not fail the bench
+        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:300])}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -236,6 +255,13 @@ def run_reference(args, rank, world):
                              "build": r["build"], "config0": r["config0"]},
             "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    try:
+        import torch
+        if torch.cuda.is_available():
+            line["reference_gpu_kernel"] = reference_kernel_leg(SHAPE["B"] // max(1, args.gpus), SHAPE["T"], SHAPE["H"], SHAPE["N"],
+                                                               SHAPE["DK"], SHAPE["G"], max(3, args.steps), max(3, args.warmup))
+    except ImportError:
+        pass
     emit(line)
 
 
@@ -244,11 +270,9 @@ def run_reference(args, rank, world):
 # (each taken at B = 8 sequences; traffic is proportional to the batch, so a launch over B sequences moves B / 8 of it).
 # A kernel that changed since its capture is taken out of this table until it is captured again.
 NCU_TRAFFIC_B8 = {
-    "replay_rows_k": (13.03e6 + 274.17e6, "profiles/replay_rows_128_bf16_small_case.md"),
-    "replay_rows_v": (13.03e6 + 274.17e6, "profiles/replay_rows_128_bf16_small_case.md"),
     "addr_fwd": (25.6e6, "profiles/addr_fwd_128_bf16_small_case.md"),
-    "rows_bwd_k": (107.8e6 + 16.7e6, "profiles/rows_bwd_128_bf16_small_case.md"),
-    "addr_bwd": (52.34e6 + 0.96e6, "profiles/addr_bwd_gather_128_bf16_small_case.md"),
+    "rows_bwd_k": (107.8e6 + 14.8e6, "profiles/rows_bwd_128_bf16_small_case.md"),
+    "addr_bwd": (52.35e6 + 1.28e6, "profiles/addr_bwd_gather_128_bf16_small_case.md"),
 }
 
 
@@ -454,10 +478,17 @@ def run_gpu(args, rank, local_rank, world):
         ab = algorithmic_bytes_per_token_head(N, DK, DV, G, 2, 2)
         peak, peak_kind = hbm_peak()
         # bytes each kernel is responsible for, per token and head (sums to ab["total"])
-        kb_bytes = {"addr_fwd": 2 * DK * 2 + 8, "replay_rows_k": N * DK * 2 / G, "replay_rows_v": DV * 2 + N * DV * 2 / G,
+        # Snapshot rows >= 64 are zero-filled by a kernel on a second stream while the address scan runs (they are zero
+        # for every sequence whose scan stays within 64 rows); the replay writes the rest.  Keys and values share one
+        # launch when dk == dv.
+        zf = 64 if N > 64 else N
+        kb_bytes = {"addr_fwd": 2 * DK * 2 + 8, "zero_fill": (N - zf) * (DK + DV) * 2 / G,
+                    "replay_rows_k": zf * (DK + DV) * 2 / G + DV * 2, "replay_rows_v": 0,
                     "rows_bwd_k": (DK + DV) * 2 + N * (DK + DV) * 2 / G + (DK + DV) * 2, "rows_bwd_v": 0,
                     "addr_bwd": DK * 2 + 8 + DK * 2 + 8, "finish": 0}
         if DK != DV:     # keys and values then run as two launches
+            kb_bytes["replay_rows_k"] = zf * DK * 2 / G
+            kb_bytes["replay_rows_v"] = DV * 2 + zf * DV * 2 / G
             kb_bytes["rows_bwd_k"] = DK * 2 + N * DK * 2 / G + DK * 2
             kb_bytes["rows_bwd_v"] = DV * 2 + N * DV * 2 / G + DV * 2
         launches = sum(c for c, _ in prof.values())
@@ -528,7 +559,9 @@ def run_gpu(args, rank, local_rank, world):
                                   "kernels_ms": {n: t / c for n, (c, t) in fprof.items() if c}}
                     del fjob
                     torch.cuda.empty_cache()
-                line["extra"] = {"read_bench": read_workload(args, local_rank, "bench"),
+                line["extra"] = {"reference_gpu_kernel": reference_kernel_leg(B, T, H, N, DK, G, 5, 3),
+                                 "reference_gpu_kernel_fill": reference_kernel_leg(B, T, H, N, DK, G, 3, 2, dist="fill"),
+                                 "read_bench": read_workload(args, local_rank, "bench"),
                                  "read_fill": read_workload(args, local_rank, "fill"),
                                  "epilogue": epilogue_workload(args, local_rank)}
             if not args.no_cpu:

@@ -34,6 +34,19 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// ---- bulk asynchronous copy shared -> global, tracked by bulk groups of the issuing thread ----
+// make shared-memory writes of this thread visible to the asynchronous proxy before a bulk copy reads them
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most PENDING of this thread's bulk groups still in flight (writes complete, not only the reads of the source)
+template <int PENDING>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
 // Bounded wait: a copy that never lands must not hang the GPU.  Returns false after ~0.2 s of polling.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
     for (int it = 0; it < (1 << 22); it++) {

@@ -51,9 +51,9 @@ struct ProfRec { int id; cudaEvent_t a, b; };
 static bool g_prof_on = false;
 static std::vector<ProfRec> g_prof;
 static std::mutex g_prof_mu;
-enum { K_ADDR_FWD = 0, K_REPLAY_K, K_REPLAY_V, K_ROWS_BWD_K, K_ROWS_BWD_V, K_ADDR_BWD, K_FINISH, K_NKERN };
+enum { K_ADDR_FWD = 0, K_REPLAY_K, K_REPLAY_V, K_ROWS_BWD_K, K_ROWS_BWD_V, K_ADDR_BWD, K_FINISH, K_ZERO_FILL, K_NKERN };
 static const char* const K_NAMES[K_NKERN] = {"addr_fwd", "replay_rows_k", "replay_rows_v", "rows_bwd_k", "rows_bwd_v",
-                                             "addr_bwd", "finish"};
+                                             "addr_bwd", "finish", "zero_fill"};
 struct ProfScope {
     int id; cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; bool on;
     ProfScope(int id_, cudaStream_t st_) : id(id_), st(st_), on(g_prof_on) {
@@ -66,29 +66,85 @@ struct ProfScope {
 
 constexpr size_t SMEM_CAP = 227 * 1024;
 
+// One extra stream per device so that the sequential address scan and the zero-fill of the snapshot rows its first
+// pass cannot touch run side by side.  Created on first use; lives until the process exits.
+constexpr int MAX_DEVICES = 64;
+static cudaStream_t g_side_stream[MAX_DEVICES] = {nullptr};
+static std::mutex g_side_mu;
+static cudaStream_t side_stream() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    std::lock_guard<std::mutex> l(g_side_mu);
+    if (g_side_stream[dev] == nullptr && cudaStreamCreateWithFlags(&g_side_stream[dev], cudaStreamNonBlocking) != cudaSuccess)
+        g_side_stream[dev] = nullptr;
+    return g_side_stream[dev];
+}
+
 static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
                            const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
                            const slotscan_fwd_extra& ex, cudaStream_t st) {
     cudaError_t e;
-    {
-        ProfScope ps(K_ADDR_FWD, st);
-        const AddrFwdState S0{ex.K0, ex.o0, ex.nsq0, ex.nsqfin};
-        e = (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, S0, st)
-                                         : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, S0, st);
+    // While the address scan runs (sequential, almost no memory traffic; on a second stream, see below) the snapshot
+    // rows its first pass cannot reach are zero-filled: rows >= AF_NCAP1 (rounded up to the row tiles of the replay) are zero in every
+    // snapshot of every sequence that finishes in that pass.  The replay, ordered after both, writes the rest and
+    // rewrites those tiles for the sequences that did need them.  Not with a carried-in state (its rows may be anywhere).
+    int zk = p.N, zv = p.N;
+    cudaEvent_t joined = nullptr, fork = nullptr;
+    cudaStream_t side = nullptr;
+    if (p.N > AF_NCAP1 && ex.K0 == nullptr) {
+        side = side_stream();
+        if (side != nullptr && cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) == cudaSuccess) {
+            auto up = [](int row, int tile) { return (row + tile - 1) / tile * tile; };
+            zk = min(up(AF_NCAP1, replay_tile_rows(p.DK)), p.N);
+            zv = min(up(AF_NCAP1, replay_tile_rows(p.DV)), p.N);
+            if ((e = cudaEventRecord(fork, st)) != cudaSuccess) { cudaEventDestroy(fork); cudaEventDestroy(joined); return e; }
+        } else {
+            if (fork != nullptr) cudaEventDestroy(fork);
+            if (joined != nullptr) cudaEventDestroy(joined);
+            fork = joined = nullptr;
+        }
+    }
+    const AddrFwdState S0{ex.K0, ex.o0, ex.nsq0, ex.nsqfin};
+    auto scan_on = [&](cudaStream_t s) {
+        ProfScope ps(K_ADDR_FWD, s);
+        return (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, S0, s)
+                                            : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, S0, s);
+    };
+    if (joined != nullptr) {
+        // The zero-fill goes on the caller's stream and the SCAN on the second stream, behind `fork`: the fill's CTAs (one
+        // per SM) are then placed first, on an idle machine, evenly, and three CTAs of the scan still fit beside each.
+        // The other way round the scan's 384 CTAs load the 148 SMs unevenly (3 on some, 2 on others) and the block
+        // scheduler packs every fill CTA onto the emptier SMs: the fill then runs at half the write bandwidth.
+        cudaError_t e2;
+        {
+            ProfScope ps(K_ZERO_FILL, st);
+            e2 = run_zero_rows(p, kbuf, zk, vbuf, zv, ex.kinv, ex.valid, st);
+        }
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(side, fork, 0);
+        if (e2 == cudaSuccess) e2 = scan_on(side);
+        if (e2 == cudaSuccess) e2 = cudaEventRecord(joined, side);
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);          // the replay comes after both
+        cudaEventDestroy(fork);
+        cudaEventDestroy(joined);
+        e = e2;
+    } else {
+        e = scan_on(st);
     }
     if (e != cudaSuccess) return e;
+    const ReplayPtrs rk{k, ex.K0, kbuf, ex.no_undo_log ? nullptr : L.kold, L.kfin, ex.kinv, ex.valid, zk};
+    const ReplayPtrs rv{v, ex.V0, vbuf, ex.no_undo_log ? nullptr : L.vold, L.vfin, nullptr, nullptr, zv};
+    if (p.DK == p.DV) {                                     // keys and values in one launch: their busy tiles overlap
+        ProfScope ps(K_REPLAY_K, st);
+        return run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, st);
+    }
     {
         ProfScope ps(K_REPLAY_K, st);
-        e = run_replay(p, p.DK, k, gate, L.addr, L.tfirst, ex.K0, kbuf, ex.no_undo_log ? nullptr : L.kold, L.kfin, ex.kinv,
-                       ex.valid, st);
+        e = run_replay(p, p.DK, 1, rk, rk, gate, L.addr, L.tfirst, st);
     }
     if (e != cudaSuccess) return e;
-    {
-        ProfScope ps(K_REPLAY_V, st);
-        e = run_replay(p, p.DV, v, gate, L.addr, L.tfirst, ex.V0, vbuf, ex.no_undo_log ? nullptr : L.vold, L.vfin, nullptr,
-                       nullptr, st);
-    }
-    return e;
+    ProfScope ps(K_REPLAY_V, st);
+    return run_replay(p, p.DV, 1, rv, rv, gate, L.addr, L.tfirst, st);
 }
 
 static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
@@ -267,8 +323,8 @@ extern "C" int slotscan_query_attrs(slotscan_kernel_attr* out, int cap) {
 extern "C" int slotscan_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     const int a = rows_bwd_status_f32(), b = rows_bwd_status_bf16(), c = read_mma_status();
-    const int d = gather_status_f32(), e = gather_status_bf16();
-    return (a < 0 || b < 0 || c < 0 || d < 0 || e < 0) ? -1 : (a | b | c | d | e);
+    const int d = gather_status_f32(), e = gather_status_bf16(), f = replay_status();
+    return (a < 0 || b < 0 || c < 0 || d < 0 || e < 0 || f < 0) ? -1 : (a | b | c | d | e | f);
 }
 
 extern "C" int slotscan_profile_enable(int on) {
@@ -308,7 +364,6 @@ extern "C" int slotscan_profile_read(slotscan_kernel_time* out, int cap) {
 // The array's name is only a host-side handle for the symbol; the device address a kernel can use comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
 static __device__ __align__(256) unsigned char g_fixed_scratch[SLOTSCAN_NOALLOC_SCRATCH_BYTES];
-constexpr int MAX_DEVICES = 64;
 static void* g_fixed_scratch_addr[MAX_DEVICES] = {nullptr};
 static std::mutex g_fixed_scratch_mu;
 

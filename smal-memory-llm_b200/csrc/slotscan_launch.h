@@ -33,10 +33,18 @@ cudaError_t run_addr_bwd_bf16(const slotscan_params& p, const void* q, const voi
 // tokens per CTA of the token-parallel address backward: the partial-sum table has one slot per such chunk (+ 1)
 constexpr int GATHER_CHUNK = 32;
 constexpr int GATHER_ROWS_MAX = 32;
-// one tensor (keys: D = DK, values: D = DV) through the forward row replay.  x0: the rows the replay starts from
-// (NULL = zeros); xold NULL: no undo log; kinv / valid: per emitted row, from the float32 state (keys only, or NULL)
-cudaError_t run_replay(const slotscan_params& p, int D, const void* x, const float* gate, const int* am, const int* tfirst,
-                       const float* x0, void* xbuf, float* xold, float* xfin, float* kinv, uint8_t* valid, cudaStream_t st);
+// One tensor (keys: D = DK, values: D = DV) of the forward row replay.  x0: the rows the replay starts from (NULL =
+// zeros); xold NULL: no undo log; kinv / valid: per emitted row, from the float32 state (keys only, or NULL);
+// zero_from: rows >= zero_from were zero-filled ahead by run_zero_rows (N = none).
+struct ReplayPtrs { const void* x; const float* x0; void* xbuf; float* xold; float* xfin; float* kinv; uint8_t* valid; int zero_from; };
+// ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs r0 only
+cudaError_t run_replay(const slotscan_params& p, int D, int ntensors, const ReplayPtrs& r0, const ReplayPtrs& r1,
+                       const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+int replay_tile_rows(int D);
+int replay_status();
+// zero-fill of rows [zk, N) of every key snapshot (+ kinv = 1e6, valid = 0 when given) and [zv, N) of every value snapshot
+cudaError_t run_zero_rows(const slotscan_params& p, void* kbuf, int zk, void* vbuf, int zv, float* kinv, uint8_t* valid,
+                          cudaStream_t st);
 // reverse row scan; ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs the first set only
 // dkinv: upstream gradient of the kinv output (keys only, NULL otherwise)
 struct RowsBwdPtrs { const void* x; const float* xold; const float* xfin; const void* dxbuf; void* dx; float* Dn; const float* dkinv; };

@@ -6,29 +6,21 @@
 // (The reverse row scan lives in slotscan_rows_bwd.cuh.)
 //
 // Layout: one group of LPR = D/8 lanes per row, 8 elements per lane in registers, RPB = 256 / LPR rows per CTA;
-// grid (B*H, row tiles).  Tokens are taken in chunks of RC = 32: the chunk's gates, a per-row bit mask of the tokens
-// that hit the row, and the chunk's token vectors are staged in shared memory once per CTA, so the walk over a chunk
-// is a walk over EVENTS (next hit, next snapshot) and never waits on a global load.  A tile whose rows are never
-// addressed (tfirst == T for all of them) only writes zeros (forward) or does nothing (reverse).
+// grid (B*H, row tiles, tensors).  Tokens are taken in chunks of RC = 32 through a two-stage shared-memory ring fed by
+// bulk asynchronous copies: the walk over a chunk is a walk over EVENTS (next hit, next snapshot) and never waits on
+// a global load.  A tile whose rows are never addressed (tfirst == T for all of them) only writes zeros, and not even
+// those where the rows were zero-filled ahead of time.
 #pragma once
+#include "slotscan_async.cuh"
 #include "slotscan_common.cuh"
 
 namespace slotscan {
 
+// Set when a bounded wait of the replay gave up (slotscan_device_status reads it through replay_status()).
+static __device__ int g_replay_status = 0;
+
 constexpr int ROW_THREADS = 256;
 constexpr int RC = 32;                        // tokens per staged chunk (hit mask per row: one bit per token)
-
-template <typename T>
-__device__ __forceinline__ void copy8(T* dst, const T* src);
-template <>
-__device__ __forceinline__ void copy8<float>(float* dst, const float* src) {
-    const float4 a = ld4(src), b = ld4(src + 4);
-    st4(dst, a); st4(dst + 4, b);
-}
-template <>
-__device__ __forceinline__ void copy8<__nv_bfloat16>(__nv_bfloat16* dst, const __nv_bfloat16* src) {
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-}
 
 // true if any row of this CTA's tile is ever a candidate (row 0 always is)
 __device__ __forceinline__ bool tile_active(const int* tfirst_bh, int n, bool live, int T, int* s_flag) {
@@ -37,27 +29,6 @@ __device__ __forceinline__ bool tile_active(const int* tfirst_bh, int n, bool li
     if (live && tfirst_bh[n] < T) *s_flag = 1;
     __syncthreads();
     return *s_flag != 0;
-}
-
-// stage one chunk: gates, per-row hit masks and (optionally) token vectors; the caller syncs afterwards
-template <int D, typename Tin>
-__device__ __forceinline__ void stage_chunk(const slotscan_params& p, int b, int h, int t0, int tc, int row0,
-                                            const float* __restrict__ gate, const int* __restrict__ am,
-                                            const Tin* __restrict__ x, float* s_g, unsigned long long* s_mask, Tin* s_x) {
-    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
-    const int tid = threadIdx.x, T = p.T, H = p.H;
-    for (int i = tid; i < RPB; i += ROW_THREADS) s_mask[i] = 0ull;
-    __syncthreads();
-    for (int i = tid; i < tc; i += ROW_THREADS) {
-        const size_t ix = ((size_t)b * T + t0 + i) * H + h;
-        s_g[i] = gate_eff(gate[ix], p.hard_gate);
-        const int a = am[ix] - row0;
-        if (a >= 0 && a < RPB) atomicOr(&s_mask[a], 1ull << i);
-    }
-    for (int it = tid; it < tc * LPR; it += ROW_THREADS) {
-        const int j = it / LPR, cc = (it % LPR) * 8;
-        copy8<Tin>(s_x + j * D + cc, x + (((size_t)b * T + t0 + j) * H + h) * D + cc);
-    }
 }
 
 // ======================================================================================================
@@ -78,21 +49,48 @@ __device__ __forceinline__ unsigned row_group_mask() {
     return (LPR >= 32) ? FULL : (((1u << LPR) - 1u) << (LPR * (lane / LPR)));
 }
 
-// NORM: also emit kinv / valid of every snapshot row (keys only).  x0 (may be NULL): the rows the replay starts from.
+// One tensor of a replay launch: blockIdx.z picks the keys (0) or the values (1) when both run in one launch.
+//   x0 (may be NULL): the rows the replay starts from; xold NULL: no undo log; kinv / valid (keys only, or NULL): per
+//   emitted row, from the float32 state; zero_from: rows >= zero_from of every snapshot (and their kinv / valid) have
+//   been zero-filled already by zero_rows_kernel, so a tile there that never becomes a candidate writes nothing
+//   (N = no prefill).
+template <typename Tin, typename Tsn>
+struct ReplayArgs {
+    const Tin* x;
+    const float* x0;
+    Tsn* xbuf;
+    float* xold;
+    float* xfin;
+    float* kinv;
+    uint8_t* valid;
+    int zero_from;
+};
+
+// NORM: kinv / valid may be asked for (checked per tensor at run time).
 template <int D, typename Tin, typename Tsn, bool NORM>
 __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
-    const slotscan_params p, const Tin* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ am,
-    const int* __restrict__ tfirst, const float* __restrict__ x0, Tsn* __restrict__ xbuf, float* __restrict__ xold,
-    float* __restrict__ xfin, float* __restrict__ kinv_out, uint8_t* __restrict__ valid_out) {
-    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR;
-    __shared__ float s_g[RC];
-    __shared__ unsigned long long s_mask[RPB];
-    __shared__ __align__(16) Tin s_x[RC * D];
+    const slotscan_params p, const ReplayArgs<Tin, Tsn> a0, const ReplayArgs<Tin, Tsn> a1,
+    const float* __restrict__ gate, const int* __restrict__ am, const int* __restrict__ tfirst) {
+    const ReplayArgs<Tin, Tsn>& A = blockIdx.z ? a1 : a0;
+    const Tin* __restrict__ x = A.x;
+    const float* __restrict__ x0 = A.x0;
+    Tsn* __restrict__ xbuf = A.xbuf;
+    float* __restrict__ xold = A.xold;
+    float* __restrict__ xfin = A.xfin;
+    float* __restrict__ kinv_out = A.kinv;
+    uint8_t* __restrict__ valid_out = A.valid;
+    const bool norm = NORM && kinv_out != nullptr;
+    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR, RPW = 32 / LPR;
+    __shared__ float s_g[2][RC];                                     // gates of the chunk in work / the next one
+    __shared__ int s_am[2][RC];                                      // addressed row - row0 (negative: not in this tile)
+    __shared__ __align__(128) Tin s_x[2][RC * D];                    // token vectors, two stages (bulk async copies)
+    __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ int s_flag;
     const int N = p.N, T = p.T, H = p.H, G = p.G;
     const int NB = (T + G - 1) / G;
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
-    const int tid = threadIdx.x, r = tid / LPR, c = tid % LPR, row0 = blockIdx.y * RPB, n = row0 + r;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = tid / LPR, c = tid % LPR, row0 = blockIdx.y * RPB, n = row0 + r;
     const bool live = n < N;
     float X[8];
 #pragma unroll
@@ -105,30 +103,89 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
 
     if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) {
         if (live) {                                                  // never a candidate: the row stays zero
-            for (int j = 0; j < NB; j++) st8(snap + j * snap_stride, X);
             st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
-            if (NORM && c == 0) {
-                for (int j = 0; j < NB; j++) { kinv_out[norm_ix + j * norm_stride] = 1e6f; valid_out[norm_ix + j * norm_stride] = 0; }
+            if (row0 < A.zero_from) {                                // (tiles at or above zero_from were zero-filled ahead)
+                for (int j = 0; j < NB; j++) st8(snap + j * snap_stride, X);
+                if (norm && c == 0) {
+                    for (int j = 0; j < NB; j++) { kinv_out[norm_ix + j * norm_stride] = 1e6f; valid_out[norm_ix + j * norm_stride] = 0; }
+                }
             }
         }
         return;
     }
     if (x0 != nullptr && live) ld8(X, x0 + ((size_t)bh * N + n) * D + c * 8);   // state carried in from the preceding chunk
     const unsigned gmask = row_group_mask<LPR>();
+    // Chunks of RC tokens through a two-stage ring: while the rows walk chunk k, the token vectors of chunk k + 1 are
+    // being copied (bulk async, one mbarrier per stage) and the gates / addresses of chunk k + 2 are in flight.
+    const int nchunk = (T + RC - 1) / RC;
+    float pre_g = 0.f;
+    int pre_a = -1;
+    auto load_scalars = [&](int ck) {
+        pre_g = 0.f; pre_a = -1;
+        const int t = ck * RC + tid;
+        if (tid < RC && t < T) {
+            const size_t ix = ((size_t)b * T + t) * H + h;
+            pre_g = gate_eff(gate[ix], p.hard_gate);
+            pre_a = am[ix] - row0;
+            if (pre_a >= RPB) pre_a = -1;
+        }
+    };
+    auto issue_x = [&](int ck, int st) {                             // warp 0
+        const int t = ck * RC + lane;
+        const bool in = t < T;
+        const unsigned nin = __popc(__ballot_sync(FULL, in));
+        if (lane == 0) mbar_arrive_expect_tx(&s_bar[st], nin * (unsigned)(D * sizeof(Tin)));
+        __syncwarp();
+        if (in) bulk_g2s(&s_x[st][lane * D], x + (((size_t)b * T + t) * H + h) * D, D * sizeof(Tin), &s_bar[st]);
+    };
+    if (tid == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        mbar_fence_init();
+    }
+    load_scalars(0);
+    __syncthreads();
+    if (warp == 0) {
+        s_g[0][lane] = pre_g;
+        s_am[0][lane] = pre_a;
+        __syncwarp();
+        issue_x(0, 0);
+    }
+    load_scalars(1);
     int tsnap = 0;                                                   // next snapshot time (multiple of G)
-    for (int t0 = 0; t0 < T; t0 += RC) {
-        const int tc = min(RC, T - t0);
-        __syncthreads();
-        stage_chunk<D, Tin>(p, b, h, t0, tc, row0, gate, am, x, s_g, s_mask, s_x);
-        __syncthreads();
+    for (int k = 0; k < nchunk; k++) {
+        const int t0 = k * RC, tc = min(RC, T - t0), st = k & 1;
+        __syncthreads();                                             // every row is done with chunk k - 1 (stage st ^ 1)
+        if (warp == 0 && k + 1 < nchunk) {
+            s_g[st ^ 1][lane] = pre_g;
+            s_am[st ^ 1][lane] = pre_a;
+            __syncwarp();
+            issue_x(k + 1, st ^ 1);
+        }
+        load_scalars(k + 2);
+        const bool landed = mbar_wait_bounded(&s_bar[st], (unsigned)(k >> 1) & 1u);
+        if (!__syncthreads_and(landed ? 1 : 0)) {                    // a copy never landed: give up, all threads together
+            if (tid == 0) atomicExch(&g_replay_status, 1);
+            return;
+        }
+        unsigned m = 0u;                                             // bit i: token t0 + i writes this lane's row
+        {
+            const int aL = s_am[st][lane];
+#pragma unroll
+            for (int rr = 0; rr < RPW; rr++) {
+                const unsigned bm = __ballot_sync(FULL, aL == warp * RPW + rr);
+                if (rr == lane / LPR) m = bm;
+            }
+        }
         if (!live) continue;
-        const unsigned long long m = s_mask[r];
+        const Tin* sx = s_x[st];
+        const float* sg = s_g[st];
         int i = 0;
         while (true) {
-            const unsigned long long mm = m >> i;                    // i < tc <= 64 here
-            const int ih = mm ? i + __ffsll((long long)mm) - 1 : tc; // next token that writes this row
+            const unsigned mm = m >> i;                              // i < tc <= 32 here
+            const int ih = mm ? i + __ffs((int)mm) - 1 : tc;         // next token that writes this row
             const int tlast = t0 + min(ih, tc - 1);
-            if (NORM) {
+            if (norm) {
                 if (tsnap <= tlast) {                                // the state is the same for every snapshot of this stretch
                     const float nsq = row_nsq<LPR>(X, gmask);
                     if (c == 0) {
@@ -145,9 +202,9 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
             }
             if (ih >= tc) break;
             const size_t ix = ((size_t)b * T + t0 + ih) * H + h;
-            const float g = s_g[ih], omw = 1.f - g;
+            const float g = sg[ih], omw = 1.f - g;
             float xv[8];
-            ld8(xv, s_x + ih * D + c * 8);
+            ld8(xv, sx + ih * D + c * 8);
             if (xold != nullptr) st8(xold + ix * D + c * 8, X);
 #pragma unroll
             for (int j = 0; j < 8; j++) X[j] = blend(X[j], xv[j], g, omw);
@@ -156,6 +213,81 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
         }
     }
     if (live) st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+}
+
+// ======================================================================================================
+// Zero-fill of the rows [zero_from, N) of every snapshot (and their kinv = 1e6 / valid = 0), launched on a second
+// stream while the sequential address scan runs: the scan needs almost no memory bandwidth, and its first pass holds
+// only the first AF_NCAP1 rows, so every sequence that finishes in that pass leaves the rows above untouched -- they
+// are zero in every snapshot.  Sequences that do need them (second pass) rewrite those tiles afterwards in the replay,
+// which is ordered after this kernel.  Small CTAs (2 warps, few registers) so that they fit beside the scan's CTAs.
+constexpr int ZR_THREADS = 64;
+template <typename Tsn>
+__global__ void __launch_bounds__(ZR_THREADS) zero_rows_kernel(Tsn* __restrict__ xbuf, float* __restrict__ kinv,
+                                                              uint8_t* __restrict__ valid, const int N, const int D,
+                                                              const int zero_from, const long long nsnap) {
+    const size_t row_bytes = (size_t)D * sizeof(Tsn);
+    const size_t chunk16 = (size_t)(N - zero_from) * row_bytes / 16;           // 16-byte pieces per snapshot
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (long long so = blockIdx.x; so < nsnap; so += gridDim.x) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(xbuf) + ((size_t)so * N + zero_from) * row_bytes);
+        for (size_t i = threadIdx.x; i < chunk16; i += ZR_THREADS) dst[i] = z;
+        if (kinv != nullptr) {
+            for (int n = zero_from + threadIdx.x; n < N; n += ZR_THREADS) {
+                kinv[(size_t)so * N + n] = 1e6f;
+                valid[(size_t)so * N + n] = 0;
+            }
+        }
+    }
+}
+
+// The same fill through the bulk-copy engine of the SM: one thread per CTA streams a zeroed shared-memory buffer to
+// global memory with bulk asynchronous stores, one CTA per SM, both tensors in one launch.  Measured beside a
+// resident kernel shaped like the scan (three CTAs of 73 KB per SM): the fill runs at the full write bandwidth
+// (6.2 TB/s) when its CTAs are spread one per SM, and at half of it when they are launched after a scan whose CTAs
+// load the SMs unevenly (384 CTAs on 148 SMs: the block scheduler then packs every fill CTA onto the 60 emptier SMs).
+// So this kernel is submitted BEFORE the scan, with exactly one CTA per SM and little enough shared memory
+// (ZB_BYTES) that three CTAs of the scan still fit beside it.
+// Requires 16-byte aligned regions: (N - zero_from) * row_bytes, zero_from * row_bytes and N * row_bytes multiples of 16.
+struct ZeroTarget {
+    unsigned char* x;      // snapshot tensor (nsnap, N, row_bytes), or NULL
+    size_t row_bytes;
+    int zero_from;
+};
+constexpr int ZB_THREADS = 32;
+constexpr int ZB_BYTES = 8192;
+constexpr int ZB_DEPTH = 8;
+static __global__ void __launch_bounds__(ZB_THREADS) zero_rows_bulk_kernel(const ZeroTarget ta, const ZeroTarget tb,
+                                                                          float* __restrict__ kinv, uint8_t* __restrict__ valid,
+                                                                          const int N, const long long nsnap) {
+    __shared__ __align__(128) unsigned char s_zero[ZB_BYTES];
+    for (int i = threadIdx.x; i < ZB_BYTES / 16; i += ZB_THREADS) reinterpret_cast<uint4*>(s_zero)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+    __syncwarp();
+    for (long long so = blockIdx.x; so < nsnap; so += gridDim.x) {
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int w = 0; w < 2; w++) {
+                const ZeroTarget& t = w ? tb : ta;
+                if (t.x == nullptr) continue;
+                const size_t region = (size_t)(N - t.zero_from) * t.row_bytes;
+                unsigned char* dst = t.x + ((size_t)so * N + t.zero_from) * t.row_bytes;
+                for (size_t off = 0; off < region; off += ZB_BYTES) {
+                    const size_t nb = region - off < (size_t)ZB_BYTES ? region - off : (size_t)ZB_BYTES;
+                    bulk_s2g(dst + off, s_zero, (unsigned)nb);
+                    bulk_commit();
+                    bulk_wait_read<ZB_DEPTH>();
+                }
+            }
+        } else if (kinv != nullptr) {
+            for (int n = ta.zero_from + (int)threadIdx.x - 1; n < N; n += ZB_THREADS - 1) {
+                kinv[(size_t)so * N + n] = 1e6f;
+                valid[(size_t)so * N + n] = 0;
+            }
+        }
+    }
+    if (threadIdx.x == 0) bulk_wait<0>();          // the buffer must outlive the copies that read it
+    __syncwarp();
 }
 
 // ======================================================================================================
