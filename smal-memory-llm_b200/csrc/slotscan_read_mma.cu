@@ -16,6 +16,7 @@
 //     reference multiplies att.to(bf16) as well), normalisation by 1 / sum is applied to the float32 result;
 //   * P V: each warp owns a quarter of the value columns, V fragments through ldmatrix.trans.
 // Other dtypes and widths take the CUDA-core kernel of slotscan_read.cu.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -269,6 +270,329 @@ __global__ void __launch_bounds__(RM_THREADS, 2) read_fwd_mma_kernel(
     }
 }
 
+
+// ======================================================================================================
+// The same read as a PERSISTENT kernel, one CTA per SM walking its share of the snapshots through a two-stage ring:
+// while the tensor cores work on snapshot i, the rows of snapshot i + 1 are already in flight and the kinv / valid
+// vectors of snapshot i + 2 behind them.  The kernel above pays, per snapshot, a serial chain "which rows count ->
+// rows land -> Q K^T -> softmax -> P V" (about 20 us with two CTAs per SM: 17 % of DRAM peak); here only the math is
+// left on that chain.
+//   * key / value tiles come in by TILED bulk tensor copies (a 3-D tensor map over (snapshot, row, column), box
+//     64 columns x 64 / 128 / 192 rows, 128-byte swizzle): 2 copies per tensor and snapshot instead of one per row,
+//     no row padding, and ldmatrix reads the swizzled tile without bank conflicts (16-byte chunk c of row r sits at
+//     chunk c ^ (r & 7));
+//   * the box height is the smallest that covers the highest valid row, read from the prefetched valid vector;
+//   * the 16 query rows and the kinv / valid vectors by plain bulk copies; sharp by ordinary loads one snapshot ahead.
+// Needs G * NQ <= 16, N a multiple of 16 and dk = dv in {64, 128}; other shapes take the kernel above.
+constexpr int RR_THREADS = 256, RR_WARPS = 8;          // two warps per scheduler: the per-snapshot chain is latency-bound
+constexpr int RR_TPW = RM_MAXN / 8 / RR_WARPS;         // 8-row tiles per warp
+constexpr int RR_ROWS = RM_MAXN;                       // rows per sub-tile slot in shared memory
+constexpr int RR_SUB = RR_ROWS * 128;                  // bytes of one 64-column sub-tile slot (a multiple of 1024)
+struct ReadMaps { CUtensorMap k[3], v[3]; };           // box heights min(N, 64), min(N, 128), N
+
+struct ReadRingSmem { int stage, stage_bytes, q, q_bytes, meta, kv, red, scale, sharp, nv, bar, total; int ldp; };
+__host__ __device__ inline ReadRingSmem read_ring_layout(int DK) {
+    ReadRingSmem L;
+    const int nsub = DK / 64;
+    L.ldp = RM_MAXN + 8;
+    L.stage = 0;
+    L.stage_bytes = 2 * nsub * RR_SUB;                 // keys then values
+    L.q = 2 * L.stage_bytes;
+    L.q_bytes = 16 * L.ldp * 2;                        // 16 query rows; reused for P once the fragments are in registers
+    L.meta = L.q + 2 * L.q_bytes;                      // 2 x (kinv [N] f32 | valid [N] u8), 1 KB each
+    L.kv = L.meta + 2 * 1024;
+    L.red = L.kv + RM_MAXN * 4;
+    L.scale = L.red + 2 * RR_WARPS * 16 * 4;
+    L.sharp = L.scale + 16 * 4;
+    L.nv = L.sharp + 16 * 4;                           // [0..1] highest valid row + 1 per stage, [2] failure flag
+    L.bar = L.nv + 16;                                 // meta[2], queries+keys[2], values[2]
+    L.total = L.bar + 6 * 8;
+    return L;
+}
+
+__device__ __forceinline__ void tensor_g2s_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+template <int DK>
+__global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
+    const slotscan_read_params p, const __grid_constant__ ReadMaps maps, const bf16* __restrict__ qr,
+    const float* __restrict__ sharp, const float* __restrict__ kinv, const uint8_t* __restrict__ valid,
+    bf16* __restrict__ rd, const int nitems) {
+    constexpr int DV = DK, NSUB = DK / 64;
+    extern __shared__ __align__(128) unsigned char rsm[];
+    // the swizzled tiles want a 1024-byte boundary (the launch adds 1 KB of slack for this)
+    unsigned char* const rsmb = rsm + ((1024u - (smem_u32(rsm) & 1023u)) & 1023u);
+    const int N = p.N, T = p.T, H = p.H, NQ = p.NQ, G = p.G;
+    const int NB = (T + G - 1) / G;
+    const ReadRingSmem L = read_ring_layout(DK);
+    float* s_kv = reinterpret_cast<float*>(rsmb + L.kv);
+    float* s_red = reinterpret_cast<float*>(rsmb + L.red);
+    float* s_scale = reinterpret_cast<float*>(rsmb + L.scale);
+    float* s_sharp = reinterpret_cast<float*>(rsmb + L.sharp);
+    volatile int* s_nv = reinterpret_cast<int*>(rsmb + L.nv);
+    uint64_t* barM = reinterpret_cast<uint64_t*>(rsmb + L.bar);
+    uint64_t* barL = barM + 2;
+    uint64_t* barV = barM + 4;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int first = blockIdx.x, stride = gridDim.x;
+    const int h64 = min(N, 64), h128 = min(N, 128);
+
+    auto meta_k = [&](int slot) { return reinterpret_cast<float*>(rsmb + L.meta + slot * 1024); };
+    auto meta_v = [&](int slot) { return rsmb + L.meta + slot * 1024 + RM_MAXN * 4; };
+    auto q_stage = [&](int s) { return reinterpret_cast<bf16*>(rsmb + L.q + s * L.q_bytes); };
+    // queries of snapshot `it`: (b, block, h) -> token t0 + m / NQ, query m % NQ
+    auto q_index = [&](int it, int m) {
+        const int hh = it % H, nb = (it / H) % NB, bb = it / (H * NB);
+        return (((size_t)bb * T + nb * G + m / NQ) * H + hh) * NQ + m % NQ;
+    };
+    auto q_count = [&](int it) { const int nb = (it / H) % NB; return min(G, T - nb * G) * NQ; };
+    // warp 0 only --------------------------------------------------------------------------------------------------
+    auto issue_meta = [&](int it, int slot) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&barM[slot], (unsigned)(N * 5));
+            bulk_g2s(meta_k(slot), kinv + (size_t)it * N, N * 4, &barM[slot]);
+            bulk_g2s(meta_v(slot), valid + (size_t)it * N, N, &barM[slot]);
+        }
+    };
+    auto scan_nv = [&](int slot) {
+        const unsigned char* mv = meta_v(slot);
+        int hi = 0;
+        for (int n = lane; n < N; n += 32) if (mv[n] != 0) hi = n + 1;
+        return (int)__reduce_max_sync(FULL, (unsigned)hi);
+    };
+    auto issue_loads = [&](int it, int s, int nv) {
+        const int sel = nv <= h64 ? 0 : (nv <= h128 ? 1 : 2);
+        const int rows = sel == 0 ? h64 : (sel == 1 ? h128 : N);
+        const int M = q_count(it);
+        unsigned char* st = rsmb + L.stage + s * L.stage_bytes;
+        fence_proxy_async_smem();                                  // the stage was last written (P) and read through the generic proxy
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&barL[s], (unsigned)(M * DK * 2 + rows * DK * 2));
+            mbar_arrive_expect_tx(&barV[s], (unsigned)(rows * DV * 2));
+        }
+        __syncwarp();
+        if (lane < NSUB) tensor_g2s_3d(st + lane * RR_SUB, &maps.k[sel], lane * 64, 0, it, &barL[s]);
+        else if (lane < 2 * NSUB) tensor_g2s_3d(st + lane * RR_SUB, &maps.v[sel], (lane - NSUB) * 64, 0, it, &barV[s]);
+        if (lane < M) bulk_g2s(q_stage(s) + (size_t)lane * L.ldp, qr + q_index(it, lane) * DK, DK * 2, &barL[s]);
+    };
+
+    if (tid == 0) {
+        for (int i = 0; i < 6; i++) mbar_init(&barM[i], 1);
+        mbar_fence_init();
+        s_nv[0] = s_nv[1] = s_nv[2] = 0;
+    }
+    for (int i = tid; i < 2 * L.q_bytes / 16; i += RR_THREADS)            // query rows beyond a short last block stay zero
+        reinterpret_cast<uint4*>(rsmb + L.q)[i] = make_uint4(0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+    __syncthreads();
+    float shn = 0.f;                                                       // sharp of the NEXT snapshot's query tid (< 16)
+    if (first < nitems) {
+        if (warp == 0) {
+            issue_meta(first, 0);
+            if (first + stride < nitems) issue_meta(first + stride, 1);
+            const bool ok = mbar_wait_bounded(&barM[0], 0u);
+            const int nv0 = ok ? scan_nv(0) : 0;
+            if (lane == 0) { s_nv[0] = nv0; if (!ok) s_nv[2] = 1; }
+            if (nv0 > RM_SPARSE_ROWS) issue_loads(first, 0, nv0);
+            if (nv0 > RM_SPARSE_ROWS && tid < 16 && tid < q_count(first)) shn = sharp[q_index(first, tid)];
+        }
+    }
+    __syncthreads();
+    unsigned phL = 0u, phV = 0u;                                 // bit s: parity of the next wait on stage s
+    bool failed = false;
+    const int r0 = lane >> 2, cq = (lane & 3) * 2;             // this thread's rows r0, r0 + 8 and column pair in a C tile
+    int i = 0;
+    for (int it = first; it < nitems; it += stride, i++) {
+        const int s = i & 1;
+        if (s_nv[2] != 0) break;                                           // a bounded wait gave up (uniform: read after a barrier)
+        const int nv = s_nv[s];
+        const int M = q_count(it);
+        const int NPv = (nv + 15) & ~15;
+        // (a) this snapshot's kinv / valid -> kinv or -1; sharp of its queries (nothing to do for a snapshot that is left
+        //     to the CUDA-core kernel: warp 0 has already scanned its valid vector)
+        if (nv > RM_SPARSE_ROWS) {
+            const float* mk = meta_k(s);
+            const unsigned char* mv = meta_v(s);
+            for (int n = tid; n < RM_MAXN; n += RR_THREADS) s_kv[n] = (n < N && mv[n] != 0) ? mk[n] : -1.f;
+            if (tid < 16) s_sharp[tid] = tid < M ? shn : 0.f;
+            __syncthreads();
+        }
+        // (b) warp 0: rows of the next snapshot in flight, kinv / valid of the one after
+        if (warp == 0) {
+            const int itn = it + stride;
+            if (itn < nitems) {
+                const bool ok = mbar_wait_bounded(&barM[s ^ 1], (unsigned)(((i + 1) >> 1) & 1));
+                const int nvn = ok ? scan_nv(s ^ 1) : 0;
+                if (lane == 0) { s_nv[s ^ 1] = nvn; if (!ok) s_nv[2] = 1; }
+                if (nvn > RM_SPARSE_ROWS) issue_loads(itn, s ^ 1, nvn);
+                shn = (nvn > RM_SPARSE_ROWS && tid < 16 && tid < q_count(itn)) ? sharp[q_index(itn, tid)] : 0.f;
+            }
+            if (it + 2 * stride < nitems) issue_meta(it + 2 * stride, s);
+        }
+        // (c) the read itself; snapshots with few rows are left to the CUDA-core kernel
+        if (nv > RM_SPARSE_ROWS) {
+            const unsigned char* Kst = rsmb + L.stage + s * L.stage_bytes;
+            const unsigned char* Vst = Kst + NSUB * RR_SUB;
+            bf16* PQ = q_stage(s);
+            bool ok = mbar_wait_bounded(&barL[s], (phL >> s) & 1u);
+            phL ^= 1u << s;
+            if (!__syncthreads_and(ok ? 1 : 0)) { failed = true; break; }
+            for (int mm = warp; mm < 16; mm += RR_WARPS) {         // |q| in float32, 4 rows per warp
+                float qq = 0.f;
+                for (int d = lane; d < DK; d += 32) { const float x = __bfloat162float(PQ[(size_t)mm * L.ldp + d]); qq = fmaf(x, x, qq); }
+                qq = warp_sum(qq);
+                if (lane == 0) s_scale[mm] = mm < M ? s_sharp[mm] / fmaxf(sqrtf(qq), 1e-6f) : 0.f;
+            }
+            unsigned qa[DK / 16][4];                               // A fragments of the query tile
+#pragma unroll
+            for (int ks = 0; ks < DK / 16; ks++)
+                ldsm_x4(qa[ks], PQ + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldp + ks * 16 + (lane >> 4) * 8);
+            __syncthreads();                                       // scales written, every warp holds its Q fragments: PQ is free for P
+            // ---- S = Q K^T over this warp's row tiles, scaled and masked ----
+            float sc[RR_TPW][4];
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+            const float sca = s_scale[r0], scb = s_scale[r0 + 8];
+#pragma unroll
+            for (int j = 0; j < RR_TPW; j++) {
+                const int nt = warp + j * RR_WARPS;                // 8-row tile index
+                sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = -INFINITY;
+                if (nt * 8 < NPv) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const int row = nt * 8 + (lane & 7);
+#pragma unroll
+                    for (int ks = 0; ks < DK / 16; ks++) {
+                        const int cidx = ks * 2 + ((lane >> 3) & 1);
+                        unsigned b0, b1;
+                        ldsm_x2(b0, b1, Kst + (cidx >> 3) * RR_SUB + row * 128 + (((cidx & 7) ^ (row & 7)) << 4));
+                        mma_bf16(acc, qa[ks], b0, b1);
+                    }
+                    const float k0 = s_kv[nt * 8 + cq], k1 = s_kv[nt * 8 + cq + 1];
+                    sc[j][0] = k0 >= 0.f ? acc[0] * k0 * sca : -INFINITY;
+                    sc[j][1] = k1 >= 0.f ? acc[1] * k1 * sca : -INFINITY;
+                    sc[j][2] = k0 >= 0.f ? acc[2] * k0 * scb : -INFINITY;
+                    sc[j][3] = k1 >= 0.f ? acc[3] * k1 * scb : -INFINITY;
+                    mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+                    mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, 2));
+            if ((lane & 3) == 0) { s_red[warp * 16 + r0] = mx0; s_red[warp * 16 + r0 + 8] = mx1; }
+            __syncthreads();
+            mx0 = s_red[r0]; mx1 = s_red[r0 + 8];
+#pragma unroll
+            for (int w = 1; w < RR_WARPS; w++) { mx0 = fmaxf(mx0, s_red[w * 16 + r0]); mx1 = fmaxf(mx1, s_red[w * 16 + r0 + 8]); }
+            // ---- P = exp(S - max) as bf16 into the query tile's place ----
+            float su0 = 0.f, su1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < RR_TPW; j++) {
+                const int nt = warp + j * RR_WARPS;
+                if (nt * 8 < NPv) {
+                    const float e0 = __expf(sc[j][0] - mx0), e1 = __expf(sc[j][1] - mx0);   // exp(-inf) = 0 for masked rows
+                    const float e2 = __expf(sc[j][2] - mx1), e3 = __expf(sc[j][3] - mx1);
+                    su0 += e0 + e1; su1 += e2 + e3;
+                    *reinterpret_cast<__nv_bfloat162*>(PQ + (size_t)r0 * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e0, e1);
+                    *reinterpret_cast<__nv_bfloat162*>(PQ + (size_t)(r0 + 8) * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e2, e3);
+                }
+            }
+            su0 += __shfl_xor_sync(FULL, su0, 1); su0 += __shfl_xor_sync(FULL, su0, 2);
+            su1 += __shfl_xor_sync(FULL, su1, 1); su1 += __shfl_xor_sync(FULL, su1, 2);
+            float* s_sum = s_red + RR_WARPS * 16;
+            if ((lane & 3) == 0) { s_sum[warp * 16 + r0] = su0; s_sum[warp * 16 + r0 + 8] = su1; }
+            ok = mbar_wait_bounded(&barV[s], (phV >> s) & 1u);
+            phV ^= 1u << s;
+            if (!__syncthreads_and(ok ? 1 : 0)) { failed = true; break; }
+            // ---- O = P V: this warp's quarter of the value columns ----
+            constexpr int DT = DV / 8 / RR_WARPS;                  // 8-column tiles per warp
+            float o[DT][4];
+#pragma unroll
+            for (int j = 0; j < DT; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+            for (int ks = 0; ks < NPv / 16; ks++) {
+                unsigned pa[4];
+                ldsm_x4(pa, PQ + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldp + ks * 16 + (lane >> 4) * 8);
+                const int row = ks * 16 + (lane & 15);
+#pragma unroll
+                for (int j = 0; j < DT; j++) {
+                    const int cidx = warp * DT + j;
+                    unsigned b0, b1;
+                    ldsm_x2_trans(b0, b1, Vst + (cidx >> 3) * RR_SUB + row * 128 + (((cidx & 7) ^ (row & 7)) << 4));
+                    mma_bf16(o[j], pa, b0, b1);
+                }
+            }
+            float t0s = 0.f, t1s = 0.f;
+#pragma unroll
+            for (int w = 0; w < RR_WARPS; w++) { t0s += s_sum[w * 16 + r0]; t1s += s_sum[w * 16 + r0 + 8]; }
+            const float inv0 = 1.f / t0s, inv1 = 1.f / t1s;
+#pragma unroll
+            for (int j = 0; j < DT; j++) {
+                const int d = (warp * DT + j) * 8 + cq;
+                if (r0 < M)
+                    *reinterpret_cast<__nv_bfloat162*>(rd + q_index(it, r0) * DV + d) = __floats2bfloat162_rn(o[j][0] * inv0, o[j][1] * inv0);
+                if (r0 + 8 < M)
+                    *reinterpret_cast<__nv_bfloat162*>(rd + q_index(it, r0 + 8) * DV + d) = __floats2bfloat162_rn(o[j][2] * inv1, o[j][3] * inv1);
+            }
+        }
+        __syncthreads();                                           // this stage, its query tile and the exchange arrays are free
+    }
+    if (failed || s_nv[2] != 0) {                                  // a bounded wait gave up: report, and give the copies still
+        if (tid == 0) atomicExch(&g_read_status, 1);               // in flight into this CTA's shared memory time to land
+        for (int k = 0; k < 1000; k++) __nanosleep(1000);
+    }
+}
+
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (TensorMapEncodeFn)f;
+    }();
+    return fn;
+}
+
+// (snapshot, row, column) bf16 tensor with a box of 64 columns x `rows` rows of one snapshot, 128-byte swizzle
+static bool snapshot_map(CUtensorMap* m, const void* base, long long nsnap, int N, int D, int rows) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)nsnap};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)rows, 1u};
+    const cuuint32_t es[3] = {1u, 1u, 1u};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// false when the ring kernel does not apply (shape, or no tensor-map support in the driver): the caller falls back
+template <int DK>
+static bool launch_ring(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
+                        const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err) {
+    const int NB = (p.T + p.G - 1) / p.G;
+    const long long nsnap = (long long)p.B * NB * p.H;
+    if (p.N % 16 || p.G * p.NQ > 16 || nsnap > 2147483647LL || (((uintptr_t)kinv | (uintptr_t)valid) & 15)) return false;
+    ReadMaps maps;
+    const int hs[3] = {p.N < 64 ? p.N : 64, p.N < 128 ? p.N : 128, p.N};
+    for (int i = 0; i < 3; i++)
+        if (!snapshot_map(&maps.k[i], kbuf, nsnap, p.N, DK, hs[i]) || !snapshot_map(&maps.v[i], vbuf, nsnap, p.N, DK, hs[i])) return false;
+    const size_t sm = (size_t)read_ring_layout(DK).total + 1024;      // + slack: the stages start on a 1024-byte boundary
+    auto kern = read_fwd_ring_kernel<DK>;
+    if ((*err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return true;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(nsnap < sms ? nsnap : sms);
+    kern<<<grid, RR_THREADS, sm, st>>>(p, maps, (const bf16*)qr, sharp, kinv, valid, (bf16*)rd, (int)nsnap);
+    *err = cudaGetLastError();
+    return true;
+}
+
 template <int DK, int DV>
 static cudaError_t launch_mma(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf,
                               const void* vbuf, const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st) {
@@ -288,9 +612,15 @@ bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float
                       const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err) {
     if (p.q_dtype != SLOTSCAN_BF16 || p.snap_dtype != SLOTSCAN_BF16 || p.N > RM_MAXN || p.DK != p.DV) return false;
     if (((uintptr_t)qr | (uintptr_t)kbuf | (uintptr_t)vbuf | (uintptr_t)rd) & 15) return false;
-    if (p.DK == 128) *err = launch_mma<128, 128>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
-    else if (p.DK == 64) *err = launch_mma<64, 64>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
-    else return false;
+    if (p.DK == 128) {
+        if (!launch_ring<128>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st, err))
+            *err = launch_mma<128, 128>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    } else if (p.DK == 64) {
+        if (!launch_ring<64>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st, err))
+            *err = launch_mma<64, 64>(p, qr, sharp, kbuf, vbuf, kinv, valid, rd, st);
+    } else {
+        return false;
+    }
     return true;
 }
 

@@ -84,14 +84,19 @@ def _(kbuf, out_bf16, bits, group):
 def _ep_setup(ctx, inputs, output):
     kbuf, out_bf16, bits, group = inputs
     ctx.in_bf16 = kbuf.dtype == torch.bfloat16
-    # d nsq / d kbuf = 2 * (the value the norm was taken of): the quantised keys when bits != 0
-    ctx.save_for_backward(output[0] if bits else kbuf, output[1], output[2])
+    ctx.bits, ctx.group = int(bits), int(group)
+    # d nsq / d kbuf = 2 * (the value the norm was taken of): the quantised keys BEFORE the cast to the output dtype when
+    # bits != 0 [memlm_sh.py:232-234, 471-472].  The emitted keys may be bf16-rounded, so the backward requantises the
+    # saved input in its own precision (one more pass of the quantiser kernel) instead of saving the output.
+    ctx.save_for_backward(kbuf, output[1], output[2])
 
 
 def _ep_backward(ctx, dy, dkinv, dvalid):
     # kinv = nsq^(-1/2) where valid: d nsq = -kinv^3 / 2 * dkinv, d kbuf = 2 kq * d nsq; the cast and the quantiser
     # pass dy straight through.  Elementwise torch ops on the device: not a kernel of this library yet.
     kq, kinv, valid = ctx.saved_tensors
+    if ctx.bits:
+        kq = _fq_op(kq, ctx.bits, ctx.group)
     in_dtype = torch.bfloat16 if ctx.in_bf16 else torch.float32
     g = dy.to(in_dtype)
     if dkinv is not None:

@@ -129,6 +129,27 @@ def test_gradients():
     assert (k1.grad.cpu().double() - k2.grad).abs().max() < 1e-5 * k2.grad.abs().max()
 
 
+def test_gradients_quantised_bf16_handover():
+    """qbits = 3 with a bf16 hand-over: the kinv gradient goes through the float32 QUANTISED keys, as in the reference
+    (memlm_sh.py:232-234: nsq of the quantised float32 kbuf, then the cast, :471-472), not through their bf16-rounded
+    copies; the quantiser itself is straight-through.  Check: float64 autograd of the same formula."""
+    S = _S()
+    g = torch.Generator().manual_seed(5)
+    kb = torch.randn(2, 3, 4, 6, 32, generator=g)
+    kb[1, 2] = 0
+    wk, wi = torch.randn(2, 3, 4, 6, 32, generator=g), torch.randn(2, 3, 4, 6, generator=g)
+    wk = wk.to(torch.bfloat16).float()          # the gradient of a bf16 tensor arrives in bf16 (here and in the reference)
+    k1 = kb.cuda().requires_grad_()
+    kq, vq, kinv, valid = S.writer_epilogue(k1, k1.detach(), torch.bfloat16, qbits=3, qgroup=16)
+    assert kq.dtype == torch.bfloat16
+    ((kq.float() * wk.cuda()).sum() + (kinv * wi.cuda()).sum()).backward()
+    k2 = kb.double().requires_grad_()
+    q2 = k2 + (_fq_torch(kb, 3, 16).double() - k2).detach()              # forward value quantised, gradient identity
+    nsq = q2.pow(2).sum(-1)
+    ((q2 * wk.double()).sum() + (torch.rsqrt(nsq.clamp_min(1e-12)) * wi.double()).sum()).backward()
+    assert (k1.grad.cpu().double() - k2.grad).abs().max() < 1e-5 * k2.grad.abs().max()
+
+
 def test_contract():
     S = _S()
     x = torch.randn(4, 48)

@@ -38,8 +38,8 @@ def _case(B, T, H, NQ, N, DK, DV, G, nvalid, seed):
     sharp = torch.nn.functional.softplus(torch.randn(B, T, H, NQ, generator=g)) + 1
     kbuf = torch.randn(B, NB, H, N, DK, generator=g)
     vbuf = 0.5 * torch.randn(B, NB, H, N, DV, generator=g)
-    # rows fill in index order as the scan proceeds; snapshot 0 is empty
-    occ = torch.minimum(torch.arange(NB) * 2, torch.tensor(nvalid)).view(1, NB, 1, 1)
+    # rows fill in index order as the scan proceeds: snapshot 0 is empty, the last one holds nvalid rows
+    occ = torch.div(torch.arange(NB) * nvalid + max(NB - 2, 0), max(NB - 1, 1), rounding_mode="floor").clamp(max=nvalid).view(1, NB, 1, 1)
     live = torch.arange(N).view(1, 1, 1, N) < occ
     kbuf = kbuf * live.unsqueeze(-1)
     vbuf = vbuf * live.unsqueeze(-1)
@@ -86,8 +86,14 @@ def test_read_after_scan_and_epilogue_bf16():
 
 
 @pytest.mark.parametrize("shape", [(2, 64, 3, 2, 192, 128, 128, 8, 192), (2, 40, 2, 2, 192, 128, 128, 8, 13),
-                                   (1, 50, 2, 4, 96, 64, 64, 16, 96), (1, 21, 2, 1, 40, 128, 128, 8, 37)],
-                         ids=["sh25_dense", "sh25_sparse", "d64_M64_T%G", "M8_n40"])
+                                   (1, 50, 2, 4, 96, 64, 64, 16, 96), (1, 21, 2, 1, 40, 128, 128, 8, 37),
+                                   # the persistent ring kernel (G * NQ <= 16, N % 16 == 0): each box height, T % G != 0,
+                                   # dk = 64, a short memory, M = 16 from NQ = 1, and more snapshots than SMs
+                                   (2, 44, 2, 2, 192, 128, 128, 8, 100), (1, 64, 2, 2, 96, 64, 64, 8, 70),
+                                   (1, 32, 2, 1, 192, 128, 128, 16, 50), (1, 30, 3, 2, 48, 128, 128, 4, 40),
+                                   (4, 256, 6, 2, 192, 128, 128, 8, 150)],
+                         ids=["sh25_dense", "sh25_sparse", "d64_M64_T%G", "M8_n40", "ring_box128_T%G", "ring_d64_n96",
+                              "ring_box64_nq1", "ring_n48_m8", "ring_768_snapshots"])
 def test_read_tensor_core_path_bf16(shape):
     """bf16 queries and snapshots with dk = dv in {64, 128}: the read runs on the tensor cores (Q K^T and P V as
     m16n8k16 MMAs with float32 accumulation, P in bf16 as the reference's att.to(bf16)).  Against the float64 oracle on
