@@ -272,41 +272,48 @@ __global__ void __launch_bounds__(RM_THREADS, 2) read_fwd_mma_kernel(
 
 
 // ======================================================================================================
-// The same read as a PERSISTENT kernel, one CTA per SM walking its share of the snapshots through a two-stage ring:
-// while the tensor cores work on snapshot i, the rows of snapshot i + 1 are already in flight and the kinv / valid
-// vectors of snapshot i + 2 behind them.  The kernel above pays, per snapshot, a serial chain "which rows count ->
-// rows land -> Q K^T -> softmax -> P V" (about 20 us with two CTAs per SM: 17 % of DRAM peak); here only the math is
-// left on that chain.
+// The same read as a PERSISTENT, warp-specialised kernel: one CTA per SM walks its share of the snapshots; one warp
+// only issues copies and runs ahead of eight math warps, coupled to them by mbarriers alone ("tile landed" one way,
+// "tile free" the other).  The kernel above pays, per snapshot, a serial chain "which rows count -> rows land ->
+// Q K^T -> softmax -> P V" (about 20 us with two CTAs per SM: 17 % of DRAM peak); here only the math is on that chain
+// and the copies of the next snapshots are in flight all the time: the key tile of snapshot i + 2 is requested as soon
+// as Q K^T of snapshot i is done, its value tile when P V of snapshot i is done (a memory-bound kernel needs
+// bandwidth x latency, about 90 KB per SM, in flight; one snapshot ahead was measured at 0.41 of the HBM peak).
 //   * key / value tiles come in by TILED bulk tensor copies (a 3-D tensor map over (snapshot, row, column), box
 //     64 columns x 64 / 128 / 192 rows, 128-byte swizzle): 2 copies per tensor and snapshot instead of one per row,
 //     no row padding, and ldmatrix reads the swizzled tile without bank conflicts (16-byte chunk c of row r sits at
 //     chunk c ^ (r & 7));
-//   * the box height is the smallest that covers the highest valid row, read from the prefetched valid vector;
-//   * the 16 query rows and the kinv / valid vectors by plain bulk copies; sharp by ordinary loads one snapshot ahead.
+//   * the box height is the smallest that covers the highest valid row, read from the valid vector, which comes in
+//     through a four-deep ring of small bulk copies together with kinv;
+//   * the 16 query rows by plain bulk copies; sharp by ordinary loads one snapshot ahead.
 // Needs G * NQ <= 16, N a multiple of 16 and dk = dv in {64, 128}; other shapes take the kernel above.
-constexpr int RR_THREADS = 256, RR_WARPS = 8;          // two warps per scheduler: the per-snapshot chain is latency-bound
-constexpr int RR_TPW = RM_MAXN / 8 / RR_WARPS;         // 8-row tiles per warp
+constexpr int RR_WARPS = 8;                            // math warps; warp RR_WARPS issues the copies
+constexpr int RR_THREADS = (RR_WARPS + 1) * 32;
+constexpr int RR_TPW = RM_MAXN / 8 / RR_WARPS;         // 8-row tiles per math warp
 constexpr int RR_ROWS = RM_MAXN;                       // rows per sub-tile slot in shared memory
 constexpr int RR_SUB = RR_ROWS * 128;                  // bytes of one 64-column sub-tile slot (a multiple of 1024)
+constexpr int RR_META = 4;                             // kinv / valid vectors in flight
 struct ReadMaps { CUtensorMap k[3], v[3]; };           // box heights min(N, 64), min(N, 128), N
 
-struct ReadRingSmem { int stage, stage_bytes, q, q_bytes, meta, kv, red, scale, sharp, nv, bar, total; int ldp; };
+struct ReadRingSmem { int stage, stage_bytes, q, q_bytes, pbuf, meta, kv, red, scale, sharp, nv, bar, total; int ldq, ldp; };
 __host__ __device__ inline ReadRingSmem read_ring_layout(int DK) {
     ReadRingSmem L;
     const int nsub = DK / 64;
-    L.ldp = RM_MAXN + 8;
+    L.ldq = DK + 8; L.ldp = RM_MAXN + 8;               // padded rows: conflict-free ldmatrix
     L.stage = 0;
     L.stage_bytes = 2 * nsub * RR_SUB;                 // keys then values
     L.q = 2 * L.stage_bytes;
-    L.q_bytes = 16 * L.ldp * 2;                        // 16 query rows; reused for P once the fragments are in registers
-    L.meta = L.q + 2 * L.q_bytes;                      // 2 x (kinv [N] f32 | valid [N] u8), 1 KB each
-    L.kv = L.meta + 2 * 1024;
-    L.red = L.kv + RM_MAXN * 4;
+    L.q_bytes = 16 * L.ldq * 2;                        // 16 query rows per stage
+    L.pbuf = L.q + 2 * L.q_bytes;                      // P = exp(S - max) as bf16, 16 x N
+    L.meta = L.pbuf + 16 * L.ldp * 2;                  // RR_META x (kinv [N] f32 | valid [N] u8), 1 KB each
+    L.kv = L.meta + RR_META * 1024;                    // [2 stages][N] kinv of a valid row, -1 for the others
+    L.red = L.kv + 2 * RM_MAXN * 4;
     L.scale = L.red + 2 * RR_WARPS * 16 * 4;
-    L.sharp = L.scale + 16 * 4;
-    L.nv = L.sharp + 16 * 4;                           // [0..1] highest valid row + 1 per stage, [2] failure flag
-    L.bar = L.nv + 16;                                 // meta[2], queries+keys[2], values[2]
-    L.total = L.bar + 6 * 8;
+    L.sharp = L.scale + 16 * 4;                        // [2 stages][16]
+    L.nv = L.sharp + 2 * 16 * 4;                       // [0..1] highest valid row + 1 per stage, [2] failure flag,
+                                                       // [4..5] snapshot index per stage (-1: no more)
+    L.bar = L.nv + 32;                                 // meta[RR_META], fullL[2], fullV[2], emptyK[2], emptyV[2]
+    L.total = L.bar + (RR_META + 8) * 8;
     return L;
 }
 
@@ -315,6 +322,30 @@ __device__ __forceinline__ void tensor_g2s_3d(void* dst, const CUtensorMap* map,
                  ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
                  : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {       // bytes to come; no arrival
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// barrier among the math warps only (the copy-issuing warp never joins it)
+__device__ __forceinline__ void math_sync() { asm volatile("bar.sync 1, %0;" ::"n"(RR_WARPS * 32) : "memory"); }
+// the same with an AND over the math threads' flags: every thread gets the same answer, so a wait that gave up in one
+// thread ends the loop in all of them at the same place (a thread must never be left alone at a barrier)
+__device__ __forceinline__ bool math_sync_and(bool ok) {
+    int r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.s32 q, %1, 0;\n"
+        "bar.red.and.pred p, 1, %2, q;\n"
+        "selp.s32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r)
+        : "r"((int)ok), "n"(RR_WARPS * 32)
+        : "memory");
+    return r != 0;
+}
 
 template <int DK>
 __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
@@ -322,26 +353,29 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
     const float* __restrict__ sharp, const float* __restrict__ kinv, const uint8_t* __restrict__ valid,
     bf16* __restrict__ rd, const int nitems) {
     constexpr int DV = DK, NSUB = DK / 64;
+    static_assert(DV / 8 % RR_WARPS == 0, "each math warp owns whole 8-column tiles of the values");
     extern __shared__ __align__(128) unsigned char rsm[];
     // the swizzled tiles want a 1024-byte boundary (the launch adds 1 KB of slack for this)
     unsigned char* const rsmb = rsm + ((1024u - (smem_u32(rsm) & 1023u)) & 1023u);
     const int N = p.N, T = p.T, H = p.H, NQ = p.NQ, G = p.G;
     const int NB = (T + G - 1) / G;
     const ReadRingSmem L = read_ring_layout(DK);
-    float* s_kv = reinterpret_cast<float*>(rsmb + L.kv);
+    float* s_kvst = reinterpret_cast<float*>(rsmb + L.kv);
     float* s_red = reinterpret_cast<float*>(rsmb + L.red);
     float* s_scale = reinterpret_cast<float*>(rsmb + L.scale);
-    float* s_sharp = reinterpret_cast<float*>(rsmb + L.sharp);
+    float* s_sharpst = reinterpret_cast<float*>(rsmb + L.sharp);
     volatile int* s_nv = reinterpret_cast<int*>(rsmb + L.nv);
     uint64_t* barM = reinterpret_cast<uint64_t*>(rsmb + L.bar);
-    uint64_t* barL = barM + 2;
-    uint64_t* barV = barM + 4;
+    uint64_t* fullL = barM + RR_META;
+    uint64_t* fullV = fullL + 2;
+    uint64_t* emptyK = fullV + 2;
+    uint64_t* emptyV = emptyK + 2;
+    bf16* Pb = reinterpret_cast<bf16*>(rsmb + L.pbuf);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int first = blockIdx.x, stride = gridDim.x;
     const int h64 = min(N, 64), h128 = min(N, 128);
+    const int nmine = first < nitems ? (nitems - first + stride - 1) / stride : 0;   // snapshots of this CTA
 
-    auto meta_k = [&](int slot) { return reinterpret_cast<float*>(rsmb + L.meta + slot * 1024); };
-    auto meta_v = [&](int slot) { return rsmb + L.meta + slot * 1024 + RM_MAXN * 4; };
     auto q_stage = [&](int s) { return reinterpret_cast<bf16*>(rsmb + L.q + s * L.q_bytes); };
     // queries of snapshot `it`: (b, block, h) -> token t0 + m / NQ, query m % NQ
     auto q_index = [&](int it, int m) {
@@ -349,38 +383,10 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
         return (((size_t)bb * T + nb * G + m / NQ) * H + hh) * NQ + m % NQ;
     };
     auto q_count = [&](int it) { const int nb = (it / H) % NB; return min(G, T - nb * G) * NQ; };
-    // warp 0 only --------------------------------------------------------------------------------------------------
-    auto issue_meta = [&](int it, int slot) {
-        if (lane == 0) {
-            mbar_arrive_expect_tx(&barM[slot], (unsigned)(N * 5));
-            bulk_g2s(meta_k(slot), kinv + (size_t)it * N, N * 4, &barM[slot]);
-            bulk_g2s(meta_v(slot), valid + (size_t)it * N, N, &barM[slot]);
-        }
-    };
-    auto scan_nv = [&](int slot) {
-        const unsigned char* mv = meta_v(slot);
-        int hi = 0;
-        for (int n = lane; n < N; n += 32) if (mv[n] != 0) hi = n + 1;
-        return (int)__reduce_max_sync(FULL, (unsigned)hi);
-    };
-    auto issue_loads = [&](int it, int s, int nv) {
-        const int sel = nv <= h64 ? 0 : (nv <= h128 ? 1 : 2);
-        const int rows = sel == 0 ? h64 : (sel == 1 ? h128 : N);
-        const int M = q_count(it);
-        unsigned char* st = rsmb + L.stage + s * L.stage_bytes;
-        fence_proxy_async_smem();                                  // the stage was last written (P) and read through the generic proxy
-        if (lane == 0) {
-            mbar_arrive_expect_tx(&barL[s], (unsigned)(M * DK * 2 + rows * DK * 2));
-            mbar_arrive_expect_tx(&barV[s], (unsigned)(rows * DV * 2));
-        }
-        __syncwarp();
-        if (lane < NSUB) tensor_g2s_3d(st + lane * RR_SUB, &maps.k[sel], lane * 64, 0, it, &barL[s]);
-        else if (lane < 2 * NSUB) tensor_g2s_3d(st + lane * RR_SUB, &maps.v[sel], (lane - NSUB) * 64, 0, it, &barV[s]);
-        if (lane < M) bulk_g2s(q_stage(s) + (size_t)lane * L.ldp, qr + q_index(it, lane) * DK, DK * 2, &barL[s]);
-    };
 
     if (tid == 0) {
-        for (int i = 0; i < 6; i++) mbar_init(&barM[i], 1);
+        for (int i = 0; i < RR_META + 4; i++) mbar_init(&barM[i], 1);      // meta, fullL, fullV: one arrive (+ bytes)
+        for (int i = 0; i < 4; i++) mbar_init(&emptyK[i], RR_WARPS);       // emptyK, emptyV: one arrive per math warp
         mbar_fence_init();
         s_nv[0] = s_nv[1] = s_nv[2] = 0;
     }
@@ -388,69 +394,104 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
         reinterpret_cast<uint4*>(rsmb + L.q)[i] = make_uint4(0u, 0u, 0u, 0u);
     fence_proxy_async_smem();
     __syncthreads();
-    float shn = 0.f;                                                       // sharp of the NEXT snapshot's query tid (< 16)
-    if (first < nitems) {
-        if (warp == 0) {
-            issue_meta(first, 0);
-            if (first + stride < nitems) issue_meta(first + stride, 1);
-            const bool ok = mbar_wait_bounded(&barM[0], 0u);
-            const int nv0 = ok ? scan_nv(0) : 0;
-            if (lane == 0) { s_nv[0] = nv0; if (!ok) s_nv[2] = 1; }
-            if (nv0 > RM_SPARSE_ROWS) issue_loads(first, 0, nv0);
-            if (nv0 > RM_SPARSE_ROWS && tid < 16 && tid < q_count(first)) shn = sharp[q_index(first, tid)];
-        }
-    }
-    __syncthreads();
-    unsigned phL = 0u, phV = 0u;                                 // bit s: parity of the next wait on stage s
-    bool failed = false;
-    const int r0 = lane >> 2, cq = (lane & 3) * 2;             // this thread's rows r0, r0 + 8 and column pair in a C tile
-    int i = 0;
-    for (int it = first; it < nitems; it += stride, i++) {
-        const int s = i & 1;
-        if (s_nv[2] != 0) break;                                           // a bounded wait gave up (uniform: read after a barrier)
-        const int nv = s_nv[s];
-        const int M = q_count(it);
-        const int NPv = (nv + 15) & ~15;
-        // (a) this snapshot's kinv / valid -> kinv or -1; sharp of its queries (nothing to do for a snapshot that is left
-        //     to the CUDA-core kernel: warp 0 has already scanned its valid vector)
-        if (nv > RM_SPARSE_ROWS) {
-            const float* mk = meta_k(s);
-            const unsigned char* mv = meta_v(s);
-            for (int n = tid; n < RM_MAXN; n += RR_THREADS) s_kv[n] = (n < N && mv[n] != 0) ? mk[n] : -1.f;
-            if (tid < 16) s_sharp[tid] = tid < M ? shn : 0.f;
-            __syncthreads();
-        }
-        // (b) warp 0: rows of the next snapshot in flight, kinv / valid of the one after
-        if (warp == 0) {
-            const int itn = it + stride;
-            if (itn < nitems) {
-                const bool ok = mbar_wait_bounded(&barM[s ^ 1], (unsigned)(((i + 1) >> 1) & 1));
-                const int nvn = ok ? scan_nv(s ^ 1) : 0;
-                if (lane == 0) { s_nv[s ^ 1] = nvn; if (!ok) s_nv[2] = 1; }
-                if (nvn > RM_SPARSE_ROWS) issue_loads(itn, s ^ 1, nvn);
-                shn = (nvn > RM_SPARSE_ROWS && tid < 16 && tid < q_count(itn)) ? sharp[q_index(itn, tid)] : 0.f;
+
+    if (warp == RR_WARPS) {
+        // ================= the copy-issuing warp =================
+        auto issue_meta = [&](int k) {                                     // kinv / valid of this CTA's k-th snapshot
+            if (lane == 0 && k < nmine) {
+                const int it = first + k * stride, slot = k % RR_META;
+                mbar_arrive_expect_tx(&barM[slot], (unsigned)(N * 5));
+                bulk_g2s(rsmb + L.meta + slot * 1024, kinv + (size_t)it * N, N * 4, &barM[slot]);
+                bulk_g2s(rsmb + L.meta + slot * 1024 + RM_MAXN * 4, valid + (size_t)it * N, N, &barM[slot]);
             }
-            if (it + 2 * stride < nitems) issue_meta(it + 2 * stride, s);
+        };
+        for (int k = 0; k < RR_META; k++) issue_meta(k);
+        int kd = 0;                                                        // snapshots handed to the math warps so far
+        bool alive = true;
+        for (int k = 0; k < nmine; k++) {
+            const int it = first + k * stride, slot = k % RR_META;
+            if (!__all_sync(FULL, mbar_wait_bounded(&barM[slot], (unsigned)((k / RR_META) & 1)))) { alive = false; break; }   // warp-uniform
+            // kinv or -1 per row and the highest valid row, from the landed vectors; then the slot is free again
+            const float* mk = reinterpret_cast<const float*>(rsmb + L.meta + slot * 1024);
+            const unsigned char* mv = rsmb + L.meta + slot * 1024 + RM_MAXN * 4;
+            float kvr[RM_MAXN / 32];
+            int hi = 0;
+#pragma unroll
+            for (int j = 0; j < RM_MAXN / 32; j++) {
+                const int n = lane + 32 * j;
+                const bool v = n < N && mv[n] != 0;
+                kvr[j] = v ? mk[n] : -1.f;
+                if (v) hi = n + 1;
+            }
+            const int nv = (int)__reduce_max_sync(FULL, (unsigned)hi);
+            fence_proxy_async_smem();
+            __syncwarp();
+            issue_meta(k + RR_META);
+            if (nv <= RM_SPARSE_ROWS) continue;                            // left to the CUDA-core kernel: the math warps never see it
+            const int M = q_count(it);
+            const float sh = (lane < 16 && lane < M) ? sharp[q_index(it, lane)] : 0.f;   // needed only after the copies are out
+            const int s = kd & 1;
+            const unsigned epar = (unsigned)(((kd >> 1) & 1) ^ 1);         // the phase that snapshot kd - 2 completed
+            // the key tile, the queries and the per-row vectors of stage s: free once Q K^T of snapshot kd - 2 is done
+            if (kd >= 2 && !__all_sync(FULL, mbar_wait_bounded(&emptyK[s], epar))) { alive = false; break; }
+            const int sel = nv <= h64 ? 0 : (nv <= h128 ? 1 : 2);
+            const int rows = sel == 0 ? h64 : (sel == 1 ? h128 : N);
+            unsigned char* st = rsmb + L.stage + s * L.stage_bytes;
+            if (lane == 0) mbar_expect_tx(&fullL[s], (unsigned)(M * DK * 2 + rows * DK * 2));
+            __syncwarp();
+            if (lane < NSUB) tensor_g2s_3d(st + lane * RR_SUB, &maps.k[sel], lane * 64, 0, it, &fullL[s]);
+            if (lane < M) bulk_g2s(q_stage(s) + (size_t)lane * L.ldq, qr + q_index(it, lane) * DK, DK * 2, &fullL[s]);
+#pragma unroll
+            for (int j = 0; j < RM_MAXN / 32; j++) s_kvst[s * RM_MAXN + lane + 32 * j] = kvr[j];
+            if (lane < 16) s_sharpst[s * 16 + lane] = sh;
+            if (lane == 0) { s_nv[s] = nv; s_nv[4 + s] = it; }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&fullL[s]);                         // the vectors are written; the phase ends when the bytes are in
+            // the value tile: free once P V of snapshot kd - 2 is done
+            if (kd >= 2 && !__all_sync(FULL, mbar_wait_bounded(&emptyV[s], epar))) { alive = false; break; }
+            if (lane == 0) mbar_arrive_expect_tx(&fullV[s], (unsigned)(rows * DV * 2));
+            __syncwarp();
+            if (lane < NSUB) tensor_g2s_3d(st + (NSUB + lane) * RR_SUB, &maps.v[sel], lane * 64, 0, it, &fullV[s]);
+            kd++;
         }
-        // (c) the read itself; snapshots with few rows are left to the CUDA-core kernel
-        if (nv > RM_SPARSE_ROWS) {
+        if (alive) {                                                       // tell the math warps that nothing follows
+            const int s = kd & 1;
+            if (kd >= 2 && !__all_sync(FULL, mbar_wait_bounded(&emptyK[s], (unsigned)(((kd >> 1) & 1) ^ 1)))) alive = false;
+            if (alive) {
+                if (lane == 0) s_nv[4 + s] = -1;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&fullL[s]);
+            }
+        }
+        if (!alive) s_nv[2] = 1;
+    } else {
+        // ================= the math warps =================
+        const int r0 = lane >> 2, cq = (lane & 3) * 2;             // this thread's rows r0, r0 + 8 and column pair in a C tile
+        bool failed = false;
+        for (int kd = 0;; kd++) {                                  // the snapshots the copy-issuing warp hands over, in order
+            const int s = kd & 1;
+            const unsigned par = (unsigned)((kd >> 1) & 1);
+            if (!math_sync_and(mbar_wait_bounded(&fullL[s], par))) { failed = true; break; }
+            const int it = s_nv[4 + s];
+            if (it < 0) break;
+            const int nv = s_nv[s];
+            const int M = q_count(it);
+            const int NPv = (nv + 15) & ~15;
             const unsigned char* Kst = rsmb + L.stage + s * L.stage_bytes;
             const unsigned char* Vst = Kst + NSUB * RR_SUB;
-            bf16* PQ = q_stage(s);
-            bool ok = mbar_wait_bounded(&barL[s], (phL >> s) & 1u);
-            phL ^= 1u << s;
-            if (!__syncthreads_and(ok ? 1 : 0)) { failed = true; break; }
-            for (int mm = warp; mm < 16; mm += RR_WARPS) {         // |q| in float32, 4 rows per warp
+            const bf16* Qs = q_stage(s);
+            const float* s_kv = s_kvst + s * RM_MAXN;
+            for (int mm = warp; mm < 16; mm += RR_WARPS) {         // |q| in float32, 2 rows per warp
                 float qq = 0.f;
-                for (int d = lane; d < DK; d += 32) { const float x = __bfloat162float(PQ[(size_t)mm * L.ldp + d]); qq = fmaf(x, x, qq); }
+                for (int d = lane; d < DK; d += 32) { const float x = __bfloat162float(Qs[(size_t)mm * L.ldq + d]); qq = fmaf(x, x, qq); }
                 qq = warp_sum(qq);
-                if (lane == 0) s_scale[mm] = mm < M ? s_sharp[mm] / fmaxf(sqrtf(qq), 1e-6f) : 0.f;
+                if (lane == 0) s_scale[mm] = mm < M ? s_sharpst[s * 16 + mm] / fmaxf(sqrtf(qq), 1e-6f) : 0.f;
             }
             unsigned qa[DK / 16][4];                               // A fragments of the query tile
 #pragma unroll
             for (int ks = 0; ks < DK / 16; ks++)
-                ldsm_x4(qa[ks], PQ + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldp + ks * 16 + (lane >> 4) * 8);
-            __syncthreads();                                       // scales written, every warp holds its Q fragments: PQ is free for P
+                ldsm_x4(qa[ks], Qs + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldq + ks * 16 + (lane >> 4) * 8);
+            math_sync();                                           // scales written
             // ---- S = Q K^T over this warp's row tiles, scaled and masked ----
             float sc[RR_TPW][4];
             float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -478,14 +519,16 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
                     mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&emptyK[s]);                // this warp is done with the key tile, the queries, kinv
             mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(FULL, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(FULL, mx1, 2));
             if ((lane & 3) == 0) { s_red[warp * 16 + r0] = mx0; s_red[warp * 16 + r0 + 8] = mx1; }
-            __syncthreads();
+            math_sync();
             mx0 = s_red[r0]; mx1 = s_red[r0 + 8];
 #pragma unroll
             for (int w = 1; w < RR_WARPS; w++) { mx0 = fmaxf(mx0, s_red[w * 16 + r0]); mx1 = fmaxf(mx1, s_red[w * 16 + r0 + 8]); }
-            // ---- P = exp(S - max) as bf16 into the query tile's place ----
+            // ---- P = exp(S - max) as bf16 ----
             float su0 = 0.f, su1 = 0.f;
 #pragma unroll
             for (int j = 0; j < RR_TPW; j++) {
@@ -494,25 +537,24 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
                     const float e0 = __expf(sc[j][0] - mx0), e1 = __expf(sc[j][1] - mx0);   // exp(-inf) = 0 for masked rows
                     const float e2 = __expf(sc[j][2] - mx1), e3 = __expf(sc[j][3] - mx1);
                     su0 += e0 + e1; su1 += e2 + e3;
-                    *reinterpret_cast<__nv_bfloat162*>(PQ + (size_t)r0 * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e0, e1);
-                    *reinterpret_cast<__nv_bfloat162*>(PQ + (size_t)(r0 + 8) * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e2, e3);
+                    *reinterpret_cast<__nv_bfloat162*>(Pb + (size_t)r0 * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e0, e1);
+                    *reinterpret_cast<__nv_bfloat162*>(Pb + (size_t)(r0 + 8) * L.ldp + nt * 8 + cq) = __floats2bfloat162_rn(e2, e3);
                 }
             }
             su0 += __shfl_xor_sync(FULL, su0, 1); su0 += __shfl_xor_sync(FULL, su0, 2);
             su1 += __shfl_xor_sync(FULL, su1, 1); su1 += __shfl_xor_sync(FULL, su1, 2);
             float* s_sum = s_red + RR_WARPS * 16;
             if ((lane & 3) == 0) { s_sum[warp * 16 + r0] = su0; s_sum[warp * 16 + r0 + 8] = su1; }
-            ok = mbar_wait_bounded(&barV[s], (phV >> s) & 1u);
-            phV ^= 1u << s;
-            if (!__syncthreads_and(ok ? 1 : 0)) { failed = true; break; }
-            // ---- O = P V: this warp's quarter of the value columns ----
+            if (!math_sync_and(mbar_wait_bounded(&fullV[s], par))) { failed = true; break; }   // also: P and the sums are written
+            // ---- O = P V: this warp's share of the value columns ----
             constexpr int DT = DV / 8 / RR_WARPS;                  // 8-column tiles per warp
             float o[DT][4];
 #pragma unroll
             for (int j = 0; j < DT; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+#pragma unroll 2
             for (int ks = 0; ks < NPv / 16; ks++) {
                 unsigned pa[4];
-                ldsm_x4(pa, PQ + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldp + ks * 16 + (lane >> 4) * 8);
+                ldsm_x4(pa, Pb + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * L.ldp + ks * 16 + (lane >> 4) * 8);
                 const int row = ks * 16 + (lane & 15);
 #pragma unroll
                 for (int j = 0; j < DT; j++) {
@@ -522,22 +564,25 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_fwd_ring_kernel(
                     mma_bf16(o[j], pa, b0, b1);
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&emptyV[s]);                // this warp is done with the value tile
             float t0s = 0.f, t1s = 0.f;
 #pragma unroll
             for (int w = 0; w < RR_WARPS; w++) { t0s += s_sum[w * 16 + r0]; t1s += s_sum[w * 16 + r0 + 8]; }
             const float inv0 = 1.f / t0s, inv1 = 1.f / t1s;
+            const size_t qi0 = q_index(it, r0), qi1 = q_index(it, r0 + 8);
 #pragma unroll
             for (int j = 0; j < DT; j++) {
                 const int d = (warp * DT + j) * 8 + cq;
-                if (r0 < M)
-                    *reinterpret_cast<__nv_bfloat162*>(rd + q_index(it, r0) * DV + d) = __floats2bfloat162_rn(o[j][0] * inv0, o[j][1] * inv0);
-                if (r0 + 8 < M)
-                    *reinterpret_cast<__nv_bfloat162*>(rd + q_index(it, r0 + 8) * DV + d) = __floats2bfloat162_rn(o[j][2] * inv1, o[j][3] * inv1);
+                if (r0 < M) *reinterpret_cast<__nv_bfloat162*>(rd + qi0 * DV + d) = __floats2bfloat162_rn(o[j][0] * inv0, o[j][1] * inv0);
+                if (r0 + 8 < M) *reinterpret_cast<__nv_bfloat162*>(rd + qi1 * DV + d) = __floats2bfloat162_rn(o[j][2] * inv1, o[j][3] * inv1);
             }
+            // no barrier here: the next snapshot's first barrier comes before anything of this one is overwritten
         }
-        __syncthreads();                                           // this stage, its query tile and the exchange arrays are free
+        if (failed) s_nv[2] = 1;
     }
-    if (failed || s_nv[2] != 0) {                                  // a bounded wait gave up: report, and give the copies still
+    __syncthreads();
+    if (s_nv[2] != 0) {                                            // a bounded wait gave up: report, and give the copies still
         if (tid == 0) atomicExch(&g_read_status, 1);               // in flight into this CTA's shared memory time to land
         for (int k = 0; k < 1000; k++) __nanosleep(1000);
     }
