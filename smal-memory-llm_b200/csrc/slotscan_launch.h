@@ -63,6 +63,9 @@ constexpr int RM_SPARSE_ROWS = 32;
 // tensor-core forward read (slotscan_read_mma.cu): returns false when the shape / dtypes are not its own
 bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
                       const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err);
+bool read_bwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
+                      const float* kinv, const uint8_t* valid, const void* drd, void* dqr, float* dsharp, void* dkbuf,
+                      void* dvbuf, float* dkinv, cudaStream_t st, cudaError_t* err);
 int read_mma_status();
 int gather_status_f32();
 int gather_status_bf16();

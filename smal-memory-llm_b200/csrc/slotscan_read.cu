@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
     const slotscan_read_params p, const Tq* __restrict__ qr, const float* __restrict__ sharp, const Tsn* __restrict__ kbuf,
     const Tsn* __restrict__ vbuf, const float* __restrict__ kinv, const uint8_t* __restrict__ valid,
     const Tq* __restrict__ drd, Tq* __restrict__ dqr, float* __restrict__ dsharp, Tsn* __restrict__ dkbuf,
-    Tsn* __restrict__ dvbuf, float* __restrict__ dkinv) {
+    Tsn* __restrict__ dvbuf, float* __restrict__ dkinv, const int sparse_only) {
     extern __shared__ __align__(16) float rsm[];
     const int N = p.N, T = p.T, H = p.H, NQ = p.NQ, DK = p.DK, DV = p.DV, G = p.G;
     const int NB = (T + G - 1) / G, N4 = (N + 3) & ~3;
@@ -265,13 +265,13 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
     float* s_qinv = rsm + L.qinv;
     float* s_att = rsm + L.att;
     float* s_cf = rsm + L.cf;
-    __shared__ int s_nv;
+    __shared__ int s_nv, s_hvb;
     const int so = blockIdx.x;
     const int h = so % H, nb = (so / H) % NB, b = so / (H * NB);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (warp == 0) {
-        int nv = 0;
+        int nv = 0, hv = 0;
         for (int base = 0; base < N; base += 32) {
             const int n = base + lane;
             const bool v = n < N && valid[(size_t)so * N + n] != 0;
@@ -282,15 +282,18 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
                 s_ki[pos] = kinv[(size_t)so * N + n];
             }
             nv += __popc(bal);
+            if (bal) hv = base + 32 - __clz(bal);              // highest valid row + 1
         }
-        if (lane == 0) s_nv = nv;
+        if (lane == 0) { s_nv = nv; s_hvb = hv; }
     }
+    __syncthreads();
+    const int nv = s_nv;
+    if (sparse_only && s_hvb > RM_SPARSE_ROWS) return;            // the tensor-core kernel takes this snapshot (uniform per CTA)
     // zero the whole block of snapshot gradients first; the valid rows are overwritten after the barrier below
     zero_fill(dkbuf + (size_t)so * N * DK, (size_t)N * DK, tid);
     zero_fill(dvbuf + (size_t)so * N * DV, (size_t)N * DV, tid);
     for (int i = tid; i < N; i += RD_THREADS) dkinv[(size_t)so * N + i] = 0.f;
     __syncthreads();
-    const int nv = s_nv;
     const int t0 = nb * G, tc = min(G, T - t0), M = tc * NQ;
     float* sc = rsm + L.sc + (size_t)warp * N4 * RD_QPW;
     float* sd = rsm + L.sd + (size_t)warp * N4 * RD_QPW;
@@ -449,7 +452,7 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
 template <typename Tq, typename Tsn>
 static cudaError_t launch_read_bwd(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf,
                                    const void* vbuf, const float* kinv, const uint8_t* valid, const void* drd, void* dqr,
-                                   float* dsharp, void* dkbuf, void* dvbuf, float* dkinv, cudaStream_t st) {
+                                   float* dsharp, void* dkbuf, void* dvbuf, float* dkinv, int sparse_only, cudaStream_t st) {
     const int NB = (p.T + p.G - 1) / p.G;
     const size_t sm = sizeof(float) * (size_t)read_bwd_layout(p.N, p.G * p.NQ).total;
     auto kern = read_bwd_kernel<Tq, Tsn>;
@@ -458,7 +461,7 @@ static cudaError_t launch_read_bwd(const slotscan_read_params& p, const void* qr
         if (e != cudaSuccess) return e;
     }
     kern<<<p.B * NB * p.H, RD_THREADS, sm, st>>>(p, (const Tq*)qr, sharp, (const Tsn*)kbuf, (const Tsn*)vbuf, kinv, valid,
-                                                  (const Tq*)drd, (Tq*)dqr, dsharp, (Tsn*)dkbuf, (Tsn*)dvbuf, dkinv);
+                                                  (const Tq*)drd, (Tq*)dqr, dsharp, (Tsn*)dkbuf, (Tsn*)dvbuf, dkinv, sparse_only);
     return cudaGetLastError();
 }
 
@@ -473,11 +476,18 @@ extern "C" int slotscan_read_bwd(const slotscan_read_params* p, const void* qr, 
         return SLOTSCAN_E_NULL;
     if (sizeof(float) * (size_t)read_bwd_layout(p->N, p->G * p->NQ).total > 200 * 1024) return SLOTSCAN_E_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream_;
-    cudaError_t e;
+    cudaError_t e = cudaSuccess;
     const bool qb = p->q_dtype == SLOTSCAN_BF16, sb = p->snap_dtype == SLOTSCAN_BF16;
-    if (qb && sb) e = launch_read_bwd<__nv_bfloat16, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st);
-    else if (qb) e = launch_read_bwd<__nv_bfloat16, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st);
-    else if (sb) e = launch_read_bwd<float, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st);
-    else e = launch_read_bwd<float, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st);
+    // bf16 with dk = dv in {64, 128}: snapshots with more than RM_SPARSE_ROWS rows in use go through the tensor-core
+    // kernel, the others through the CUDA-core one (each tests the row count itself and leaves the other's alone)
+    int sparse_only = 0;
+    if (read_bwd_mma_try(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st, &e)) {
+        if (e != cudaSuccess) return (int)e;
+        sparse_only = 1;
+    }
+    if (qb && sb) e = launch_read_bwd<__nv_bfloat16, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, sparse_only, st);
+    else if (qb) e = launch_read_bwd<__nv_bfloat16, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, 0, st);
+    else if (sb) e = launch_read_bwd<float, __nv_bfloat16>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, 0, st);
+    else e = launch_read_bwd<float, float>(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, 0, st);
     return (int)e;
 }

@@ -177,3 +177,44 @@ def test_read_backward_matches_oracle(shape):
     again = torch.ops.slotscan.read_bwd(qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).float().cuda(),
                                         torch.from_numpy(valid).cuda(), drd.cuda(), G)
     assert all(torch.equal(a, b) for a, b in zip(again, (dqr, dsharp, dkbuf, dvbuf, dkinv)))
+
+
+@pytest.mark.parametrize("shape", [(2, 44, 2, 2, 192, 128, 128, 8, 100), (1, 64, 2, 2, 96, 64, 64, 8, 70),
+                                   (1, 32, 2, 1, 192, 128, 128, 16, 50), (4, 256, 6, 2, 192, 128, 128, 8, 150),
+                                   (1, 64, 3, 2, 192, 128, 128, 8, 192)],
+                         ids=["box128_T%G", "d64_n96", "box64_nq1", "768_snapshots", "all_rows"])
+def test_read_backward_tensor_core_path_bf16(shape):
+    """bf16 queries, snapshots and upstream gradient with dk = dv in {64, 128}: snapshots with more than 32 rows in use
+    take the tensor-core backward (five MMAs per snapshot, att and G in bf16, float32 accumulation, snapshot gradients
+    leave by tiled bulk tensor stores), the others the CUDA-core kernel.  Against the float64 oracle on the same
+    bf16-rounded inputs: bf16-typed gradients within 6e-3 of their max (one bf16 rounding of att / G per term plus the
+    rounding of the result), the float32-typed ones (dsharp, dkinv) within 2e-3; rows that are not valid exactly zero."""
+    S = _S()
+    B, T, H, NQ, N, DK, DV, G, nvalid = shape
+    qr, sharp, kbuf, vbuf = _case(*shape, seed=21)
+    drd = torch.randn(B, T, H, NQ, DV, generator=torch.Generator().manual_seed(22))
+    qr, kbuf, vbuf, drd = (x.to(torch.bfloat16) for x in (qr, kbuf, vbuf, drd))
+    kinv, valid = O.epilogue(kbuf.float().numpy(), dtype=np.float32)
+    f64 = lambda x: x.float().numpy().astype(np.float64)
+    want = O.read_bwd(f64(qr), sharp.numpy(), f64(kbuf), f64(vbuf), kinv, valid, G, f64(drd), kinv_const=True, dtype=np.float64)
+    args = (qr.cuda(), sharp.cuda(), kbuf.cuda(), vbuf.cuda(), torch.from_numpy(kinv).cuda(), torch.from_numpy(valid).cuda(),
+            drd.cuda(), G)
+    dqr, dsharp, dkbuf, dvbuf, dkinv = torch.ops.slotscan.read_bwd(*args)
+    assert dqr.dtype == torch.bfloat16 and dkbuf.dtype == torch.bfloat16 and dvbuf.dtype == torch.bfloat16
+    errs = {n: rel(g.float().cpu().numpy(), want[n]) for n, g in (("dqr", dqr), ("dkbuf", dkbuf), ("dvbuf", dvbuf), ("dsharp", dsharp))}
+    # dkinv against the oracle: d kbuf with kinv differentiated minus the direct part, divided out row by row
+    full = O.read_bwd(f64(qr), sharp.numpy(), f64(kbuf), f64(vbuf), kinv, valid, G, f64(drd), kinv_const=False, dtype=np.float64)
+    kb = f64(kbuf)
+    chain = (full["dkbuf"] - want["dkbuf"])                                  # = dkinv * (-kinv^3) * kbuf on valid rows
+    dkinv_want = (chain * kb).sum(-1) / np.maximum((kb * kb).sum(-1), 1e-30) / -(kinv.astype(np.float64) ** 3) * valid
+    errs["dkinv"] = rel(dkinv.cpu().numpy(), dkinv_want)
+    print(shape, {n: "%.1e" % e for n, e in errs.items()})
+    for n in ("dqr", "dkbuf", "dvbuf"):
+        assert errs[n] < 6e-3, (n, errs[n])
+    assert errs["dsharp"] < 2e-3 and errs["dkinv"] < 2e-3, errs
+    inval = ~torch.from_numpy(valid.astype(bool))
+    assert (dkbuf.cpu()[inval] == 0).all() and (dvbuf.cpu()[inval] == 0).all() and (dkinv.cpu()[inval] == 0).all()
+    again = torch.ops.slotscan.read_bwd(*args)
+    assert all(torch.equal(a, b) for a, b in zip(again, (dqr, dsharp, dkbuf, dvbuf, dkinv)))       # repeatable bit for bit
+    from slotscan_b200 import _lib
+    assert _lib.device_status() == 0
