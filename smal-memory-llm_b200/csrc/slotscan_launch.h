@@ -60,6 +60,9 @@ static inline cudaError_t run_rows_bwd(const slotscan_params& p, int D, int nten
 }
 // rows (highest valid row + 1) up to which a snapshot is read by the CUDA-core kernel even when the tensor-core one runs
 constexpr int RM_SPARSE_ROWS = 32;
+// The backward writes whole snapshots of gradients (zeros included), so it is bound by those writes whatever the row
+// count: every snapshot with at least one valid row takes the tensor-core kernel, the empty ones the CUDA-core kernel.
+constexpr int RB_SPARSE_ROWS = 0;
 // tensor-core forward read (slotscan_read_mma.cu): returns false when the shape / dtypes are not its own
 bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
                       const float* kinv, const uint8_t* valid, void* rd, cudaStream_t st, cudaError_t* err);

@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(RD_THREADS) read_bwd_kernel(
     }
     __syncthreads();
     const int nv = s_nv;
-    if (sparse_only && s_hvb > RM_SPARSE_ROWS) return;            // the tensor-core kernel takes this snapshot (uniform per CTA)
+    if (sparse_only && s_hvb > RB_SPARSE_ROWS) return;            // the tensor-core kernel takes this snapshot (uniform per CTA)
     // zero the whole block of snapshot gradients first; the valid rows are overwritten after the barrier below
     zero_fill(dkbuf + (size_t)so * N * DK, (size_t)N * DK, tid);
     zero_fill(dvbuf + (size_t)so * N * DV, (size_t)N * DV, tid);
@@ -478,7 +478,7 @@ extern "C" int slotscan_read_bwd(const slotscan_read_params* p, const void* qr, 
     cudaStream_t st = (cudaStream_t)stream_;
     cudaError_t e = cudaSuccess;
     const bool qb = p->q_dtype == SLOTSCAN_BF16, sb = p->snap_dtype == SLOTSCAN_BF16;
-    // bf16 with dk = dv in {64, 128}: snapshots with more than RM_SPARSE_ROWS rows in use go through the tensor-core
+    // bf16 with dk = dv in {64, 128}: snapshots with more than RB_SPARSE_ROWS rows in use go through the tensor-core
     // kernel, the others through the CUDA-core one (each tests the row count itself and leaves the other's alone)
     int sparse_only = 0;
     if (read_bwd_mma_try(*p, qr, sharp, kbuf, vbuf, kinv, valid, drd, dqr, dsharp, dkbuf, dvbuf, dkinv, st, &e)) {

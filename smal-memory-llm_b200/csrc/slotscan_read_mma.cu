@@ -781,7 +781,7 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_bwd_ring_kernel(
             fence_proxy_async_smem();
             __syncwarp();
             issue_meta(k + RR_META);
-            if (nv <= RM_SPARSE_ROWS) continue;                            // left to the CUDA-core kernel
+            if (nv <= RB_SPARSE_ROWS) continue;                            // left to the CUDA-core kernel
             const int M = q_count(it);
             const float sh = (lane < 16 && lane < M) ? sharp[q_index(it, lane)] : 0.f;
             // queries and upstream gradient: one buffer, free as soon as the math warps hold its fragments
@@ -839,6 +839,7 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_bwd_ring_kernel(
         // ================= the math warps =================
         const int r0 = lane >> 2, cq = (lane & 3) * 2;
         bool failed = false;
+        int dirty0 = N, dirty1 = N;                                // rows of stage 0 / 1 below this may hold non-zero data
         for (int kd = 0;; kd++) {
             const int s = kd & 1;
             bool ok = mbar_wait_bounded(&fullL[s], (unsigned)((kd >> 1) & 1));
@@ -1059,8 +1060,12 @@ __global__ void __launch_bounds__(RR_THREADS, 1) read_bwd_ring_kernel(
                     *reinterpret_cast<__nv_bfloat162*>(Vst + offb) = __floats2bfloat162_rn(cv[2], cv[3]);
                 }
             }
-            // rows above the visited ones leave as zeros (the stores cover whole snapshots)
-            for (int i = tid; i < (N - NPv) * 8 * NSUB; i += RR_WARPS * 32) {
+            // Rows above the visited ones leave as zeros (the stores cover whole snapshots).  Only rows that can hold
+            // something else are rewritten: what this snapshot's box brought in, or the previous gradients of this stage.
+            const int hb = nv <= h64 ? h64 : (nv <= h128 ? h128 : N);
+            const int dirty = max(hb, s ? dirty1 : dirty0);
+            if (s) dirty1 = NPv; else dirty0 = NPv;
+            for (int i = tid; i < (dirty - NPv) * 8 * NSUB; i += RR_WARPS * 32) {
                 const int row = NPv + i / (8 * NSUB), c = i % (8 * NSUB);
                 const int off = (c >> 3) * RR_SUB + row * 128 + ((c & 7) << 4);
                 *reinterpret_cast<uint4*>(Kst + off) = make_uint4(0u, 0u, 0u, 0u);
@@ -1136,7 +1141,7 @@ bool read_fwd_mma_try(const slotscan_read_params& p, const void* qr, const float
     return true;
 }
 
-// true (and *err set) when the tensor-core backward takes the snapshots with more than RM_SPARSE_ROWS rows in use; the
+// true (and *err set) when the tensor-core backward takes the snapshots with more than RB_SPARSE_ROWS rows in use; the
 // caller then runs the CUDA-core kernel for the others
 bool read_bwd_mma_try(const slotscan_read_params& p, const void* qr, const float* sharp, const void* kbuf, const void* vbuf,
                       const float* kinv, const uint8_t* valid, const void* drd, void* dqr, float* dsharp, void* dkbuf,

@@ -188,7 +188,8 @@ def test_read_backward_tensor_core_path_bf16(shape):
     take the tensor-core backward (five MMAs per snapshot, att and G in bf16, float32 accumulation, snapshot gradients
     leave by tiled bulk tensor stores), the others the CUDA-core kernel.  Against the float64 oracle on the same
     bf16-rounded inputs: bf16-typed gradients within 6e-3 of their max (one bf16 rounding of att / G per term plus the
-    rounding of the result), the float32-typed ones (dsharp, dkinv) within 2e-3; rows that are not valid exactly zero."""
+    rounding of the result; measured 2e-3 .. 4e-3), the float32-typed ones (dsharp, dkinv) within 1e-5 (measured 3e-7); rows
+    that are not valid exactly zero."""
     S = _S()
     B, T, H, NQ, N, DK, DV, G, nvalid = shape
     qr, sharp, kbuf, vbuf = _case(*shape, seed=21)
@@ -211,7 +212,7 @@ def test_read_backward_tensor_core_path_bf16(shape):
     print(shape, {n: "%.1e" % e for n, e in errs.items()})
     for n in ("dqr", "dkbuf", "dvbuf"):
         assert errs[n] < 6e-3, (n, errs[n])
-    assert errs["dsharp"] < 2e-3 and errs["dkinv"] < 2e-3, errs
+    assert errs["dsharp"] < 1e-5 and errs["dkinv"] < 1e-5, errs
     inval = ~torch.from_numpy(valid.astype(bool))
     assert (dkbuf.cpu()[inval] == 0).all() and (dvbuf.cpu()[inval] == 0).all() and (dkinv.cpu()[inval] == 0).all()
     again = torch.ops.slotscan.read_bwd(*args)
