@@ -327,7 +327,10 @@ template <int D, typename Tin>
 struct RowsBwd3Layout {
     static constexpr int RPB = ROW_THREADS / (D / 8);
     static constexpr int XRS = D * (int)sizeof(Tin) + 16;                 // bytes per padded token row
-    static constexpr int off_S = 0, S_bytes = (RC / 8) * RPB * D * 4;     // [block][row][D]
+    // [block][row][D] with 16 bytes between the blocks: in the token-parallel pass the lanes of a warp (tokens of up to
+    // four blocks) read the same element of up to four blocks at once, and without the stagger those sit in the same banks
+    static constexpr int SBS = RPB * D + 4;                               // floats per block
+    static constexpr int off_S = 0, S_bytes = (RC / 8) * SBS * 4;
     static constexpr int off_x = off_S + S_bytes, x_bytes = RC * XRS;     // two stages
     static constexpr int off_xo = off_x + 2 * x_bytes, xo_bytes = RC * D * 4;
     static constexpr int off_c = off_xo + xo_bytes, c_bytes = RC * RPB * 4;   // [row][token]
@@ -502,7 +505,12 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
                 if (sg < nseg) {
                     const int ilo = sg * G, ihi = min(tc, ilo + G) - 1;
                     // top of the block: dX is S, c = 1
-                    st8(s_S + ((size_t)sg * RPB + r) * D + c * 8, dX);
+                    {   // the row's two float4 halves of every lane go to [c] and [D/8 + c] of the row's float4 slots: lanes
+                        // c and c + 4 of a quarter-warp would otherwise store to the same banks (the pass below reads it so)
+                        float* Sw = s_S + (size_t)sg * LY::SBS + r * D;
+                        st4(Sw + 4 * c, make_float4(dX[0], dX[1], dX[2], dX[3]));
+                        st4(Sw + D / 2 + 4 * c, make_float4(dX[4], dX[5], dX[6], dX[7]));
+                    }
                     float c_cur = 1.f;
                     float xdx_cur = dotXdX();
                     unsigned ms = (m >> ilo) & ((1u << G) - 1u);
@@ -557,13 +565,13 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             const Tin* xr = reinterpret_cast<const Tin*>(dsm + LY::off_x + st * LY::x_bytes + lane * LY::XRS);
             for (int rr = warp; rr < RPB; rr += ROW_THREADS / 32) {
                 if (row0 + rr >= N || t < s_ts[rr]) continue;
-                const float* Sr = s_S + ((size_t)sg * RPB + rr) * D;
+                const float* Sr = s_S + (size_t)sg * LY::SBS + rr * D;
                 float a0_ = 0.f, a1_ = 0.f, a2_ = 0.f, a3_ = 0.f;
 #pragma unroll 4
                 for (int d = 0; d < D; d += 8) {
                     float xv[8];
                     row8(xv, xr + d);
-                    const float4 s0 = ld4(Sr + d), s1 = ld4(Sr + d + 4);
+                    const float4 s0 = ld4(Sr + d / 2), s1 = ld4(Sr + D / 2 + d / 2);      // elements d .. d+3 and d+4 .. d+7
                     a0_ = fmaf(xv[0], s0.x, a0_); a1_ = fmaf(xv[1], s0.y, a1_);
                     a2_ = fmaf(xv[2], s0.z, a2_); a3_ = fmaf(xv[3], s0.w, a3_);
                     a0_ = fmaf(xv[4], s1.x, a0_); a1_ = fmaf(xv[5], s1.y, a1_);
