@@ -66,18 +66,29 @@ struct ProfScope {
 
 constexpr size_t SMEM_CAP = 227 * 1024;
 
-// One extra stream per device so that the sequential address scan and the zero-fill of the snapshot rows its first
-// pass cannot touch run side by side.  Created on first use; lives until the process exits.
+// Extra streams so that the sequential address scan and the zero-fill of the snapshot rows its first pass cannot touch
+// run side by side: one per (device, caller stream), created on first use and kept until the process exits, so that
+// callers that work on several streams of a device at once (a pipeline over batch chunks) keep their scans independent
+// of one another.  Beyond SIDE_STREAMS_MAX caller streams per device the extra streams are shared round-robin.
 constexpr int MAX_DEVICES = 64;
-static cudaStream_t g_side_stream[MAX_DEVICES] = {nullptr};
+constexpr int SIDE_STREAMS_MAX = 32;
+struct SideStreams { cudaStream_t caller[SIDE_STREAMS_MAX]; cudaStream_t side[SIDE_STREAMS_MAX]; int n; };
+static SideStreams g_side[MAX_DEVICES];
 static std::mutex g_side_mu;
-static cudaStream_t side_stream() {
+static cudaStream_t side_stream(cudaStream_t caller) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
     std::lock_guard<std::mutex> l(g_side_mu);
-    if (g_side_stream[dev] == nullptr && cudaStreamCreateWithFlags(&g_side_stream[dev], cudaStreamNonBlocking) != cudaSuccess)
-        g_side_stream[dev] = nullptr;
-    return g_side_stream[dev];
+    SideStreams& S = g_side[dev];
+    for (int i = 0; i < S.n; i++)
+        if (S.caller[i] == caller) return S.side[i];
+    if (S.n == SIDE_STREAMS_MAX) return S.side[(size_t)((uintptr_t)caller >> 4) % SIDE_STREAMS_MAX];
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    S.caller[S.n] = caller;
+    S.side[S.n] = s;
+    S.n++;
+    return s;
 }
 
 static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,
@@ -92,7 +103,7 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
     cudaEvent_t joined = nullptr, fork = nullptr;
     cudaStream_t side = nullptr;
     if (p.N > AF_NCAP1 && ex.K0 == nullptr) {
-        side = side_stream();
+        side = side_stream(st);
         if (side != nullptr && cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess &&
             cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) == cudaSuccess) {
             auto up = [](int row, int tile) { return (row + tile - 1) / tile * tile; };
