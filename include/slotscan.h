@@ -217,8 +217,13 @@ int slotscan_v_bwd(const slotscan_v_params* p, const void* v, const float* wa, c
  *   bits   0: y = x.  2, 3, 4 or 8 (memlm_sh.py:81): y = _fq(x, bits, group), the midrise quantiser with one
  *          absmax scale per `group` channels, evaluated in the reference's arithmetic including its straight-through
  *          form x + (q - x); an all-zero group stays exactly zero.  group: a power of two, 4 <= group <= D.
+ *          SLOTSCAN_BITS_E4M3 (-8): fp8-e4m3 storage with one scale per ROW, s = max(absmax / 448, 1e-30),
+ *          y = e4m3(x / s) * s (round to nearest even, saturating), `group` ignored; an all-zero row stays zero.  The
+ *          reference has no fp8 format (only a remark on storing the scale in fp8, memlm_sh.py:217-218): this mode
+ *          follows a restatement, not reference code.
  *   kinv and valid are taken from the quantised row before the cast, as _quantize_mem does (:232-234).
  * Forward values only (the reference's gradient is the identity through _fq). */
+#define SLOTSCAN_BITS_E4M3 (-8)
 typedef struct {
     int64_t rows;
     int32_t D;              /* 8, 16, 32, 64 or 128 */

@@ -10,6 +10,7 @@
 // group / 8 neighbouring lanes (absmax by shuffles); groups of 4 are two per lane.  Grid: a multiple of the SM
 // count, grid-stride over rows.  HBM-bound: (e_in + e_out) * D bytes per row plus 5 bytes for kinv and valid.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* 
                                                                      const int bits, const int group) {
     constexpr int LPR = D / 8, RPB = EP_THREADS / LPR;
     const int r = threadIdx.x / LPR, c = threadIdx.x % LPR;
-    const float half = bits ? (float)(1 << (bits - 1)) : 0.f;
+    const float half = bits > 0 ? (float)(1 << (bits - 1)) : 0.f;
     for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += (long long)gridDim.x * RPB) {
         const long long row = row0 + r;
         const bool live = row < rows;                    // dead lanes keep running the shuffles on zeros
@@ -72,7 +73,19 @@ __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* 
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = 0.f;
         }
-        if (bits) {
+        if (bits == SLOTSCAN_BITS_E4M3) {                 // fp8-e4m3 storage, one scale per row
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) a = fmaxf(a, fabsf(v[j]));
+            for (int off = 1; off < LPR; off <<= 1) a = fmaxf(a, __shfl_xor_sync(FULL, a, off));
+            const float sc = fmaxf(__fdiv_rn(a, 448.f), 1e-30f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[j], sc), __NV_SATFINITE, __NV_E4M3);
+                const float f = __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+                v[j] = a > 0.f ? __fmul_rn(f, sc) : 0.f;
+            }
+        } else if (bits) {
             if (group >= 8) {
                 float a = 0.f;
 #pragma unroll
@@ -141,7 +154,7 @@ extern "C" int slotscan_epilogue_check(const slotscan_epilogue_params* p) {
     if ((p->in_dtype != SLOTSCAN_F32 && p->in_dtype != SLOTSCAN_BF16) ||
         (p->out_dtype != SLOTSCAN_F32 && p->out_dtype != SLOTSCAN_BF16))
         return SLOTSCAN_E_DTYPE;
-    if (p->bits != 0) {
+    if (p->bits != 0 && p->bits != SLOTSCAN_BITS_E4M3) {
         if (!(p->bits == 2 || p->bits == 3 || p->bits == 4 || p->bits == 8)) return SLOTSCAN_E_MODE;   /* memlm_sh.py:81 */
         const int g = p->group;
         if (g < 4 || g > D || (g & (g - 1)) != 0) return SLOTSCAN_E_MODE;   /* power of two that divides D (:82-83) */

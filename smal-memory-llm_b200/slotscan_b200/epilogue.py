@@ -16,6 +16,12 @@ from . import _lib
 from .ops import _ptr, _require_cuda, _stream
 
 _CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+E4M3 = "e4m3"            # value of `bits` / `qbits` for fp8-e4m3 storage with one absmax scale per row (SLOTSCAN_BITS_E4M3)
+
+
+def _bits(bits):
+    """2, 3, 4, 8 (the reference's midrise quantiser), 0 (none) or "e4m3" -> the C ABI's code."""
+    return -8 if bits == E4M3 else int(bits)
 
 
 def _run(x, out_dtype, bits, group, want_y, want_norm):
@@ -61,11 +67,12 @@ def _fq_backward(ctx, dy):
 _fq_op.register_autograd(_fq_backward, setup_context=_fq_setup)
 
 
-def fq(x, bits, group):
-    """`_fq(x, bits, group)` of the reference (memlm_sh.py:221-229): forward the quantised value, gradient identity."""
-    if x.shape[-1] % group:
+def fq(x, bits, group=16):
+    """`_fq(x, bits, group)` of the reference (memlm_sh.py:221-229): forward the quantised value, gradient identity.
+    bits = "e4m3": fp8-e4m3 storage with one scale per row (no counterpart in the reference; `group` ignored)."""
+    if bits != E4M3 and x.shape[-1] % group:
         raise ValueError("group %d does not divide the channel count %d" % (group, x.shape[-1]))
-    return _fq_op(x, int(bits), int(group))
+    return _fq_op(x, _bits(bits), int(group))
 
 
 @torch.library.custom_op("slotscan::epilogue", mutates_args=())
@@ -110,15 +117,16 @@ _epilogue_op.register_autograd(_ep_backward, setup_context=_ep_setup)
 
 def writer_epilogue(kbuf, buf, out_dtype, qbits=0, qgroup=16):
     """What the writer hands to the readers (memlm_sh.py:464-475): `(kbuf', buf', kinv, valid)` with the snapshots
-    cast to `out_dtype`, quantised first when `qbits` is 2, 3, 4 or 8 (`_quantize_mem`).  `valid` is a bool tensor."""
+    cast to `out_dtype`, quantised first when `qbits` is 2, 3, 4 or 8 (`_quantize_mem`) or "e4m3" (fp8 storage, one
+    scale per row).  `valid` is a bool tensor."""
     if out_dtype not in _CODE:
         raise TypeError("out_dtype must be float32 or bfloat16")
-    kq, kinv, valid = _epilogue_op(kbuf, out_dtype == torch.bfloat16, int(qbits), int(qgroup))
+    kq, kinv, valid = _epilogue_op(kbuf, out_dtype == torch.bfloat16, _bits(qbits), int(qgroup))
     vq = fq(buf, qbits, qgroup).to(out_dtype) if qbits else buf.to(out_dtype)
     return kq, vq, kinv, valid.bool()
 
 
 def quantize_mem(kbuf, buf, bits, group):
     """`_quantize_mem(kbuf, buf, bits, group)` of the reference (memlm_sh.py:231-234): dtypes unchanged."""
-    kq, kinv, valid = _epilogue_op(kbuf, kbuf.dtype == torch.bfloat16, int(bits), int(group))
+    kq, kinv, valid = _epilogue_op(kbuf, kbuf.dtype == torch.bfloat16, _bits(bits), int(group))
     return kq, fq(buf, bits, group), kinv, valid.bool()
