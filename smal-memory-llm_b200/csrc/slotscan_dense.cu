@@ -98,18 +98,33 @@ __device__ __forceinline__ float dense_scores(const float* K, const float* qv, i
     qq = warp_sum_d(qq);
     const double qnorm = sqrt(qq), qinv = 1.0 / fmax(qnorm, 1e-6);
     if (qnorm_out != nullptr) *qnorm_out = (float)qnorm;
-    for (int n = warp; n <= lim; n += DN_WARPS) {
+    // 8 lanes per row, 4 rows per warp at a time: three shuffle stages per row group instead of five per row
+    const int r4 = lane >> 3, l8 = lane & 7;
+    for (int base = warp * 4; base <= lim; base += DN_WARPS * 4) {
+        const int n = min(base + r4, lim);
         const float* Kn = K + (size_t)n * DK;
+        // the row may sit in global memory (the backward's replayed states): every load of the slice is issued before
+        // the first use, or each iteration would wait out a memory latency of its own
+        float kx[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++) { const int d = l8 + 8 * c; kx[c] = d < DK ? Kn[d] : 0.f; }
         double kk = 0.0, dt = 0.0;
-        for (int d = lane; d < DK; d += 32) {
-            const double kd = (double)Kn[d];
-            kk = fma(kd, kd, kk);
-            dt = fma(kd, (double)qv[d], dt);
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            const int d = l8 + 8 * c;
+            if (d < DK) {
+                const double kd = (double)kx[c];
+                kk = fma(kd, kd, kk);
+                dt = fma(kd, (double)qv[d], dt);
+            }
         }
-        kk = warp_sum_d(kk);
-        dt = warp_sum_d(dt);
+#pragma unroll
+        for (int off = 1; off < 8; off <<= 1) {
+            kk += __shfl_xor_sync(FULL, kk, off);
+            dt += __shfl_xor_sync(FULL, dt, off);
+        }
         const double ki = 1.0 / fmax(sqrt(kk), 1e-6);
-        if (lane == 0) { s[n] = (dt * ki * qinv) * (double)temp; kinv[n] = (float)ki; }
+        if (l8 == 0 && base + r4 <= lim) { s[n] = (dt * ki * qinv) * (double)temp; kinv[n] = (float)ki; }
     }
     return (float)qinv;
 }
@@ -181,15 +196,15 @@ __global__ void __launch_bounds__(DN_THREADS) dense_fwd_kernel(
         __syncthreads();
         {
             const float g = s_f[0];
-            for (int i = tid; i < (lim + 1) * DK; i += DN_THREADS) {
-                const int n = i / DK, d = i - n * DK;
-                const float w = g * a[n];
-                if (a[n] != 0.f) K[i] = (1.f - w) * K[i] + w * kt[d];
-            }
-            for (int i = tid; i < (lim + 1) * DV; i += DN_THREADS) {
-                const int n = i / DV, d = i - n * DV;
-                const float w = g * a[n];
-                if (a[n] != 0.f) V[i] = (1.f - w) * V[i] + w * vt[d];
+            const int lane = tid & 31;
+            for (int n = warp; n <= lim; n += DN_WARPS) {      // a warp per row, lanes over the columns
+                const float an = a[n];
+                if (an == 0.f) continue;
+                const float w = g * an;
+                float* Kr = K + (size_t)n * DK;
+                float* Vr = V + (size_t)n * DV;
+                for (int d = lane; d < DK; d += 32) Kr[d] = (1.f - w) * Kr[d] + w * kt[d];
+                for (int d = lane; d < DV; d += 32) Vr[d] = (1.f - w) * Vr[d] + w * vt[d];
             }
         }
         __syncthreads();
@@ -282,17 +297,24 @@ __global__ void __launch_bounds__(DN_THREADS) dense_bwd_kernel(
             }
             __syncthreads();
             const float g = s_f[0];
-            for (size_t i = tid; i < SK; i += DN_THREADS) {
-                const int n = (int)(i / DK), d = (int)(i - (size_t)n * DK);
-                float x = Kp[i];
-                if (n <= lim && a[n] != 0.f) { const float w = g * a[n]; x = (1.f - w) * x + w * kt[d]; }
-                Kn[i] = x;
-            }
-            for (size_t i = tid; i < SV; i += DN_THREADS) {
-                const int n = (int)(i / DV), d = (int)(i - (size_t)n * DV);
-                float x = Vp[i];
-                if (n <= lim && a[n] != 0.f) { const float w = g * a[n]; x = (1.f - w) * x + w * vt[d]; }
-                Vn[i] = x;
+            for (int n = warp; n < N; n += DN_WARPS) {          // a warp per row, lanes over the columns
+                const bool hit = n <= lim && a[n] != 0.f;
+                const float w = hit ? g * a[n] : 0.f;
+                const float *Kr = Kp + (size_t)n * DK, *Vr = Vp + (size_t)n * DV;
+                float *Ko = Kn + (size_t)n * DK, *Vo = Vn + (size_t)n * DV;
+                float kx[4], vx[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    kx[c] = d < DK ? Kr[d] : 0.f;
+                    vx[c] = d < DV ? Vr[d] : 0.f;
+                }
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    if (d < DK) Ko[d] = hit ? (1.f - w) * kx[c] + w * kt[d] : kx[c];
+                    if (d < DV) Vo[d] = hit ? (1.f - w) * vx[c] + w * vt[d] : vx[c];
+                }
             }
             for (int n = tid; n < N; n += DN_THREADS) {
                 float x = op[n];
@@ -318,9 +340,18 @@ __global__ void __launch_bounds__(DN_THREADS) dense_bwd_kernel(
             const float qinv = dense_scores(Kp, qv, DK, lim, temp, s, ki, &qnorm);
             // dw_n = <k_t - K_n, dK_n> + <v_t - V_n, dV_n> + (1 - o_n) dO_n      (slotkern_kvg.py:165)
             for (int n = warp; n <= lim; n += DN_WARPS) {
+                float kx[4], vx[4];                          // all loads of the row first (global memory: see dense_scores)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    kx[c] = d < DK ? Kp[(size_t)n * DK + d] : 0.f;
+                    vx[c] = d < DV ? Vp[(size_t)n * DV + d] : 0.f;
+                }
                 float a1 = 0.f;
-                for (int d = lane; d < DK; d += 32) a1 = fmaf(kt[d] - Kp[(size_t)n * DK + d], dK[(size_t)n * DK + d], a1);
-                for (int d = lane; d < DV; d += 32) a1 = fmaf(vt[d] - Vp[(size_t)n * DV + d], dV[(size_t)n * DV + d], a1);
+#pragma unroll
+                for (int c = 0; c < 4; c++) { const int d = lane + 32 * c; if (d < DK) a1 = fmaf(kt[d] - kx[c], dK[(size_t)n * DK + d], a1); }
+#pragma unroll
+                for (int c = 0; c < 4; c++) { const int d = lane + 32 * c; if (d < DV) a1 = fmaf(vt[d] - vx[c], dV[(size_t)n * DV + d], a1); }
                 a1 = warp_sum(a1);
                 if (lane == 0) dw[n] = a1 + (1.f - op[n]) * dO[n];
             }
@@ -357,9 +388,18 @@ __global__ void __launch_bounds__(DN_THREADS) dense_bwd_kernel(
             if (tid < DK) {
                 const int d = tid;
                 float acc = 0.f, qacc = 0.f;
-                for (int n = 0; n <= lim; n++) {
-                    if (a[n] != 0.f) acc = fmaf(g * a[n], dK[(size_t)n * DK + d], acc);
-                    if (dz[n] != 0.f) qacc = fmaf(dz[n] * temp, Kp[(size_t)n * DK + d] * ki[n], qacc);
+                for (int n0 = 0; n0 <= lim; n0 += 8) {          // eight rows of the (global) state in flight at a time
+                    float kp[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) kp[u] = (n0 + u <= lim) ? Kp[(size_t)(n0 + u) * DK + d] : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int n = n0 + u;
+                        if (n <= lim) {
+                            if (a[n] != 0.f) acc = fmaf(g * a[n], dK[(size_t)n * DK + d], acc);
+                            if (dz[n] != 0.f) qacc = fmaf(dz[n] * temp, kp[u] * ki[n], qacc);
+                        }
+                    }
                 }
                 sttok(dk + ix * DK + d, acc);
                 my_dqn = qacc;
@@ -387,22 +427,42 @@ __global__ void __launch_bounds__(DN_THREADS) dense_bwd_kernel(
             }
             // ---- carry the state adjoints to the pre-write side (slotkern_kvg.py:183-196) ----
             const bool emit = (j == 0);
-            for (int i = tid; i < (lim + 1) * DK; i += DN_THREADS) {
-                const int n = i / DK, d = i - n * DK;
+            for (int n = warp; n <= lim; n += DN_WARPS) {        // a warp per row, lanes over the columns
                 const float om = 1.f - g * a[n];
-                float x = om * dK[i];
-                if (emit && dkbuf != nullptr) x += dkbuf[so * SK + i];
-                if (!detach && dz[n] != 0.f && ki[n] < 1e6f) {           // the key-match gradient; zero under the norm clamp
-                    const float kh = Kp[i] * ki[n];
-                    x = fmaf(ki[n] * dz[n], temp * (qv[d] * qinv) - kh * sf[n], x);
+                const bool match = !detach && dz[n] != 0.f && ki[n] < 1e6f;   // the key-match gradient; zero under the norm clamp
+                const float kin = ki[n], dzn = dz[n], sfn = sf[n];
+                float kx[4], gk[4], gv[4];                   // global loads of the row first
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    kx[c] = (match && d < DK) ? Kp[(size_t)n * DK + d] : 0.f;
+                    gk[c] = (emit && dkbuf != nullptr && d < DK) ? dkbuf[so * SK + (size_t)n * DK + d] : 0.f;
+                    gv[c] = (emit && dvbuf != nullptr && d < DV) ? dvbuf[so * SV + (size_t)n * DV + d] : 0.f;
                 }
-                dK[i] = x;
-            }
-            for (int i = tid; i < (lim + 1) * DV; i += DN_THREADS) {
-                const int n = i / DV;
-                float x = (1.f - g * a[n]) * dV[i];
-                if (emit && dvbuf != nullptr) x += dvbuf[so * SV + i];
-                dV[i] = x;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    if (d < DK) {
+                        const size_t i = (size_t)n * DK + d;
+                        float x = om * dK[i];
+                        if (emit && dkbuf != nullptr) x += gk[c];
+                        if (match) {
+                            const float kh = kx[c] * kin;
+                            x = fmaf(kin * dzn, temp * (qv[d] * qinv) - kh * sfn, x);
+                        }
+                        dK[i] = x;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int d = lane + 32 * c;
+                    if (d < DV) {
+                        const size_t i = (size_t)n * DV + d;
+                        float x = om * dV[i];
+                        if (emit && dvbuf != nullptr) x += gv[c];
+                        dV[i] = x;
+                    }
+                }
             }
             for (int n = tid; n <= lim; n += DN_THREADS)
                 dO[n] = (1.f - g * a[n]) * dO[n] - (p.occ_bin ? 0.f : fr_t * dz[n]);

@@ -111,10 +111,12 @@ __global__ void __launch_bounds__(KV_THREADS) keyless_fwd_kernel(const slotscan_
         }
         __syncthreads();
         const float g = s_f[0];
-        for (int i = tid; i < N * DV; i += KV_THREADS) {
-            const int n = i / DV, d = i - n * DV;
-            const float w = g * a[n];
-            if (a[n] != 0.f) V[i] = (1.f - w) * V[i] + w * vt[d];
+        for (int n = tid >> 5; n < N; n += KV_THREADS / 32) {      // a warp per row, lanes over the columns
+            const float an = a[n];
+            if (an == 0.f) continue;
+            const float w = g * an;
+            float* Vr = V + (size_t)n * DV;
+            for (int d = tid & 31; d < DV; d += 32) Vr[d] = (1.f - w) * Vr[d] + w * vt[d];
         }
         __syncthreads();
     }
@@ -172,11 +174,19 @@ __global__ void __launch_bounds__(KV_THREADS) keyless_bwd_kernel(const slotscan_
             }
             __syncthreads();
             const float g = s_f[0];
-            for (size_t i = tid; i < SV; i += KV_THREADS) {
-                const int n = (int)(i / DV), d = (int)(i - (size_t)n * DV);
-                float x = Vp[i];
-                if (a[n] != 0.f) { const float w = g * a[n]; x = (1.f - w) * x + w * vt[d]; }
-                Vn[i] = x;
+            for (int n = tid >> 5; n < N; n += KV_THREADS / 32) {  // a warp per row; the row's loads first (global memory)
+                const bool hit = a[n] != 0.f;
+                const float w = hit ? g * a[n] : 0.f;
+                for (int d0 = 0; d0 < DV; d0 += 128) {         // 128 columns at a time, four loads per lane in flight
+                    float vx[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) { const int d = d0 + (tid & 31) + 32 * c; vx[c] = d < DV ? Vp[(size_t)n * DV + d] : 0.f; }
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const int d = d0 + (tid & 31) + 32 * c;
+                        if (d < DV) Vn[(size_t)n * DV + d] = hit ? (1.f - w) * vx[c] + w * vt[d] : vx[c];
+                    }
+                }
             }
             for (int n = tid; n < N; n += KV_THREADS) {
                 float x = op[n];
@@ -225,11 +235,14 @@ __global__ void __launch_bounds__(KV_THREADS) keyless_bwd_kernel(const slotscan_
             }
             __syncthreads();
             const bool emit = (j == 0);
-            for (size_t i = tid; i < SV; i += KV_THREADS) {
-                const int n = (int)(i / DV);
-                float x = (1.f - g * a[n]) * dV[i];
-                if (emit && dbuf != nullptr) x += dbuf[so * SV + i];
-                dV[i] = x;
+            for (int n = tid >> 5; n < N; n += KV_THREADS / 32) {
+                const float om = 1.f - g * a[n];
+                for (int d = tid & 31; d < DV; d += 32) {
+                    const size_t i = (size_t)n * DV + d;
+                    float x = om * dV[i];
+                    if (emit && dbuf != nullptr) x += dbuf[so * SV + i];
+                    dV[i] = x;
+                }
             }
             for (int n = tid; n < N; n += KV_THREADS) dO[n] = (1.f - g * a[n]) * dO[n] - frf * dz[n];
             __syncthreads();
