@@ -405,8 +405,24 @@ def run_gpu(args, rank, local_rank, world):
     bs = B // P
     streams = [torch.cuda.Stream(device=dev) for _ in range(P)]
     host = job.host
-    hout = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (host["k"], host["q"], host["v"], host["gate"], host["fr"])]
-    htemp = torch.empty(P, dtype=torch.float32).pin_memory()
+    # One pinned staging buffer per chunk and direction: [k | q | v | gate | fr] of the chunk's sequences back to back, so
+    # that a chunk moves in ONE host->device copy and its gradients (+ dtemp) leave in ONE device->host copy.  The
+    # "application" owns these buffers: producing the inputs into them / consuming the gradients from them is its side.
+    names = ("k", "q", "v", "gate", "fr")
+    sizes = [host[n][:bs].numel() * host[n].element_size() for n in names]
+    offs = [sum(sizes[:i]) for i in range(len(names))]
+    chunk_bytes = (sum(sizes) + 4 + 255) // 256 * 256             # + dtemp on the way out
+    hin = [torch.empty(chunk_bytes, dtype=torch.uint8).pin_memory() for _ in range(P)]
+    hout = [torch.empty(chunk_bytes, dtype=torch.uint8).pin_memory() for _ in range(P)]
+    din = [torch.empty(chunk_bytes, dtype=torch.uint8, device=dev) for _ in range(P)]
+    dout = [torch.empty(chunk_bytes, dtype=torch.uint8, device=dev) for _ in range(P)]
+
+    def view(flat, j):                                            # tensor j of a chunk inside its staging buffer
+        t = host[names[j]]
+        return flat[offs[j]:offs[j] + sizes[j]].view(t.dtype).view((bs,) + tuple(t.shape[1:]))
+    for i in range(P):                                            # the inputs, as the application would have left them
+        for j, n in enumerate(names):
+            view(hin[i], j).copy_(host[n][i * bs:(i + 1) * bs])
 
     def e2e_step():
         cur = torch.cuda.current_stream()
@@ -416,15 +432,17 @@ def run_gpu(args, rank, local_rank, world):
             sl = slice(i * bs, (i + 1) * bs)
             st.wait_event(start)
             with torch.cuda.stream(st):
-                x = {n: t[sl].to(dev, non_blocking=True) for n, t in host.items()}
+                din[i].copy_(hin[i], non_blocking=True)
+                x = {n: view(din[i], j) for j, n in enumerate(names)}
                 grads = job.scan(x, sl)
-                for h_, g_ in zip(hout, grads[:5]):
-                    h_[sl].copy_(g_, non_blocking=True)
-                htemp[i:i + 1].copy_(grads[5], non_blocking=True)
+                for j in range(5):
+                    view(dout[i], j).copy_(grads[j])
+                dout[i][offs[4] + sizes[4]:offs[4] + sizes[4] + 4].view(torch.float32).copy_(grads[5].reshape(1))
+                hout[i].copy_(dout[i], non_blocking=True)
         for st in streams:
             cur.wait_stream(st)
         cur.synchronize()                                  # the caller holds the gradients on the host
-        return float(htemp.sum())                          # dtemp is the sum over the chunks
+        return sum(float(h[offs[4] + sizes[4]:offs[4] + sizes[4] + 4].view(torch.float32)[0]) for h in hout)   # dtemp
     e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -434,20 +452,19 @@ def run_gpu(args, rank, local_rank, world):
     f1.record()
     barrier()
     ms_e2e = f0.elapsed_time(f1)
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = sum(t.numel() * t.element_size() for t in hout) + 4 * P
+    h2d = P * chunk_bytes
+    d2h = P * chunk_bytes
 
     # copies alone, both directions at once on two streams: the link's share of the end-to-end step on this host
     up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    dsrc = {n: torch.empty_like(t) for n, t in job.devin.items()}
 
     def copies_only():
         with torch.cuda.stream(up):
-            for n, t in host.items():
-                job.devin[n].copy_(t, non_blocking=True)
+            for i in range(P):
+                din[i].copy_(hin[i], non_blocking=True)
         with torch.cuda.stream(down):
-            for h_, n in zip(hout, ("k", "q", "v", "gate", "fr")):
-                h_.copy_(dsrc[n], non_blocking=True)
+            for i in range(P):
+                hout[i].copy_(dout[i], non_blocking=True)
         up.synchronize(); down.synchronize()
     copies_only()
     barrier()
@@ -455,7 +472,6 @@ def run_gpu(args, rank, local_rank, world):
     for _ in range(3):
         copies_only()
     ms_copy = (time.perf_counter() - t0) / 3 * 1e3
-    del dsrc
 
     # strong scaling is the headline; the weak figure (64 sequences on every GPU) rides along when ranks > 1
     weak = None
@@ -527,7 +543,7 @@ def run_gpu(args, rank, local_rank, world):
                            "global_batch": global_B, "seq_len": T, "sharding": "batch, no collective",
                            "l2": "working set %.1f GB per step and GPU >> 126 MB L2 (no flush needed)" % (step_bytes / 1e9)},
                 "e2e": {"value": toks / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e / args.steps, "pipeline": "%d batch chunks on %d streams" % (P, P),
+                        "ms_per_step": ms_e2e / args.steps, "pipeline": "%d batch chunks on %d streams, one pinned staging buffer and one copy per chunk and direction" % (P, P),
                         "copies_only_ms": ms_copy, "copies_only_gbs_each_way": h2d / (ms_copy * 1e-3) / 1e9},
                 "gpu_launches": launches,
                 "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
