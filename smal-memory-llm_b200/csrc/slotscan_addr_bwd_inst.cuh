@@ -43,7 +43,10 @@ static cudaError_t launch_gather(const slotscan_params& p, const void* q, const 
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         dim3 grid(p.B * p.H, (p.T + GC - 1) / GC);
-        addr_bwd_gather_kernel<DK, Tin><<<grid, GA_THREADS, 0, st>>>(p, (const Tin*)q, gate, fr, temp, L.addr, L.kold, L.oold,
+        const size_t dyn = (size_t)GC * DK * sizeof(Tin) + 2 * (size_t)GC * GATHER_ROWS * sizeof(float);   // queries + D rows
+        auto gk = addr_bwd_gather_kernel<DK, Tin>;
+        if ((e = opt_in_smem(gk, dyn)) != cudaSuccess) return e;
+        gk<<<grid, GA_THREADS, dyn, st>>>(p, (const Tin*)q, gate, fr, temp, L.addr, L.kold, L.oold,
                                                                       L.kiold, L.kfin, L.ofin, L.tfirst, vend, Dn, (Tin*)dq,
                                                                       dgate, dfr, part, part_stride);
         return cudaGetLastError();

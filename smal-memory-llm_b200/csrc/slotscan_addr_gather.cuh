@@ -76,6 +76,13 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
     __shared__ float s_S[GA_WARPS][GATHER_ROWS];
     __shared__ float s_red[2][GA_WARPS];
     __shared__ __align__(8) uint64_t s_bar;
+    // The chunk's queries and the candidate rows' entries of both D tables come in with the same bulk copies (dynamic
+    // shared memory: GC x DK queries, then 2 x GC x GATHER_ROWS floats): the per-token loop then never waits on global
+    // memory (its loads of q and D were the kernel's first stall, 3.6 cycles per issue).
+    extern __shared__ __align__(128) unsigned char ga_dyn[];
+    Tin* s_q = reinterpret_cast<Tin*>(ga_dyn);
+    float* s_D = reinterpret_cast<float*>(ga_dyn + (size_t)GC * DK * sizeof(Tin));      // [2 tables][GC][GATHER_ROWS]
+    __shared__ float s_gt[GC], s_frt[GC];
     const int N = p.N, T = p.T, H = p.H;
     const int bh = blockIdx.x, c = blockIdx.y, b = bh / H, h = bh % H;    // chunks on grid.y: T / 32 <= 65535
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -95,6 +102,8 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         const size_t ix = ((size_t)b * T + t0 + i) * H + h;
         s_kiv[GATHER_ROWS + i] = (i < tc) ? kiold[ix] : 0.f;
         s_ov[GATHER_ROWS + i] = (i < tc) ? oold[ix] : 0.f;
+        s_gt[i] = (i < tc) ? gate[ix] : 0.f;
+        s_frt[i] = (i < tc) ? (p.fr_per_token ? fr[ix] : fr[0]) : 0.f;
     }
     if (tid == 0) {
         mbar_init(&s_bar, 1);
@@ -105,8 +114,26 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         const int ve = (lane < NR) ? vend[((size_t)bh * nc + c) * GATHER_ROWS + lane] : -1;
         const bool r_in = lane < NR, t_in = lane < tc;
         const unsigned nrow = __popc(__ballot_sync(FULL, r_in)) + __popc(__ballot_sync(FULL, t_in));
-        if (lane == 0) mbar_arrive_expect_tx(&s_bar, nrow * (unsigned)(DK * 4));
+        const unsigned ntok = __popc(__ballot_sync(FULL, t_in));
+        const unsigned drow = (unsigned)(NR * 4);                          // bytes of one token's candidate entries of a D table
+        const bool d_ok = (drow & 15u) == 0u && ((size_t)N * 4 & 15u) == 0u;   // bulk copies want 16-byte pieces
+        if (lane == 0)
+            mbar_arrive_expect_tx(&s_bar, nrow * (unsigned)(DK * 4) + ntok * (unsigned)(DK * sizeof(Tin)) + (d_ok ? ntok * 2u * drow : 0u));
         __syncwarp();
+        if (t_in) {
+            const size_t ixq = ((size_t)b * T + t0 + lane) * H + h;
+            bulk_g2s(s_q + (size_t)lane * DK, q + ixq * DK, DK * sizeof(Tin), &s_bar);
+            const size_t di = ((size_t)bh * T + t0 + lane) * N;
+            if (d_ok) {
+                bulk_g2s(s_D + lane * GATHER_ROWS, Din + di, drow, &s_bar);
+                bulk_g2s(s_D + (GC + lane) * GATHER_ROWS, Din + (size_t)p.B * H * T * N + di, drow, &s_bar);
+            } else {
+                for (int n = 0; n < NR; n++) {
+                    s_D[lane * GATHER_ROWS + n] = Din[di + n];
+                    s_D[(GC + lane) * GATHER_ROWS + n] = Din[(size_t)p.B * H * T * N + di + n];
+                }
+            }
+        }
         if (r_in)
             bulk_g2s(s_rows + lane * DK, ve < 0 ? kfin + ((size_t)bh * N + lane) * DK : kold + (((size_t)b * T + ve) * H + h) * DK,
                      DK * 4, &s_bar);
@@ -159,7 +186,7 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         float4 q4[NF];
         float qq = 0.f;
 #pragma unroll
-        for (int f = 0; f < NF; f++) { q4[f] = ld4(q + ix * DK + (l8 + 8 * f) * 4); qq += dot4(q4[f], q4[f]); }
+        for (int f = 0; f < NF; f++) { q4[f] = ld4(s_q + (size_t)i * DK + (l8 + 8 * f) * 4); qq += dot4(q4[f], q4[f]); }
         qq += __shfl_xor_sync(FULL, qq, 1); qq += __shfl_xor_sync(FULL, qq, 2); qq += __shfl_xor_sync(FULL, qq, 4);
         const float qinv = fminf(rsqrtf(qq), 1e6f);
         for (int base = 0; base <= lim; base += 4) {
@@ -177,7 +204,7 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         const int sl = in ? slot_of(lane) : 0;
         const float ki = in ? s_kiv[sl] : 0.f;
         const float oc = in ? s_ov[sl] : 0.f;
-        const float g = gate_eff(gate[ix], p.hard_gate), frv = p.fr_per_token ? fr[ix] : fr[0];
+        const float g = gate_eff(s_gt[i], p.hard_gate), frv = s_frt[i];
         const float s = in ? temp * qinv * (ki * s_S[warp][lane]) : 0.f;
         const float occ = oc >= eps ? 1.f : 0.f;
         const float z = s - frv * occ;
@@ -186,10 +213,7 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         const unsigned kk = __reduce_max_sync(FULL, ok ? ord_key(z) : 0u);
         const float zmax = __uint_as_float((kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk);
         float dw = 0.f;
-        if (in) {
-            const size_t di = ((size_t)bh * T + t) * N + lane;                 // key part + value part
-            dw = Din[di] + Din[(size_t)p.B * H * T * N + di];
-        }
+        if (in) dw = s_D[i * GATHER_ROWS + lane] + s_D[(GC + i) * GATHER_ROWS + lane];     // key part + value part
         const float e = ok ? __expf(z - zmax) : 0.f;
         float se = e, sd = e * dw;
 #pragma unroll
@@ -222,7 +246,7 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
             const float4 K4 = act ? ld4(s_rows + slot_of(n) * DK + col) : zero4;
             acc.x += cn * K4.x; acc.y += cn * K4.y; acc.z += cn * K4.z; acc.w += cn * K4.w;
         }
-        const float4 qv = act ? ld4(q + ix * DK + col) : zero4;
+        const float4 qv = act ? ld4(s_q + (size_t)i * DK + col) : zero4;
         const float4 qn = make_float4(qv.x * qinv, qv.y * qinv, qv.z * qinv, qv.w * qinv);
         const float pr = warp_sum(dot4(acc, qn));
         if (act) {
