@@ -70,7 +70,8 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
     // The per-token work then reads shared memory only (before: ~11 KB of gathered rows per token out of L2).
     __shared__ __align__(128) float s_rows[2 * GATHER_ROWS * DK];
     __shared__ float s_kiv[2 * GATHER_ROWS], s_ov[2 * GATHER_ROWS];    // 1 / |row| (clamped) and occupancy per slot
-    __shared__ int s_ver[GC][GATHER_ROWS];        // next write of row n as token i sees it
+    __shared__ unsigned char s_slot[GC][GATHER_ROWS];   // slot that holds row n as token i sees it
+    __shared__ int s_lim[GC];                     // highest candidate row of token i
     __shared__ int s_am[GC];
     __shared__ int s_tf[GATHER_ROWS], s_vend[GATHER_ROWS];
     __shared__ float s_S[GA_WARPS][GATHER_ROWS];
@@ -151,8 +152,14 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         int ver = ve;                                                      // per-token versions, walking the chunk backwards
         for (int i = GC - 1; i >= 0; i--) {
             if (s_am[i] == lane) ver = t0 + i;
-            s_ver[i][lane] = ver;
+            s_slot[i][lane] = (unsigned char)((ver >= t0 && ver < t0 + GC) ? GATHER_ROWS + (ver - t0) : lane);
         }
+    }
+    if (warp == 1) {                              // candidate limit of every token of the chunk (rows become candidates in order)
+        const int t = t0 + min(lane, tc - 1);
+        int lim = NR - 1;
+        while (lim > 0 && s_tf[lim] > t) lim--;
+        s_lim[lane] = lim;
     }
     {
         const bool landed = mbar_wait_bounded(&s_bar, 0u);
@@ -174,13 +181,9 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
     for (int i = warp; i < tc; i += GA_WARPS) {
         const int t = t0 + i;
         const size_t ix = ((size_t)b * T + t) * H + h;
-        int lim = NR - 1;
-        while (lim > 0 && s_tf[lim] > t) lim--;
+        const int lim = s_lim[i];
         // slot of row n as this token sees it
-        auto slot_of = [&](int n) {
-            const int ver = s_ver[i][n];
-            return (ver >= t0 && ver < t0 + GC) ? GATHER_ROWS + (ver - t0) : n;
-        };
+        auto slot_of = [&](int n) { return (int)s_slot[i][n]; };
         // ---- scores: 8 lanes per row (lane l of the 8 takes float4 chunks l, l + 8, ...: conflict-free), 4 rows per pass ----
         const int r = lane >> 3, l8 = lane & 7;
         float4 q4[NF];
