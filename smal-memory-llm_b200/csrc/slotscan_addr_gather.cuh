@@ -38,15 +38,21 @@ static __global__ void __launch_bounds__(32) next_write_kernel(const slotscan_pa
     const int bh = blockIdx.x, b = bh / H, h = bh % H, lane = threadIdx.x;
     if (!gather_sequence(tfirst + (size_t)bh * N, N, T)) return;
     const int nc = (T + GC - 1) / GC;
+    __shared__ int s_first[GATHER_ROWS];            // first token of the chunk that writes row n (lane = token, then lane = row)
     int ver = -1;
+    int a_next = ((nc - 1) * GC + lane < T) ? am[((size_t)b * T + (nc - 1) * GC + lane) * H + h] : -1;
     for (int c = nc - 1; c >= 0; c--) {
         vend[((size_t)bh * nc + c) * GATHER_ROWS + lane] = ver;
-        const int t = c * GC + lane;
-        const int a = (t < T) ? am[((size_t)b * T + t) * H + h] : -1;
-        for (int i = GC - 1; i >= 0; i--) {
-            const int ai = __shfl_sync(FULL, a, i);
-            if (ai == lane) ver = c * GC + i;
-        }
+        const int a = a_next;
+        if (c > 0) a_next = am[((size_t)b * T + (c - 1) * GC + lane) * H + h];     // the next chunk's addresses, in flight
+        s_first[lane] = -1;
+        __syncwarp();
+        const unsigned same = __match_any_sync(FULL, a);                       // the tokens of the chunk with this address
+        if (a >= 0 && a < GATHER_ROWS && lane == __ffs((int)same) - 1) s_first[a] = lane;
+        __syncwarp();
+        const int f = s_first[lane];
+        if (f >= 0) ver = c * GC + f;
+        __syncwarp();
     }
 }
 
