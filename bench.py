@@ -498,7 +498,7 @@ def run_gpu(args, rank, local_rank, world):
         # Snapshot rows >= 64 are zero-filled by a kernel on a second stream while the address scan runs (they are zero
         # for every sequence whose scan stays within 64 rows); the replay writes the rest.  Keys and values share one
         # launch when dk == dv.
-        zf = 64 if N > 64 else N
+        zf = min(N, 256 // max(DK // 8, 1))          # rows of the first row tile: everything above is zero-filled beside the scan
         kb_bytes = {"addr_fwd": 2 * DK * 2 + 8, "zero_fill": (N - zf) * (DK + DV) * 2 / G,
                     "replay_rows_k": zf * (DK + DV) * 2 / G + DV * 2, "replay_rows_v": 0,
                     "rows_bwd_k": (DK + DV) * 2 + N * (DK + DV) * 2 / G + (DK + DV) * 2, "rows_bwd_v": 0,

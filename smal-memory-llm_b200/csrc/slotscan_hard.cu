@@ -95,20 +95,20 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
                            const float* fr, const float* temp, void* kbuf, void* vbuf, const slotscan_log& L,
                            const slotscan_fwd_extra& ex, cudaStream_t st) {
     cudaError_t e;
-    // While the address scan runs (sequential, almost no memory traffic; on a second stream, see below) the snapshot
-    // rows its first pass cannot reach are zero-filled: rows >= AF_NCAP1 (rounded up to the row tiles of the replay) are zero in every
-    // snapshot of every sequence that finishes in that pass.  The replay, ordered after both, writes the rest and
-    // rewrites those tiles for the sequences that did need them.  Not with a carried-in state (its rows may be anywhere).
+    // While the address scan runs (sequential, almost no memory traffic; on a second stream, see below) every snapshot
+    // row above the first row tile is zero-filled: rows are taken in index order, so a tile that never becomes a
+    // candidate is zero in every snapshot, and with few rows in use that is most of the snapshot bytes.  The replay,
+    // ordered after both, writes the first tile and rewrites every tile that did become a candidate (tile_active) on top
+    // of the zeros; the others it leaves alone.  Not with a carried-in state (its rows may be anywhere).
     int zk = p.N, zv = p.N;
     cudaEvent_t joined = nullptr, fork = nullptr;
     cudaStream_t side = nullptr;
-    if (p.N > AF_NCAP1 && ex.K0 == nullptr) {
+    if (p.N > min(replay_tile_rows(p.DK), replay_tile_rows(p.DV)) && ex.K0 == nullptr) {
         side = side_stream(st);
         if (side != nullptr && cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess &&
             cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) == cudaSuccess) {
-            auto up = [](int row, int tile) { return (row + tile - 1) / tile * tile; };
-            zk = min(up(AF_NCAP1, replay_tile_rows(p.DK)), p.N);
-            zv = min(up(AF_NCAP1, replay_tile_rows(p.DV)), p.N);
+            zk = min(replay_tile_rows(p.DK), p.N);
+            zv = min(replay_tile_rows(p.DV), p.N);
             if ((e = cudaEventRecord(fork, st)) != cudaSuccess) { cudaEventDestroy(fork); cudaEventDestroy(joined); return e; }
         } else {
             if (fork != nullptr) cudaEventDestroy(fork);
