@@ -270,8 +270,8 @@ def run_reference(args, rank, world):
 # (each taken at B = 8 sequences; traffic is proportional to the batch, so a launch over B sequences moves B / 8 of it).
 # A kernel that changed since its capture is taken out of this table until it is captured again.
 NCU_TRAFFIC_B8 = {
-    "addr_fwd||zero_fill": (25.6e6 + 342.7e6, "profiles/addr_fwd_128_bf16_small_case.md + profiles/zero_rows_bulk_128_bf16_small_case.md"),
-    "replay_rows_k": (25.6e6 + 203.3e6, "profiles/replay_rows_128_bf16_small_case.md"),
+    "addr_fwd||zero_fill": (25.6e6 + 493.8e6, "profiles/addr_fwd_128_bf16_small_case.md + profiles/zero_rows_bulk_128_bf16_small_case.md"),
+    "replay_rows_k": (25.6e6 + 52.3e6, "profiles/replay_rows_128_bf16_small_case.md"),
     "rows_bwd_k": (107.8e6 + 15.7e6, "profiles/rows_bwd_128_bf16_small_case.md"),
     "addr_bwd": (52.43e6 + 1.18e6, "profiles/addr_bwd_gather_128_bf16_small_case.md"),
 }
