@@ -122,11 +122,17 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
         return (p.in_dtype == SLOTSCAN_F32) ? run_addr_fwd_f32(p, q ? q : k, k, gate, fr, temp, L, S0, s)
                                             : run_addr_fwd_bf16(p, q ? q : k, k, gate, fr, temp, L, S0, s);
     };
+    const ReplayPtrs rk{k, ex.K0, kbuf, ex.no_undo_log ? nullptr : L.kold, L.kfin, ex.kinv, ex.valid, zk};
+    const ReplayPtrs rv{v, ex.V0, vbuf, ex.no_undo_log ? nullptr : L.vold, L.vfin, nullptr, nullptr, zv};
     if (joined != nullptr) {
         // The zero-fill goes on the caller's stream and the SCAN on the second stream, behind `fork`: the fill's CTAs (one
         // per SM) are then placed first, on an idle machine, evenly, and three CTAs of the scan still fit beside each.
         // The other way round the scan's 384 CTAs load the 148 SMs unevenly (3 on some, 2 on others) and the block
         // scheduler packs every fill CTA onto the emptier SMs: the fill then runs at half the write bandwidth.
+        // The replay of the row tiles BELOW the fill (the busy ones) follows the scan on the second stream and does not
+        // wait for the fill; the tiles above it are replayed after both.
+        const bool merged = p.DK == p.DV;                    // keys and values in one launch: their busy tiles overlap
+        const int tz = merged ? zk / replay_tile_rows(p.DK) : 0;    // first row tile that the fill covers
         cudaError_t e2;
         {
             ProfScope ps(K_ZERO_FILL, st);
@@ -134,28 +140,34 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
         }
         if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(side, fork, 0);
         if (e2 == cudaSuccess) e2 = scan_on(side);
+        if (e2 == cudaSuccess && tz > 0) {
+            ProfScope ps(K_REPLAY_K, side);
+            e2 = run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, 0, tz, side);
+        }
         if (e2 == cudaSuccess) e2 = cudaEventRecord(joined, side);
-        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);          // the replay comes after both
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);          // the rest of the replay comes after both
         cudaEventDestroy(fork);
         cudaEventDestroy(joined);
-        e = e2;
+        if (e2 != cudaSuccess) return e2;
+        if (merged) {
+            ProfScope ps(K_REPLAY_V, st);
+            return run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, tz, -1, st);
+        }
     } else {
         e = scan_on(st);
-    }
-    if (e != cudaSuccess) return e;
-    const ReplayPtrs rk{k, ex.K0, kbuf, ex.no_undo_log ? nullptr : L.kold, L.kfin, ex.kinv, ex.valid, zk};
-    const ReplayPtrs rv{v, ex.V0, vbuf, ex.no_undo_log ? nullptr : L.vold, L.vfin, nullptr, nullptr, zv};
-    if (p.DK == p.DV) {                                     // keys and values in one launch: their busy tiles overlap
-        ProfScope ps(K_REPLAY_K, st);
-        return run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, st);
+        if (e != cudaSuccess) return e;
+        if (p.DK == p.DV) {
+            ProfScope ps(K_REPLAY_K, st);
+            return run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, 0, -1, st);
+        }
     }
     {
         ProfScope ps(K_REPLAY_K, st);
-        e = run_replay(p, p.DK, 1, rk, rk, gate, L.addr, L.tfirst, st);
+        e = run_replay(p, p.DK, 1, rk, rk, gate, L.addr, L.tfirst, 0, -1, st);
     }
     if (e != cudaSuccess) return e;
     ProfScope ps(K_REPLAY_V, st);
-    return run_replay(p, p.DV, 1, rv, rv, gate, L.addr, L.tfirst, st);
+    return run_replay(p, p.DV, 1, rv, rv, gate, L.addr, L.tfirst, 0, -1, st);
 }
 
 static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* q, const void* v, const float* gate,

@@ -38,8 +38,9 @@ constexpr int GATHER_ROWS_MAX = 32;
 // zero_from: rows >= zero_from were zero-filled ahead by run_zero_rows (N = none).
 struct ReplayPtrs { const void* x; const float* x0; void* xbuf; float* xold; float* xfin; float* kinv; uint8_t* valid; int zero_from; };
 // ntensors = 2 runs keys and values in one launch (needs DK == DV), 1 runs r0 only
+// row tiles [tile_lo, tile_hi) of replay_tile_rows(D) rows each; tile_hi < 0: up to the last one
 cudaError_t run_replay(const slotscan_params& p, int D, int ntensors, const ReplayPtrs& r0, const ReplayPtrs& r1,
-                       const float* gate, const int* am, const int* tfirst, cudaStream_t st);
+                       const float* gate, const int* am, const int* tfirst, int tile_lo, int tile_hi, cudaStream_t st);
 int replay_tile_rows(int D);
 int replay_status();
 // zero-fill of rows [zk, N) of every key snapshot (+ kinv = 1e6, valid = 0 when given) and [zv, N) of every value snapshot

@@ -8,15 +8,18 @@ namespace slotscan {
 
 template <int D, typename Tin, typename Tsn>
 static cudaError_t replay_one(const slotscan_params& p, int ntensors, const ReplayPtrs& r0, const ReplayPtrs& r1,
-                              const float* gate, const int* am, const int* tfirst, cudaStream_t st) {
+                              const float* gate, const int* am, const int* tfirst, int tile_lo, int tile_hi, cudaStream_t st) {
     constexpr int RPB = ROW_THREADS / (D / 8);
-    dim3 grid(p.B * p.H, (p.N + RPB - 1) / RPB, ntensors);
+    const int ntiles = (p.N + RPB - 1) / RPB;
+    if (tile_hi < 0 || tile_hi > ntiles) tile_hi = ntiles;
+    if (tile_lo >= tile_hi) return cudaSuccess;
+    dim3 grid(p.B * p.H, tile_hi - tile_lo, ntensors);
     const ReplayArgs<Tin, Tsn> a0{(const Tin*)r0.x, r0.x0, (Tsn*)r0.xbuf, r0.xold, r0.xfin, r0.kinv, r0.valid, r0.zero_from};
     const ReplayArgs<Tin, Tsn> a1{(const Tin*)r1.x, r1.x0, (Tsn*)r1.xbuf, r1.xold, r1.xfin, r1.kinv, r1.valid, r1.zero_from};
     if (r0.kinv != nullptr || r1.kinv != nullptr)
-        replay_rows_kernel<D, Tin, Tsn, true><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst);
+        replay_rows_kernel<D, Tin, Tsn, true><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
     else
-        replay_rows_kernel<D, Tin, Tsn, false><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst);
+        replay_rows_kernel<D, Tin, Tsn, false><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
     return cudaGetLastError();
 }
 
@@ -29,18 +32,19 @@ static cudaError_t replay_one(const slotscan_params& p, int ntensors, const Repl
 
 template <int D>
 static cudaError_t replay_d(const slotscan_params& p, int nt, const ReplayPtrs& r0, const ReplayPtrs& r1, const float* gate,
-                            const int* am, const int* tfirst, cudaStream_t st) {
+                            const int* am, const int* tfirst, int tlo, int thi, cudaStream_t st) {
     typedef __nv_bfloat16 bf;
-    ROWS_TYPES(return (replay_one<D, float, float>(p, nt, r0, r1, gate, am, tfirst, st)),
-               return (replay_one<D, float, bf>(p, nt, r0, r1, gate, am, tfirst, st)),
-               return (replay_one<D, bf, float>(p, nt, r0, r1, gate, am, tfirst, st)),
-               return (replay_one<D, bf, bf>(p, nt, r0, r1, gate, am, tfirst, st)))
+    ROWS_TYPES(return (replay_one<D, float, float>(p, nt, r0, r1, gate, am, tfirst, tlo, thi, st)),
+               return (replay_one<D, float, bf>(p, nt, r0, r1, gate, am, tfirst, tlo, thi, st)),
+               return (replay_one<D, bf, float>(p, nt, r0, r1, gate, am, tfirst, tlo, thi, st)),
+               return (replay_one<D, bf, bf>(p, nt, r0, r1, gate, am, tfirst, tlo, thi, st)))
 }
 
+// row tiles [tile_lo, tile_hi) of every (sequence, head); tile_hi < 0: up to the last one
 cudaError_t run_replay(const slotscan_params& p, int D, int ntensors, const ReplayPtrs& r0, const ReplayPtrs& r1,
-                       const float* gate, const int* am, const int* tfirst, cudaStream_t st) {
+                       const float* gate, const int* am, const int* tfirst, int tile_lo, int tile_hi, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
-    SLOTSCAN_DISPATCH_D(D, e = (replay_d<DD>(p, ntensors, r0, r1, gate, am, tfirst, st)));
+    SLOTSCAN_DISPATCH_D(D, e = (replay_d<DD>(p, ntensors, r0, r1, gate, am, tfirst, tile_lo, tile_hi, st)));
     return e;
 }
 

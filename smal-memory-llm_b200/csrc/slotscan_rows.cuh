@@ -70,7 +70,7 @@ struct ReplayArgs {
 template <int D, typename Tin, typename Tsn, bool NORM>
 __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     const slotscan_params p, const ReplayArgs<Tin, Tsn> a0, const ReplayArgs<Tin, Tsn> a1,
-    const float* __restrict__ gate, const int* __restrict__ am, const int* __restrict__ tfirst) {
+    const float* __restrict__ gate, const int* __restrict__ am, const int* __restrict__ tfirst, const int tile0) {
     const ReplayArgs<Tin, Tsn>& A = blockIdx.z ? a1 : a0;
     const Tin* __restrict__ x = A.x;
     const float* __restrict__ x0 = A.x0;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     const int NB = (T + G - 1) / G;
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = tid / LPR, c = tid % LPR, row0 = blockIdx.y * RPB, n = row0 + r;
+    const int r = tid / LPR, c = tid % LPR, row0 = ((int)blockIdx.y + tile0) * RPB, n = row0 + r;   // this launch covers the row tiles from tile0 on
     const bool live = n < N;
     float X[8];
 #pragma unroll
