@@ -56,6 +56,38 @@ __device__ __forceinline__ float fq_one(float x, const FqScale& g) {
     return round_to(__fadd_rn(x, diff), Tin());
 }
 
+// bf16 input, two elements at a time.  The group's extreme a is a bf16 value, so s = a / half (half a power of two)
+// is exact with 8 significant bits, and k * s (|k| <= 128) and (f + 0.5) * s are exact in float.  Then
+// floor(x / s) = k - (k * s > x) with k = rint(x * (1 / s)), with no division and no near-integer case left over, and
+// the straight-through form x + (q - x), each step rounded to bf16, is two packed bf16 operations (a bf16 sum or
+// difference of two bf16 values rounds once; the float detour of the reference rounds a value that is either exact in
+// float or within 2^-16 of one operand, so both land on the same bf16).  Groups whose scale is clamped or denormal
+// take fq_one.
+__device__ __forceinline__ unsigned fq_pair_bf16(const unsigned xw, const FqScale& g) {
+    const __nv_bfloat162 x2 = *reinterpret_cast<const __nv_bfloat162*>(&xw);
+    const float2 x = __bfloat1622float2(x2);
+    __nv_bfloat162 r2;
+    if (g.a == 0.f) return 0u;                           // an all-zero group stays zero (x + (0 - x) = +0)
+    if (g.plain) {
+        const float k0 = rintf(x.x * g.rs), k1 = rintf(x.y * g.rs);
+        float f0 = k0 - (__fmul_rn(k0, g.s) > x.x ? 1.f : 0.f), f1 = k1 - (__fmul_rn(k1, g.s) > x.y ? 1.f : 0.f);
+        f0 = fminf(fmaxf(f0, -g.half), g.half - 1.f);
+        f1 = fminf(fmaxf(f1, -g.half), g.half - 1.f);
+        const __nv_bfloat162 qd = __floats2bfloat162_rn(__fmul_rn(f0 + 0.5f, g.s), __fmul_rn(f1 + 0.5f, g.s));
+        r2 = __hadd2(x2, __hsub2(qd, x2));
+    } else {
+        r2 = __floats2bfloat162_rn(fq_one<__nv_bfloat16>(x.x, g), fq_one<__nv_bfloat16>(x.y, g));
+    }
+    return *reinterpret_cast<const unsigned*>(&r2);
+}
+__device__ __forceinline__ float absmax_pair(const unsigned a, const unsigned b) {     // max |.| of four bf16 values
+    const unsigned m = 0x7fff7fffu;
+    const unsigned ua = a & m, ub = b & m;
+    const __nv_bfloat162 h = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&ua), *reinterpret_cast<const __nv_bfloat162*>(&ub));
+    const float2 f = __bfloat1622float2(h);
+    return fmaxf(f.x, f.y);
+}
+
 template <int D, typename Tin, typename Tout>
 __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
                                                                      float* __restrict__ kinv,
@@ -64,10 +96,56 @@ __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* 
     constexpr int LPR = D / 8, RPB = EP_THREADS / LPR;
     const int r = threadIdx.x / LPR, c = threadIdx.x % LPR;
     const float half = bits > 0 ? (float)(1 << (bits - 1)) : 0.f;
-    for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += (long long)gridDim.x * RPB) {
+    const long long stride = (long long)gridDim.x * RPB;
+    uint4 ahead = make_uint4(0, 0, 0, 0);                // the next row of this lane, in flight while this one is worked on
+    if constexpr (sizeof(Tin) == 2) {
+        const long long first = (long long)blockIdx.x * RPB + r;
+        if (bits > 0 && first < rows) ahead = *reinterpret_cast<const uint4*>(x + first * D + c * 8);
+    }
+    for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += stride) {
         const long long row = row0 + r;
         const bool live = row < rows;                    // dead lanes keep running the shuffles on zeros
         float v[8];
+        if constexpr (sizeof(Tin) == 2) {
+            if (bits > 0) {                               // midrise quantiser on packed bf16 pairs
+                const uint4 u = ahead;
+                ahead = row + stride < rows ? *reinterpret_cast<const uint4*>(x + (row + stride) * D + c * 8) : make_uint4(0, 0, 0, 0);
+                unsigned w[4] = {u.x, u.y, u.z, u.w};
+                float a0 = absmax_pair(w[0], w[1]), a1 = absmax_pair(w[2], w[3]);
+                if (group >= 8) {
+                    a0 = fmaxf(a0, a1);
+                    for (int off = 1; off < group / 8; off <<= 1) a0 = fmaxf(a0, __shfl_xor_sync(FULL, a0, off));
+                    a1 = a0;
+                }
+                const FqScale g0 = fq_scale(a0, half), g1 = group >= 8 ? g0 : fq_scale(a1, half);
+                w[0] = fq_pair_bf16(w[0], g0); w[1] = fq_pair_bf16(w[1], g0);
+                w[2] = fq_pair_bf16(w[2], g1); w[3] = fq_pair_bf16(w[3], g1);
+                if (y != nullptr && live) {
+                    if constexpr (sizeof(Tout) == 2) *reinterpret_cast<uint4*>(y + row * D + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                if (kinv != nullptr || sizeof(Tout) == 4) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        v[2 * i] = __uint_as_float(w[i] << 16);
+                        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+                    }
+                    if constexpr (sizeof(Tout) == 4) {
+                        if (y != nullptr && live) st8(y + row * D + c * 8, v);
+                    }
+                }
+                if (kinv != nullptr) {
+                    float nsq = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) nsq = fmaf(v[j], v[j], nsq);
+                    nsq = group_sum<LPR>(nsq);
+                    if (live && c == 0) {
+                        kinv[row] = rsqrtf(fmaxf(nsq, 1e-12f));
+                        valid[row] = nsq > 1e-12f ? 1 : 0;
+                    }
+                }
+                continue;
+            }
+        }
         if (live) ld8(v, x + row * D + c * 8);
         else {
 #pragma unroll
