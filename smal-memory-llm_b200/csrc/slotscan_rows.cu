@@ -16,10 +16,12 @@ static cudaError_t replay_one(const slotscan_params& p, int ntensors, const Repl
     dim3 grid(p.B * p.H, tile_hi - tile_lo, ntensors);
     const ReplayArgs<Tin, Tsn> a0{(const Tin*)r0.x, r0.x0, (Tsn*)r0.xbuf, r0.xold, r0.xfin, r0.kinv, r0.valid, r0.zero_from};
     const ReplayArgs<Tin, Tsn> a1{(const Tin*)r1.x, r1.x0, (Tsn*)r1.xbuf, r1.xold, r1.xfin, r1.kinv, r1.valid, r1.zero_from};
+    constexpr int EPL = D >= 128 ? 16 : 8;                 // elements per lane: half-size CTAs for the widest rows
+    constexpr int THREADS = ROW_THREADS * 8 / EPL;
     if (r0.kinv != nullptr || r1.kinv != nullptr)
-        replay_rows_kernel<D, Tin, Tsn, true><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
+        replay_rows_kernel<D, Tin, Tsn, true, EPL><<<grid, THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
     else
-        replay_rows_kernel<D, Tin, Tsn, false><<<grid, ROW_THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
+        replay_rows_kernel<D, Tin, Tsn, false, EPL><<<grid, THREADS, 0, st>>>(p, a0, a1, gate, am, tfirst, tile_lo);
     return cudaGetLastError();
 }
 
@@ -95,9 +97,9 @@ cudaError_t run_zero_rows(const slotscan_params& p, void* kbuf, int zk, void* vb
 }
 
 void attrs_rows(slotscan_kernel_attr* out, int cap, int& n) {
-    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, false>);
-    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16,kinv>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, true>);
-    fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float, false>);
+    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, false, 16>);
+    fill_attr(out, cap, n, "replay_rows<128,bf16,bf16,kinv>", replay_rows_kernel<128, __nv_bfloat16, __nv_bfloat16, true, 16>);
+    fill_attr(out, cap, n, "replay_rows<128,f32,f32>", replay_rows_kernel<128, float, float, false, 16>);
 }
 
 }  // namespace slotscan

@@ -34,11 +34,11 @@ __device__ __forceinline__ bool tile_active(const int* tfirst_bh, int n, bool li
 // ======================================================================================================
 // kinv / valid of a row from its float32 state: rsqrt(max(|X|^2, 1e-12)) and [|X|^2 > 1e-12]  [memlm_sh.py:474-475]
 // The rows of one warp walk their events independently, so the sum runs over the row's own LPR lanes only (`gmask`).
-template <int LPR>
+template <int LPR, int EPL>
 __device__ __forceinline__ float row_nsq(const float* X, unsigned gmask) {
     float a = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; j++) a = fmaf(X[j], X[j], a);
+    for (int j = 0; j < EPL; j++) a = fmaf(X[j], X[j], a);
 #pragma unroll
     for (int off = LPR / 2; off > 0; off >>= 1) a += __shfl_xor_sync(gmask, a, off);
     return a;
@@ -67,8 +67,11 @@ struct ReplayArgs {
 };
 
 // NORM: kinv / valid may be asked for (checked per tensor at run time).
-template <int D, typename Tin, typename Tsn, bool NORM>
-__global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
+// EPL: elements per lane, 8 or 16.  With 16 a lane holds two pieces of 8 columns half a row apart (every load and store
+// of a row group stays one contiguous run of 16-byte pieces) and a CTA has half the threads: the busy tiles of a large
+// batch (one CTA per sequence, head and tensor) then all fit on the machine at once instead of in two waves.
+template <int D, typename Tin, typename Tsn, bool NORM, int EPL>
+__global__ void __launch_bounds__(ROW_THREADS * 8 / EPL, EPL == 16 ? 6 : 1) replay_rows_kernel(
     const slotscan_params p, const ReplayArgs<Tin, Tsn> a0, const ReplayArgs<Tin, Tsn> a1,
     const float* __restrict__ gate, const int* __restrict__ am, const int* __restrict__ tfirst, const int tile0) {
     const ReplayArgs<Tin, Tsn>& A = blockIdx.z ? a1 : a0;
@@ -80,7 +83,17 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     float* __restrict__ kinv_out = A.kinv;
     uint8_t* __restrict__ valid_out = A.valid;
     const bool norm = NORM && kinv_out != nullptr;
-    constexpr int LPR = D / 8, RPB = ROW_THREADS / LPR, RPW = 32 / LPR;
+    constexpr int NPC = EPL / 8, PS = D / NPC;                       // pieces of 8 columns per lane, columns between them
+    constexpr int LPR = PS / 8, RPB = ROW_THREADS / (D / 8), RPW = 32 / LPR;
+    static_assert(LPR >= 1 && RPB * LPR >= RC, "at least one lane per row and one thread per staged token");
+    auto ldE = [](float* d, const auto* s) {
+#pragma unroll
+        for (int q = 0; q < NPC; q++) ld8(d + 8 * q, s + q * PS);
+    };
+    auto stE = [](auto* d, const float* s) {
+#pragma unroll
+        for (int q = 0; q < NPC; q++) st8(d + q * PS, s + 8 * q);
+    };
     __shared__ float s_g[2][RC];                                     // gates of the chunk in work / the next one
     __shared__ int s_am[2][RC];                                      // addressed row - row0 (negative: not in this tile)
     __shared__ __align__(128) Tin s_x[2][RC * D];                    // token vectors, two stages (bulk async copies)
@@ -92,9 +105,9 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = tid / LPR, c = tid % LPR, row0 = ((int)blockIdx.y + tile0) * RPB, n = row0 + r;   // this launch covers the row tiles from tile0 on
     const bool live = n < N;
-    float X[8];
+    float X[EPL];
 #pragma unroll
-    for (int j = 0; j < 8; j++) X[j] = 0.f;
+    for (int j = 0; j < EPL; j++) X[j] = 0.f;
     const size_t snap_stride = (size_t)H * N * D;                   // between consecutive snapshots of one sequence
     Tsn* snap = xbuf + (((size_t)b * NB) * H + h) * N * D + (size_t)n * D + c * 8;
     // kinv / valid of snapshot j of this row live at norm_base + j * norm_stride (one lane per row writes them)
@@ -103,9 +116,9 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
 
     if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) {
         if (live) {                                                  // never a candidate: the row stays zero
-            st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+            stE(xfin + ((size_t)bh * N + n) * D + c * 8, X);
             if (row0 < A.zero_from) {                                // (tiles at or above zero_from were zero-filled ahead)
-                for (int j = 0; j < NB; j++) st8(snap + j * snap_stride, X);
+                for (int j = 0; j < NB; j++) stE(snap + j * snap_stride, X);
                 if (norm && c == 0) {
                     for (int j = 0; j < NB; j++) { kinv_out[norm_ix + j * norm_stride] = 1e6f; valid_out[norm_ix + j * norm_stride] = 0; }
                 }
@@ -113,7 +126,7 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
         }
         return;
     }
-    if (x0 != nullptr && live) ld8(X, x0 + ((size_t)bh * N + n) * D + c * 8);   // state carried in from the preceding chunk
+    if (x0 != nullptr && live) ldE(X, x0 + ((size_t)bh * N + n) * D + c * 8);   // state carried in from the preceding chunk
     const unsigned gmask = row_group_mask<LPR>();
     // Chunks of RC tokens through a two-stage ring: while the rows walk chunk k, the token vectors of chunk k + 1 are
     // being copied (bulk async, one mbarrier per stage) and the gates / addresses of chunk k + 2 are in flight.
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
             const int tlast = t0 + min(ih, tc - 1);
             if (norm) {
                 if (tsnap <= tlast) {                                // the state is the same for every snapshot of this stretch
-                    const float nsq = row_nsq<LPR>(X, gmask);
+                    const float nsq = row_nsq<LPR, EPL>(X, gmask);
                     if (c == 0) {
                         const float ki = rsqrtf(fmaxf(nsq, 1e-12f));
                         const uint8_t va = nsq > 1e-12f ? 1 : 0;
@@ -197,22 +210,22 @@ __global__ void __launch_bounds__(ROW_THREADS) replay_rows_kernel(
                 }
             }
             for (; tsnap <= tlast; tsnap += G) {                     // pre-write copies
-                st8(snap, X);
+                stE(snap, X);
                 snap += snap_stride; norm_ix += norm_stride;
             }
             if (ih >= tc) break;
             const size_t ix = ((size_t)b * T + t0 + ih) * H + h;
             const float g = sg[ih], omw = 1.f - g;
-            float xv[8];
-            ld8(xv, sx + ih * D + c * 8);
-            if (xold != nullptr) st8(xold + ix * D + c * 8, X);
+            float xv[EPL];
+            ldE(xv, sx + ih * D + c * 8);
+            if (xold != nullptr) stE(xold + ix * D + c * 8, X);
 #pragma unroll
-            for (int j = 0; j < 8; j++) X[j] = blend(X[j], xv[j], g, omw);
+            for (int j = 0; j < EPL; j++) X[j] = blend(X[j], xv[j], g, omw);
             i = ih + 1;
             if (i >= tc) break;
         }
     }
-    if (live) st8(xfin + ((size_t)bh * N + n) * D + c * 8, X);
+    if (live) stE(xfin + ((size_t)bh * N + n) * D + c * 8, X);
 }
 
 // ======================================================================================================
