@@ -42,6 +42,18 @@ __device__ __forceinline__ FqScale fq_scale(float a, float half) {
     g.plain = a > 1e-20f;                    // s = a / half exactly: not clamped, not denormal
     return g;
 }
+// The same for the packed bf16 path: a * (1 / half) is the same float as a / half (half is a power of two), and 1 / s
+// only has to place k within one of the quotient, so the approximate reciprocal will do; a group that is not `plain`
+// goes through fq_one and gets the exact one.
+__device__ __forceinline__ FqScale fq_scale_packed(float a, float half, float inv_half) {
+    FqScale g;
+    g.a = a; g.half = half;
+    g.s = fmaxf(__fmul_rn(a, inv_half), 1e-30f);
+    g.plain = a > 1e-20f;
+    if (g.plain) asm("rcp.approx.f32 %0, %1;" : "=f"(g.rs) : "f"(g.s));     // (no .ftz: 1 / s may be subnormal for huge rows)
+    else g.rs = __frcp_rn(g.s);
+    return g;
+}
 template <typename Tin>
 __device__ __forceinline__ float fq_one(float x, const FqScale& g) {
     float f;
@@ -56,24 +68,29 @@ __device__ __forceinline__ float fq_one(float x, const FqScale& g) {
     return round_to(__fadd_rn(x, diff), Tin());
 }
 
-// bf16 input, two elements at a time.  The group's extreme a is a bf16 value, so s = a / half (half a power of two)
-// is exact with 8 significant bits, and k * s (|k| <= 128) and (f + 0.5) * s are exact in float.  Then
-// floor(x / s) = k - (k * s > x) with k = rint(x * (1 / s)), with no division and no near-integer case left over, and
-// the straight-through form x + (q - x), each step rounded to bf16, is two packed bf16 operations (a bf16 sum or
-// difference of two bf16 values rounds once; the float detour of the reference rounds a value that is either exact in
-// float or within 2^-16 of one operand, so both land on the same bf16).  Groups whose scale is clamped or denormal
-// take fq_one.
+// bf16 input, two elements at a time, in packed bf16 arithmetic wherever that is exact.  The group's extreme a is a
+// bf16 value, so s = a / half (half a power of two) is a bf16 value too.  With k = rint(x * (1 / s)) (|k| <= 128, a
+// bf16 value; one fused multiply-add against 1.5 * 2^23 rounds it)
+//     floor(x / s) = k - [k * s > x],   and the sign of k * s - x survives the single rounding of a bf16 fma;
+//     (f + 0.5) has at most 8 significant bits, and the bf16 product (f + 0.5) * s rounds the exact product once, as
+//     the reference's float product (exact, 17 bits) followed by its cast does;
+//     x + (q - x), each step rounded to bf16: a bf16 sum or difference of two bf16 values rounds once, and the float
+//     detour of the reference rounds a value that is either exact in float or within 2^-16 of one operand, so both
+//     land on the same bf16.
+// No division and no near-integer case is left over.  The lower clamp never binds (x >= -a gives k * s >= x at
+// k = -half).  Groups whose scale is clamped or denormal take fq_one.
 __device__ __forceinline__ unsigned fq_pair_bf16(const unsigned xw, const FqScale& g) {
     const __nv_bfloat162 x2 = *reinterpret_cast<const __nv_bfloat162*>(&xw);
     const float2 x = __bfloat1622float2(x2);
     __nv_bfloat162 r2;
     if (g.a == 0.f) return 0u;                           // an all-zero group stays zero (x + (0 - x) = +0)
     if (g.plain) {
-        const float k0 = rintf(x.x * g.rs), k1 = rintf(x.y * g.rs);
-        float f0 = k0 - (__fmul_rn(k0, g.s) > x.x ? 1.f : 0.f), f1 = k1 - (__fmul_rn(k1, g.s) > x.y ? 1.f : 0.f);
-        f0 = fminf(fmaxf(f0, -g.half), g.half - 1.f);
-        f1 = fminf(fmaxf(f1, -g.half), g.half - 1.f);
-        const __nv_bfloat162 qd = __floats2bfloat162_rn(__fmul_rn(f0 + 0.5f, g.s), __fmul_rn(f1 + 0.5f, g.s));
+        const float MAGIC = 12582912.f;                  // 1.5 * 2^23: adding it rounds to an integer
+        const float k0 = __fadd_rn(__fmaf_rn(x.x, g.rs, MAGIC), -MAGIC), k1 = __fadd_rn(__fmaf_rn(x.y, g.rs, MAGIC), -MAGIC);
+        const __nv_bfloat162 k2 = __floats2bfloat162_rn(k0, k1), s2 = __float2bfloat162_rn(g.s);
+        const __nv_bfloat162 over = __hgt2(__hfma2(k2, s2, __hneg2(x2)), __float2bfloat162_rn(0.f));   // 1.0 where k * s > x
+        const __nv_bfloat162 f2 = __hmin2(__hsub2(k2, over), __float2bfloat162_rn(g.half - 1.f));
+        const __nv_bfloat162 qd = __hmul2(__hadd2(f2, __float2bfloat162_rn(0.5f)), s2);
         r2 = __hadd2(x2, __hsub2(qd, x2));
     } else {
         r2 = __floats2bfloat162_rn(fq_one<__nv_bfloat16>(x.x, g), fq_one<__nv_bfloat16>(x.y, g));
@@ -88,26 +105,29 @@ __device__ __forceinline__ float absmax_pair(const unsigned a, const unsigned b)
     return fmaxf(f.x, f.y);
 }
 
-template <int D, typename Tin, typename Tout>
-__global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
+// PACKED: the midrise quantiser on bf16 input (bits > 0), a kernel of its own so that its registers do not cost the
+// plain pass its eight resident CTAs per SM.
+template <int D, typename Tin, typename Tout, bool PACKED>
+__global__ void __launch_bounds__(EP_THREADS, PACKED ? 6 : 1) writer_epilogue_kernel(const Tin* __restrict__ x, Tout* __restrict__ y,
                                                                      float* __restrict__ kinv,
                                                                      uint8_t* __restrict__ valid, const long long rows,
                                                                      const int bits, const int group) {
     constexpr int LPR = D / 8, RPB = EP_THREADS / LPR;
     const int r = threadIdx.x / LPR, c = threadIdx.x % LPR;
     const float half = bits > 0 ? (float)(1 << (bits - 1)) : 0.f;
+    const float inv_half = bits > 0 ? 1.f / half : 0.f;
     const long long stride = (long long)gridDim.x * RPB;
     uint4 ahead = make_uint4(0, 0, 0, 0);                // the next row of this lane, in flight while this one is worked on
-    if constexpr (sizeof(Tin) == 2) {
+    if constexpr (PACKED) {
         const long long first = (long long)blockIdx.x * RPB + r;
-        if (bits > 0 && first < rows) ahead = *reinterpret_cast<const uint4*>(x + first * D + c * 8);
+        if (first < rows) ahead = *reinterpret_cast<const uint4*>(x + first * D + c * 8);
     }
     for (long long row0 = (long long)blockIdx.x * RPB; row0 < rows; row0 += stride) {
         const long long row = row0 + r;
         const bool live = row < rows;                    // dead lanes keep running the shuffles on zeros
         float v[8];
-        if constexpr (sizeof(Tin) == 2) {
-            if (bits > 0) {                               // midrise quantiser on packed bf16 pairs
+        if constexpr (PACKED) {
+            {                                             // midrise quantiser on packed bf16 pairs
                 const uint4 u = ahead;
                 ahead = row + stride < rows ? *reinterpret_cast<const uint4*>(x + (row + stride) * D + c * 8) : make_uint4(0, 0, 0, 0);
                 unsigned w[4] = {u.x, u.y, u.z, u.w};
@@ -117,7 +137,7 @@ __global__ void __launch_bounds__(EP_THREADS) writer_epilogue_kernel(const Tin* 
                     for (int off = 1; off < group / 8; off <<= 1) a0 = fmaxf(a0, __shfl_xor_sync(FULL, a0, off));
                     a1 = a0;
                 }
-                const FqScale g0 = fq_scale(a0, half), g1 = group >= 8 ? g0 : fq_scale(a1, half);
+                const FqScale g0 = fq_scale_packed(a0, half, inv_half), g1 = group >= 8 ? g0 : fq_scale_packed(a1, half, inv_half);
                 w[0] = fq_pair_bf16(w[0], g0); w[1] = fq_pair_bf16(w[1], g0);
                 w[2] = fq_pair_bf16(w[2], g1); w[3] = fq_pair_bf16(w[3], g1);
                 if (y != nullptr && live) {
@@ -206,9 +226,15 @@ static cudaError_t launch_ep(const void* x, void* y, float* kinv, uint8_t* valid
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     long long want = (rows + RPB - 1) / RPB;
-    const long long cap = (long long)sms * 8;           // 8 resident CTAs of 256 threads per SM
-    const int grid = (int)(want < cap ? (want > 0 ? want : 1) : cap);
-    writer_epilogue_kernel<D, Tin, Tout><<<grid, EP_THREADS, 0, st>>>((const Tin*)x, (Tout*)y, kinv, valid, rows, bits, group);
+    auto go = [&](auto kern) {
+        int per_sm = 8;                                  // resident CTAs per SM: the grid is exactly one wave
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, EP_THREADS, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+        const long long cap = (long long)sms * per_sm;
+        const int grid = (int)(want < cap ? (want > 0 ? want : 1) : cap);
+        kern<<<grid, EP_THREADS, 0, st>>>((const Tin*)x, (Tout*)y, kinv, valid, rows, bits, group);
+    };
+    if (sizeof(Tin) == 2 && bits > 0) go(writer_epilogue_kernel<D, Tin, Tout, sizeof(Tin) == 2>);
+    else go(writer_epilogue_kernel<D, Tin, Tout, false>);
     return cudaGetLastError();
 }
 

@@ -85,6 +85,32 @@ def test_epilogue_unquantised_matches_oracle():
     assert not valid[:, 0].any() and not valid[1, 3, 2, 7]
 
 
+def test_fq_bf16_exact_quotients_and_tiny_values():
+    """bf16 input built to sit ON the quantiser's decision points: every element an integer multiple of the group's
+    step s = a / half (so x / s is exactly an integer and floor must not slip below it), mixed with values one bf16
+    ulp beside those, bf16 subnormals and signed zeros.  Bit-exact against the torch restatement."""
+    S = _S()
+    g = torch.Generator().manual_seed(11)
+    for bits, group in ((3, 16), (2, 8), (4, 32), (8, 128), (3, 4)):
+        half = 2 ** (bits - 1)
+        rows, D = 4096, 128
+        a = (0.25 + 3.0 * torch.rand(rows, D // group, 1, generator=g)).to(torch.bfloat16).float()
+        kint = torch.randint(-half, half + 1, (rows, D // group, group), generator=g).float()
+        x = (kint * (a / half)).to(torch.bfloat16)                       # exact: k * a / 2^(bits-1) keeps a's 8 bits when k is small
+        bump = torch.randint(-1, 2, x.shape, generator=g).to(torch.int16)   # -1, 0, +1 ulp
+        x = (x.view(torch.int16) + bump).view(torch.bfloat16)
+        x[..., 0] = a[..., 0].to(torch.bfloat16)                          # the group's extreme itself, both signs
+        x[1::2, :, 0] = -x[1::2, :, 0]
+        tiny = torch.tensor([1e-39, -1e-39, 0.0, -0.0, 9.2e-41, -9.2e-41], dtype=torch.float32).to(torch.bfloat16)
+        x[:, :, 1] = tiny[torch.randint(0, 6, (rows, D // group), generator=g)]
+        x = torch.nan_to_num(x.float(), nan=0.0, posinf=0.0, neginf=0.0).to(torch.bfloat16).reshape(rows, D).cuda()
+        want = _fq_torch(x, bits, group)
+        kq, vq, kinv, valid = S.writer_epilogue(x.reshape(1, 1, 1, rows, D), x.reshape(1, 1, 1, rows, D), torch.bfloat16,
+                                                qbits=bits, qgroup=group)
+        same = kq.reshape(rows, D).view(torch.int16) == want.view(torch.int16)
+        assert bool(same.all()), (bits, group, int((~same).sum()), x[~same][:4], kq.reshape(rows, D)[~same][:4], want[~same][:4])
+
+
 @pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
 def test_epilogue_quantised_storage_modes(in_dtype):
     """Quantise in the scan's dtype, store in the model dtype, kinv / valid from the quantised keys before the cast."""
@@ -93,7 +119,7 @@ def test_epilogue_quantised_storage_modes(in_dtype):
     kbuf = (torch.randn(2, 5, 6, 33, 128, generator=g)).to(in_dtype).cuda()
     vbuf = (0.5 * torch.randn(2, 5, 6, 33, 128, generator=g)).to(in_dtype).cuda()
     kbuf[:, 0] = 0
-    for bits, group in ((3, 16), (8, 128), (4, 32), (2, 8)):
+    for bits, group in ((3, 16), (8, 128), (4, 32), (2, 8), (3, 4), (8, 64)):
         kq_w = _fq_torch(kbuf, bits, group)
         vq_w = _fq_torch(vbuf, bits, group)
         nsq = kq_w.float().pow(2).sum(-1)
