@@ -79,18 +79,22 @@ __device__ __forceinline__ float fq_one(float x, const FqScale& g) {
 //     land on the same bf16.
 // No division and no near-integer case is left over.  The lower clamp never binds (x >= -a gives k * s >= x at
 // k = -half).  Groups whose scale is clamped or denormal take fq_one.
-__device__ __forceinline__ unsigned fq_pair_bf16(const unsigned xw, const FqScale& g) {
+template <bool KNOWN_PLAIN>
+__device__ __forceinline__ unsigned fq_pair_bf16(const unsigned xw, const FqScale& g, const unsigned hm1) {   // hm1: half - 1 | half - 1
     const __nv_bfloat162 x2 = *reinterpret_cast<const __nv_bfloat162*>(&xw);
     const float2 x = __bfloat1622float2(x2);
     __nv_bfloat162 r2;
-    if (g.a == 0.f) return 0u;                           // an all-zero group stays zero (x + (0 - x) = +0)
-    if (g.plain) {
+    if (!KNOWN_PLAIN && g.a == 0.f) return 0u;           // an all-zero group stays zero (x + (0 - x) = +0)
+    if (KNOWN_PLAIN || g.plain) {
         const float MAGIC = 12582912.f;                  // 1.5 * 2^23: adding it rounds to an integer
         const float k0 = __fadd_rn(__fmaf_rn(x.x, g.rs, MAGIC), -MAGIC), k1 = __fadd_rn(__fmaf_rn(x.y, g.rs, MAGIC), -MAGIC);
-        const __nv_bfloat162 k2 = __floats2bfloat162_rn(k0, k1), s2 = __float2bfloat162_rn(g.s);
-        const __nv_bfloat162 over = __hgt2(__hfma2(k2, s2, __hneg2(x2)), __float2bfloat162_rn(0.f));   // 1.0 where k * s > x
-        const __nv_bfloat162 f2 = __hmin2(__hsub2(k2, over), __float2bfloat162_rn(g.half - 1.f));
-        const __nv_bfloat162 qd = __hmul2(__hadd2(f2, __float2bfloat162_rn(0.5f)), s2);
+        // k and s are bf16 values held in floats: their bf16 forms are the upper halves (byte permutes, no conversion)
+        const unsigned kw = __byte_perm(__float_as_uint(k0), __float_as_uint(k1), 0x7632);
+        const unsigned sw = __byte_perm(__float_as_uint(g.s), 0u, 0x3232), zw = 0u, hw = 0x3f003f00u;   // s | s, 0 | 0, 0.5 | 0.5
+        const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&kw), s2 = *reinterpret_cast<const __nv_bfloat162*>(&sw);
+        const __nv_bfloat162 over = __hgt2(__hfma2(k2, s2, __hneg2(x2)), *reinterpret_cast<const __nv_bfloat162*>(&zw));   // 1.0 where k * s > x
+        const __nv_bfloat162 f2 = __hmin2(__hsub2(k2, over), *reinterpret_cast<const __nv_bfloat162*>(&hm1));
+        const __nv_bfloat162 qd = __hmul2(__hadd2(f2, *reinterpret_cast<const __nv_bfloat162*>(&hw)), s2);
         r2 = __hadd2(x2, __hsub2(qd, x2));
     } else {
         r2 = __floats2bfloat162_rn(fq_one<__nv_bfloat16>(x.x, g), fq_one<__nv_bfloat16>(x.y, g));
@@ -116,6 +120,7 @@ __global__ void __launch_bounds__(EP_THREADS, PACKED ? 6 : 1) writer_epilogue_ke
     const int r = threadIdx.x / LPR, c = threadIdx.x % LPR;
     const float half = bits > 0 ? (float)(1 << (bits - 1)) : 0.f;
     const float inv_half = bits > 0 ? 1.f / half : 0.f;
+    const unsigned hm1 = __byte_perm(__float_as_uint(half - 1.f), 0u, 0x3232);     // half - 1 as a bf16 pair (exact)
     const long long stride = (long long)gridDim.x * RPB;
     uint4 ahead = make_uint4(0, 0, 0, 0);                // the next row of this lane, in flight while this one is worked on
     if constexpr (PACKED) {
@@ -138,8 +143,13 @@ __global__ void __launch_bounds__(EP_THREADS, PACKED ? 6 : 1) writer_epilogue_ke
                     a1 = a0;
                 }
                 const FqScale g0 = fq_scale_packed(a0, half, inv_half), g1 = group >= 8 ? g0 : fq_scale_packed(a1, half, inv_half);
-                w[0] = fq_pair_bf16(w[0], g0); w[1] = fq_pair_bf16(w[1], g0);
-                w[2] = fq_pair_bf16(w[2], g1); w[3] = fq_pair_bf16(w[3], g1);
+                if (g0.plain && g1.plain) {                  // the usual case, straight-line
+                    w[0] = fq_pair_bf16<true>(w[0], g0, hm1); w[1] = fq_pair_bf16<true>(w[1], g0, hm1);
+                    w[2] = fq_pair_bf16<true>(w[2], g1, hm1); w[3] = fq_pair_bf16<true>(w[3], g1, hm1);
+                } else {
+                    w[0] = fq_pair_bf16<false>(w[0], g0, hm1); w[1] = fq_pair_bf16<false>(w[1], g0, hm1);
+                    w[2] = fq_pair_bf16<false>(w[2], g1, hm1); w[3] = fq_pair_bf16<false>(w[3], g1, hm1);
+                }
                 if (y != nullptr && live) {
                     if constexpr (sizeof(Tout) == 2) *reinterpret_cast<uint4*>(y + row * D + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
