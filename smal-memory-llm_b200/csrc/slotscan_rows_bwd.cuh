@@ -563,8 +563,8 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
         if (lane < tc) {
             const int t = t0 + lane, sg = lane / G;
             const Tin* xr = reinterpret_cast<const Tin*>(dsm + LY::off_x + st * LY::x_bytes + lane * LY::XRS);
-            for (int rr = warp; rr < RPB; rr += ROW_THREADS / 32) {
-                if (row0 + rr >= N || t < s_ts[rr]) continue;
+            // one row: 128-long dot of the token vector with the row's S of this token's block
+            auto one_row = [&](int rr) {
                 const float* Sr = s_S + (size_t)sg * LY::SBS + rr * D;
                 float a0_ = 0.f, a1_ = 0.f, a2_ = 0.f, a3_ = 0.f;
 #pragma unroll 4
@@ -579,6 +579,38 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
                 }
                 const float dot = (a0_ + a1_) + (a2_ + a3_);
                 Dn[((size_t)bh * T + t) * N + row0 + rr] = fmaf(s_c[rr * RC + lane], dot, -s_xdx[rr * RC + lane]);
+            };
+            constexpr int NW = ROW_THREADS / 32;
+            for (int rr = warp; rr < RPB; rr += 2 * NW) {                  // rows rr and rr + NW of this warp
+                const int rb = rr + NW;
+                const bool okA = row0 + rr < N && t >= s_ts[rr], okB = rb < RPB && row0 + rb < N && t >= s_ts[rb];
+                if (okA && okB) {                                          // both: the token vector is unpacked once
+                    const float* SA = s_S + (size_t)sg * LY::SBS + rr * D;
+                    const float* SB = s_S + (size_t)sg * LY::SBS + rb * D;
+                    float a0_ = 0.f, a1_ = 0.f, a2_ = 0.f, a3_ = 0.f, b0_ = 0.f, b1_ = 0.f, b2_ = 0.f, b3_ = 0.f;
+#pragma unroll 4
+                    for (int d = 0; d < D; d += 8) {
+                        float xv[8];
+                        row8(xv, xr + d);
+                        const float4 s0 = ld4(SA + d / 2), s1 = ld4(SA + D / 2 + d / 2);
+                        const float4 u0 = ld4(SB + d / 2), u1 = ld4(SB + D / 2 + d / 2);
+                        a0_ = fmaf(xv[0], s0.x, a0_); a1_ = fmaf(xv[1], s0.y, a1_);
+                        a2_ = fmaf(xv[2], s0.z, a2_); a3_ = fmaf(xv[3], s0.w, a3_);
+                        b0_ = fmaf(xv[0], u0.x, b0_); b1_ = fmaf(xv[1], u0.y, b1_);
+                        b2_ = fmaf(xv[2], u0.z, b2_); b3_ = fmaf(xv[3], u0.w, b3_);
+                        a0_ = fmaf(xv[4], s1.x, a0_); a1_ = fmaf(xv[5], s1.y, a1_);
+                        a2_ = fmaf(xv[6], s1.z, a2_); a3_ = fmaf(xv[7], s1.w, a3_);
+                        b0_ = fmaf(xv[4], u1.x, b0_); b1_ = fmaf(xv[5], u1.y, b1_);
+                        b2_ = fmaf(xv[6], u1.z, b2_); b3_ = fmaf(xv[7], u1.w, b3_);
+                    }
+                    const float dotA = (a0_ + a1_) + (a2_ + a3_), dotB = (b0_ + b1_) + (b2_ + b3_);
+                    Dn[((size_t)bh * T + t) * N + row0 + rr] = fmaf(s_c[rr * RC + lane], dotA, -s_xdx[rr * RC + lane]);
+                    Dn[((size_t)bh * T + t) * N + row0 + rb] = fmaf(s_c[rb * RC + lane], dotB, -s_xdx[rb * RC + lane]);
+                } else if (okA) {
+                    one_row(rr);
+                } else if (okB) {
+                    one_row(rb);
+                }
             }
         }
     }
