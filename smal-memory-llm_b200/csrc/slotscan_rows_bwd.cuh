@@ -424,13 +424,18 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
         return rsum(a);
     };
 
-    // scalars of a chunk: fetched into registers two chunks ahead, stored one chunk ahead (warp 0)
+    // The copies and the scalars of the chunks ahead are the duty of the LAST warp: it holds the highest rows of the
+    // tile, which are taken last and walk the fewest events, and it does this work after the barrier that releases the
+    // other warps into their walk, so that the time it takes to issue a chunk's copies (32 bulk operations) is not on
+    // the path of the busy rows.
+    const bool issuer = warp == ROW_THREADS / 32 - 1;
+    // scalars of a chunk: fetched into registers two chunks ahead, stored one chunk ahead (issuing warp)
     float pre_g = 0.f;
     int pre_a = -1;
     auto load_scalars = [&](int ck) {
         pre_g = 0.f; pre_a = -1;
-        if (tid < RC && ck >= c_lo) {
-            const int t = ck * RC + tid;
+        if (issuer && ck >= c_lo) {
+            const int t = ck * RC + lane;
             if (t < T) {
                 const size_t ix = ((size_t)b * T + t) * H + h;
                 pre_g = gate_eff(gate[ix], p.hard_gate);
@@ -439,7 +444,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             }
         }
     };
-    // warp 0: token vectors of chunk ck into stage st (padded rows, as they are in memory)
+    // issuing warp: token vectors of chunk ck into stage st (padded rows, as they are in memory)
     auto issue_x = [&](int ck, int st) {
         const int t = ck * RC + lane;
         const bool in = t < T;
@@ -449,7 +454,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
         if (in) bulk_g2s(dsm + LY::off_x + st * LY::x_bytes + lane * LY::XRS, x + (((size_t)b * T + t) * H + h) * D,
                          D * sizeof(Tin), &s_bar[st]);
     };
-    // warp 0: undo rows of the tokens of chunk ck that write a row of this tile (addresses in slot `slot`)
+    // issuing warp: undo rows of the tokens of chunk ck that write a row of this tile (addresses in slot `slot`)
     auto issue_xo = [&](int ck, int slot) {
         const int t = ck * RC + lane;
         const bool hit = t < T && s_am[slot * RC + lane] >= 0;
@@ -461,7 +466,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
 
     // ---- prologue: chunk c_hi's scalars and copies; chunk c_hi - 1's scalars into registers ----
     load_scalars(c_hi);
-    if (warp == 0) {
+    if (issuer) {
         s_g[lane] = pre_g;
         s_am[lane] = pre_a;
         __syncwarp();
@@ -473,18 +478,21 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
     for (int k = 0; c_hi - k >= c_lo; k++) {
         const int ck = c_hi - k, st = k & 1;
         const int t0 = ck * RC, tc = min(RC, T - t0);
-        __syncthreads();                                    // the previous chunk's token-parallel pass is over
-        if (warp == 0 && ck - 1 >= c_lo) {                  // next chunk: scalars into the other slot, token vectors in flight
-            s_g[(st ^ 1) * RC + lane] = pre_g;
-            s_am[(st ^ 1) * RC + lane] = pre_a;
-            __syncwarp();
-            issue_x(ck - 1, st ^ 1);
-        }
-        load_scalars(ck - 2);
         const bool landed = mbar_wait_bounded(&s_bar[st], (unsigned)(k >> 1) & 1u) && mbar_wait_bounded(&s_bar[2], (unsigned)k & 1u);
-        if (!__syncthreads_and(landed ? 1 : 0)) {           // a copy never landed: give up, all threads together
+        // one barrier: the previous chunk's token-parallel pass is over (its stage and scalar slot are free), and
+        // this chunk's copies have landed for everybody -- or never will: then give up, all threads together
+        if (!__syncthreads_and(landed ? 1 : 0)) {
             if (tid == 0) atomicExch(&g_rows_bwd_status, 1);
             return;
+        }
+        if (issuer) {                                       // next chunk: scalars into the other slot, token vectors in flight
+            if (ck - 1 >= c_lo) {
+                s_g[(st ^ 1) * RC + lane] = pre_g;
+                s_am[(st ^ 1) * RC + lane] = pre_a;
+                __syncwarp();
+                issue_x(ck - 1, st ^ 1);
+            }
+            load_scalars(ck - 2);
         }
         // hit mask of this lane's row: bit i set when token t0 + i writes it
         unsigned m = 0u;
@@ -558,7 +566,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             }
         }
         __syncthreads();
-        if (warp == 0 && ck - 1 >= c_lo) issue_xo(ck - 1, st ^ 1);   // the undo rows of this chunk are consumed
+        if (issuer && ck - 1 >= c_lo) issue_xo(ck - 1, st ^ 1);      // the undo rows of this chunk are consumed
         // ---------------- (P) token-parallel pass: lane = token, warp = rows warp, warp + 8, ... ----------------
         if (lane < tc) {
             const int t = t0 + lane, sg = lane / G;
