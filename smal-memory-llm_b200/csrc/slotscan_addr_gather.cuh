@@ -117,34 +117,31 @@ __global__ void __launch_bounds__(GA_THREADS, 4) addr_bwd_gather_kernel(
         mbar_fence_init();
     }
     __syncthreads();
+    // The chunk's staging is up to 160 bulk copies; a warp issues its 32 one after the other, so the five groups go out
+    // from five warps at once (warp 1 computes the candidate limits meanwhile).  One thread posts the byte count of all
+    // of them; copies that complete before it has done so only make the count negative for a moment.
+    const bool r_in = lane < NR, t_in = lane < tc;
+    const unsigned drow = (unsigned)(NR * 4);                              // bytes of one token's candidate entries of a D table
+    const bool d_ok = (drow & 15u) == 0u && ((size_t)N * 4 & 15u) == 0u;   // bulk copies want 16-byte pieces
+    const size_t ixq = ((size_t)b * T + t0 + lane) * H + h;
+    const size_t di = ((size_t)bh * T + t0 + lane) * N;
+    if (warp == 2 && t_in) bulk_g2s(s_q + (size_t)lane * DK, q + ixq * DK, DK * sizeof(Tin), &s_bar);
+    if ((warp == 3 || warp == 4) && t_in) {
+        const int w = warp - 3;                                            // D table of the keys (0) / of the values (1)
+        const float* src = Din + (size_t)w * p.B * H * T * N + di;
+        if (d_ok) bulk_g2s(s_D + (w * GC + lane) * GATHER_ROWS, src, drow, &s_bar);
+        else for (int n = 0; n < NR; n++) s_D[(w * GC + lane) * GATHER_ROWS + n] = src[n];
+    }
+    if (warp == 5 && t_in) bulk_g2s(s_rows + (GATHER_ROWS + lane) * DK, kold + ixq * DK, DK * 4, &s_bar);
     if (warp == 0) {
         const int ve = (lane < NR) ? vend[((size_t)bh * nc + c) * GATHER_ROWS + lane] : -1;
-        const bool r_in = lane < NR, t_in = lane < tc;
-        const unsigned nrow = __popc(__ballot_sync(FULL, r_in)) + __popc(__ballot_sync(FULL, t_in));
-        const unsigned ntok = __popc(__ballot_sync(FULL, t_in));
-        const unsigned drow = (unsigned)(NR * 4);                          // bytes of one token's candidate entries of a D table
-        const bool d_ok = (drow & 15u) == 0u && ((size_t)N * 4 & 15u) == 0u;   // bulk copies want 16-byte pieces
         if (lane == 0)
-            mbar_arrive_expect_tx(&s_bar, nrow * (unsigned)(DK * 4) + ntok * (unsigned)(DK * sizeof(Tin)) + (d_ok ? ntok * 2u * drow : 0u));
+            mbar_arrive_expect_tx(&s_bar, (unsigned)(NR + tc) * (unsigned)(DK * 4) + (unsigned)tc * (unsigned)(DK * sizeof(Tin)) +
+                                              (d_ok ? (unsigned)tc * 2u * drow : 0u));
         __syncwarp();
-        if (t_in) {
-            const size_t ixq = ((size_t)b * T + t0 + lane) * H + h;
-            bulk_g2s(s_q + (size_t)lane * DK, q + ixq * DK, DK * sizeof(Tin), &s_bar);
-            const size_t di = ((size_t)bh * T + t0 + lane) * N;
-            if (d_ok) {
-                bulk_g2s(s_D + lane * GATHER_ROWS, Din + di, drow, &s_bar);
-                bulk_g2s(s_D + (GC + lane) * GATHER_ROWS, Din + (size_t)p.B * H * T * N + di, drow, &s_bar);
-            } else {
-                for (int n = 0; n < NR; n++) {
-                    s_D[lane * GATHER_ROWS + n] = Din[di + n];
-                    s_D[(GC + lane) * GATHER_ROWS + n] = Din[(size_t)p.B * H * T * N + di + n];
-                }
-            }
-        }
         if (r_in)
             bulk_g2s(s_rows + lane * DK, ve < 0 ? kfin + ((size_t)bh * N + lane) * DK : kold + (((size_t)b * T + ve) * H + h) * DK,
                      DK * 4, &s_bar);
-        if (t_in) bulk_g2s(s_rows + (GATHER_ROWS + lane) * DK, kold + (((size_t)b * T + t0 + lane) * H + h) * DK, DK * 4, &s_bar);
         s_vend[lane] = ve;
         if (r_in) {
             if (ve >= 0) {

@@ -133,17 +133,21 @@ __global__ void __launch_bounds__(ROW_THREADS * 8 / EPL, EPL == 16 ? 6 : 1) repl
     const int nchunk = (T + RC - 1) / RC;
     float pre_g = 0.f;
     int pre_a = -1;
+    // The copies and scalars of the chunks ahead are the duty of the LAST warp (the highest rows of the tile: taken last,
+    // fewest events), after the barrier that releases the other warps into their walk: issuing a chunk's 32 bulk copies
+    // takes a couple of thousand cycles, which would otherwise sit on the path of the busiest rows.
+    const bool issuer = warp == (int)(blockDim.x >> 5) - 1;
     auto load_scalars = [&](int ck) {
         pre_g = 0.f; pre_a = -1;
-        const int t = ck * RC + tid;
-        if (tid < RC && t < T) {
+        const int t = ck * RC + lane;
+        if (issuer && t < T) {
             const size_t ix = ((size_t)b * T + t) * H + h;
             pre_g = gate_eff(gate[ix], p.hard_gate);
             pre_a = am[ix] - row0;
             if (pre_a >= RPB) pre_a = -1;
         }
     };
-    auto issue_x = [&](int ck, int st) {                             // warp 0
+    auto issue_x = [&](int ck, int st) {                             // issuing warp
         const int t = ck * RC + lane;
         const bool in = t < T;
         const unsigned nin = __popc(__ballot_sync(FULL, in));
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__(ROW_THREADS * 8 / EPL, EPL == 16 ? 6 : 1) repl
     }
     load_scalars(0);
     __syncthreads();
-    if (warp == 0) {
+    if (issuer) {
         s_g[0][lane] = pre_g;
         s_am[0][lane] = pre_a;
         __syncwarp();
@@ -168,18 +172,21 @@ __global__ void __launch_bounds__(ROW_THREADS * 8 / EPL, EPL == 16 ? 6 : 1) repl
     int tsnap = 0;                                                   // next snapshot time (multiple of G)
     for (int k = 0; k < nchunk; k++) {
         const int t0 = k * RC, tc = min(RC, T - t0), st = k & 1;
-        __syncthreads();                                             // every row is done with chunk k - 1 (stage st ^ 1)
-        if (warp == 0 && k + 1 < nchunk) {
-            s_g[st ^ 1][lane] = pre_g;
-            s_am[st ^ 1][lane] = pre_a;
-            __syncwarp();
-            issue_x(k + 1, st ^ 1);
-        }
-        load_scalars(k + 2);
         const bool landed = mbar_wait_bounded(&s_bar[st], (unsigned)(k >> 1) & 1u);
-        if (!__syncthreads_and(landed ? 1 : 0)) {                    // a copy never landed: give up, all threads together
+        // one barrier: every row is done with chunk k - 1 (stage st ^ 1 and its scalar slot are free) and chunk k has
+        // landed for everybody -- or never will: then give up, all threads together
+        if (!__syncthreads_and(landed ? 1 : 0)) {
             if (tid == 0) atomicExch(&g_replay_status, 1);
             return;
+        }
+        if (issuer) {
+            if (k + 1 < nchunk) {
+                s_g[st ^ 1][lane] = pre_g;
+                s_am[st ^ 1][lane] = pre_a;
+                __syncwarp();
+                issue_x(k + 1, st ^ 1);
+            }
+            load_scalars(k + 2);
         }
         unsigned m = 0u;                                             // bit i: token t0 + i writes this lane's row
         {
