@@ -370,7 +370,10 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
     const int NB = (T + G - 1) / G;
     const int b = bh / H, h = bh % H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = tid / LPR, c = tid % LPR, row0 = tile * RPB, n0 = row0 + r;
+    // (Neighbouring rows share a warp.  Pairing row r with row r + 8 instead, so that a busy low row sits with an idle
+    // high one, was measured: faster with few sequences per GPU, slower with three CTAs per SM, where it only spreads
+    // the same instructions over more warps.)
+    const int r = tid / LPR, c = lane % LPR, row0 = tile * RPB, n0 = row0 + r;
     const bool live = n0 < N;
     const int n = live ? n0 : 0;
     if (!tile_active(tfirst + (size_t)bh * N, n, live, T, &s_flag)) return;
@@ -424,10 +427,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
         return rsum(a);
     };
 
-    // The copies and the scalars of the chunks ahead are the duty of the LAST warp: it holds the highest rows of the
-    // tile, which are taken last and walk the fewest events, and it does this work after the barrier that releases the
-    // other warps into their walk, so that the time it takes to issue a chunk's copies (32 bulk operations) is not on
-    // the path of the busy rows.
+    // The scalars of the chunks ahead are the duty of the last warp, after the barrier that releases the walk.
     const bool issuer = warp == ROW_THREADS / 32 - 1;
     // scalars of a chunk: fetched into registers two chunks ahead, stored one chunk ahead (issuing warp)
     float pre_g = 0.f;
@@ -444,24 +444,27 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             }
         }
     };
-    // issuing warp: token vectors of chunk ck into stage st (padded rows, as they are in memory)
+    // Every warp issues its share (RC / 8 tokens) of a chunk's copies: a warp's bulk copies leave one after the other,
+    // some 75 cycles apiece, so 32 of them from one warp would hold that warp's rows up for a couple of thousand cycles.
+    // One thread posts the byte count; copies that complete before it has done so make the count negative for a moment.
+    constexpr int PER = RC / (ROW_THREADS / 32);
+    // token vectors of chunk ck into stage st (padded rows, as they are in memory)
     auto issue_x = [&](int ck, int st) {
-        const int t = ck * RC + lane;
-        const bool in = t < T;
-        const unsigned nin = __popc(__ballot_sync(FULL, in));
-        if (lane == 0) mbar_arrive_expect_tx(&s_bar[st], nin * (unsigned)(D * sizeof(Tin)));
-        __syncwarp();
-        if (in) bulk_g2s(dsm + LY::off_x + st * LY::x_bytes + lane * LY::XRS, x + (((size_t)b * T + t) * H + h) * D,
-                         D * sizeof(Tin), &s_bar[st]);
+        const int i = warp * PER + lane, t = ck * RC + i;
+        if (tid == 0) mbar_arrive_expect_tx(&s_bar[st], (unsigned)min(RC, T - ck * RC) * (unsigned)(D * sizeof(Tin)));
+        if (lane < PER && t < T)
+            bulk_g2s(dsm + LY::off_x + st * LY::x_bytes + i * LY::XRS, x + (((size_t)b * T + t) * H + h) * D, D * sizeof(Tin), &s_bar[st]);
     };
-    // issuing warp: undo rows of the tokens of chunk ck that write a row of this tile (addresses in slot `slot`)
+    // undo rows of the tokens of chunk ck that write a row of this tile (addresses in slot `slot`)
     auto issue_xo = [&](int ck, int slot) {
-        const int t = ck * RC + lane;
-        const bool hit = t < T && s_am[slot * RC + lane] >= 0;
-        const unsigned nhit = __popc(__ballot_sync(FULL, hit));
-        if (lane == 0) mbar_arrive_expect_tx(&s_bar[2], nhit * (unsigned)(D * 4));
-        __syncwarp();
-        if (hit) bulk_g2s(s_xo + lane * D, xold + (((size_t)b * T + t) * H + h) * D, D * 4, &s_bar[2]);
+        if (warp == 0) {
+            const bool hit = ck * RC + lane < T && s_am[slot * RC + lane] >= 0;
+            const unsigned nhit = __popc(__ballot_sync(FULL, hit));
+            if (lane == 0) mbar_arrive_expect_tx(&s_bar[2], nhit * (unsigned)(D * 4));
+        }
+        const int i = warp * PER + lane, t = ck * RC + i;
+        if (lane < PER && t < T && s_am[slot * RC + i] >= 0)
+            bulk_g2s(s_xo + i * D, xold + (((size_t)b * T + t) * H + h) * D, D * 4, &s_bar[2]);
     };
 
     // ---- prologue: chunk c_hi's scalars and copies; chunk c_hi - 1's scalars into registers ----
@@ -469,10 +472,10 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
     if (issuer) {
         s_g[lane] = pre_g;
         s_am[lane] = pre_a;
-        __syncwarp();
-        issue_x(c_hi, 0);
-        issue_xo(c_hi, 0);
     }
+    __syncthreads();
+    issue_x(c_hi, 0);
+    issue_xo(c_hi, 0);
     load_scalars(c_hi - 1);
 
     for (int k = 0; c_hi - k >= c_lo; k++) {
@@ -485,12 +488,11 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             if (tid == 0) atomicExch(&g_rows_bwd_status, 1);
             return;
         }
-        if (issuer) {                                       // next chunk: scalars into the other slot, token vectors in flight
+        if (ck - 1 >= c_lo) issue_x(ck - 1, st ^ 1);        // next chunk: token vectors in flight
+        if (issuer) {                                       // its scalars into the other slot; those of the chunk after it fetched
             if (ck - 1 >= c_lo) {
                 s_g[(st ^ 1) * RC + lane] = pre_g;
                 s_am[(st ^ 1) * RC + lane] = pre_a;
-                __syncwarp();
-                issue_x(ck - 1, st ^ 1);
             }
             load_scalars(ck - 2);
         }
@@ -566,7 +568,7 @@ __global__ void __launch_bounds__(ROW_THREADS, (sizeof(Tin) == 2 ? 3 : 2)) rows_
             }
         }
         __syncthreads();
-        if (issuer && ck - 1 >= c_lo) issue_xo(ck - 1, st ^ 1);      // the undo rows of this chunk are consumed
+        if (ck - 1 >= c_lo) issue_xo(ck - 1, st ^ 1);       // the undo rows of this chunk are consumed
         // ---------------- (P) token-parallel pass: lane = token, warp = rows warp, warp + 8, ... ----------------
         if (lane < tc) {
             const int t = t0 + lane, sg = lane / G;
