@@ -334,12 +334,13 @@ class ScanJob:
 
 
 def timed(job, steps, barrier, clock_index=None):
-    """`steps` calls of job.step() between two events on the current stream, barrier + synchronize on both sides;
-    per-kernel event times from the library."""
+    """`steps` calls of job.step() between two events on the current stream, barrier + synchronize on both sides.
+    The per-kernel event times come from a few more steps AFTER the timed region: the library's per-launch events
+    cost two event creations and two records per kernel on the host, which a step of a millisecond (few sequences per
+    GPU) would feel."""
     import torch
     from slotscan_b200 import _lib
-    _lib.profile_enable(True)
-    _lib.profile_read()
+    _lib.profile_enable(False)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clk = ClockSampler(clock_index) if clock_index is not None else None
     if clk:
@@ -352,8 +353,16 @@ def timed(job, steps, barrier, clock_index=None):
     barrier()
     if clk:
         clk.__exit__()
+    _lib.profile_enable(True)
+    _lib.profile_read()
+    psteps = min(steps, 5)
+    for _ in range(psteps):
+        job.step()
+    torch.cuda.synchronize()
     prof = _lib.profile_read()
     _lib.profile_enable(False)
+    # counts and times as of the timed region: the same launches per step, `steps` steps
+    prof = {n: (c * steps // psteps, t * steps / psteps) for n, (c, t) in prof.items()}
     return e0.elapsed_time(e1), prof, (clk.summary() if clk else None)
 
 
