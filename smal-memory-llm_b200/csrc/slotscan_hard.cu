@@ -140,12 +140,27 @@ static cudaError_t fwd_run(const slotscan_params& p, const void* k, const void* 
         }
         if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(side, fork, 0);
         if (e2 == cudaSuccess) e2 = scan_on(side);
-        if (e2 == cudaSuccess && tz > 0) {
-            ProfScope ps(K_REPLAY_K, side);
-            e2 = run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, 0, tz, side);
+        if (merged && tz > 0) {
+            // tiles below the fill on the second stream, the tiles above it on the caller's (after scan and fill), side by
+            // side; the caller's stream then waits for the second one
+            if (e2 == cudaSuccess) e2 = cudaEventRecord(fork, side);              // `fork` has been waited for: reused as "scan done"
+            if (e2 == cudaSuccess) {
+                ProfScope ps(K_REPLAY_K, side);
+                e2 = run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, 0, tz, side);
+            }
+            if (e2 == cudaSuccess) e2 = cudaEventRecord(joined, side);
+            if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, fork, 0);
+            if (e2 == cudaSuccess) {
+                ProfScope ps(K_REPLAY_V, st);
+                e2 = run_replay(p, p.DK, 2, rk, rv, gate, L.addr, L.tfirst, tz, -1, st);
+            }
+            if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);
+            cudaEventDestroy(fork);
+            cudaEventDestroy(joined);
+            return e2;
         }
         if (e2 == cudaSuccess) e2 = cudaEventRecord(joined, side);
-        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);          // the rest of the replay comes after both
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, joined, 0);          // the replay comes after both
         cudaEventDestroy(fork);
         cudaEventDestroy(joined);
         if (e2 != cudaSuccess) return e2;
