@@ -37,11 +37,13 @@ static cudaError_t launch_one(const slotscan_params& p, const void* q, const voi
 template <int DK>
 static cudaError_t launch_gather(const slotscan_params& p, const void* q, const float* gate, const float* fr,
                                  const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate,
-                                 float* dfr, float* part, int* vend, int part_stride, cudaStream_t st) {
+                                 float* dfr, float* part, int* vend, int part_stride, bool vend_ready, cudaStream_t st) {
     if constexpr (DK >= 32) {
-        next_write_kernel<<<p.B * p.H, 32, 0, st>>>(p, L.addr, L.tfirst, vend);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
+        cudaError_t e = cudaSuccess;
+        if (!vend_ready) {
+            next_write_kernel<<<p.B * p.H, 32, 0, st>>>(p, L.addr, L.tfirst, vend);
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
         dim3 grid(p.B * p.H, (p.T + GC - 1) / GC);
         const size_t dyn = (size_t)GC * DK * sizeof(Tin) + 2 * (size_t)GC * GATHER_ROWS * sizeof(float);   // queries + D rows
         auto gk = addr_bwd_gather_kernel<DK, Tin>;
@@ -58,12 +60,12 @@ static cudaError_t launch_gather(const slotscan_params& p, const void* q, const 
 template <int DK>
 static cudaError_t launch_dk(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                              const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
-                             float* part, int* vend, int part_stride, cudaStream_t st) {
+                             float* part, int* vend, int part_stride, bool vend_ready, cudaStream_t st) {
     // Sequences with at most GATHER_ROWS candidate rows go to the token-parallel gather kernel (occ_bin only: the
     // occupancy adjoint is not carried there); the rest, and every sequence of the other modes, to the chunked one.
     int skip = 0;
     if (p.occ_bin && DK >= 32) {
-        cudaError_t e = launch_gather<DK>(p, q, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st);
+        cudaError_t e = launch_gather<DK>(p, q, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, vend_ready, st);
         if (e != cudaSuccess) return e;
         skip = GATHER_ROWS;
         if (p.N <= GATHER_ROWS) return cudaSuccess;
@@ -78,11 +80,19 @@ static cudaError_t launch_dk(const slotscan_params& p, const void* q, const void
 cudaError_t SS_CAT(run_addr_bwd_, SLOTSCAN_SUFFIX)(const slotscan_params& p, const void* q, const void* k, const float* gate,
                                                   const float* fr, const float* temp, const slotscan_log& L,
                                                   const float* Dn, void* dq, float* dgate, float* dfr, float* part,
-                                                  int* vend, int part_stride, cudaStream_t st) {
+                                                  int* vend, int part_stride, bool vend_ready, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
-    SLOTSCAN_DISPATCH_D(p.DK, e = (launch_dk<DD>(p, q, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st)));
+    SLOTSCAN_DISPATCH_D(p.DK, e = (launch_dk<DD>(p, q, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, vend_ready, st)));
     return e;
 }
+
+#ifdef SLOTSCAN_DEFINE_NEXT_WRITE
+bool next_write_used(const slotscan_params& p) { return p.occ_bin && p.DK >= 32; }
+cudaError_t run_next_write(const slotscan_params& p, const slotscan_log& L, int* vend, cudaStream_t st) {
+    next_write_kernel<<<p.B * p.H, 32, 0, st>>>(p, L.addr, L.tfirst, vend);
+    return cudaGetLastError();
+}
+#endif
 
 // 1 when a bounded wait of this translation unit's kernels gave up since the last call (clears the flag)
 int SS_CAT(gather_status_, SLOTSCAN_SUFFIX)() {

@@ -194,6 +194,25 @@ static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* 
     // kernel fills must read as zero
     const int part_stride = (p.T + GATHER_CHUNK - 1) / GATHER_CHUNK + 1;
     const size_t part_n = (size_t)p.B * p.H * part_stride;
+    // The next-write table of the address backward needs the forward's log only: it runs on the second stream beside the
+    // reverse row scan, and the address backward waits for it.
+    bool vend_ready = false;
+    cudaEvent_t joined = nullptr;
+    if (next_write_used(p)) {
+        cudaStream_t side = side_stream(st);
+        cudaEvent_t fork = nullptr;
+        if (side != nullptr && cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess &&
+            cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) == cudaSuccess) {
+            if (cudaEventRecord(fork, st) == cudaSuccess && cudaStreamWaitEvent(side, fork, 0) == cudaSuccess) {
+                vend_ready = run_next_write(p, L, vend, side) == cudaSuccess && cudaEventRecord(joined, side) == cudaSuccess;
+                // error path: nothing of this call stays in flight on the second stream; the table is then filled on the caller's
+                if (!vend_ready) cudaStreamSynchronize(side);
+            }
+        }
+        if (fork != nullptr) cudaEventDestroy(fork);
+        if (!vend_ready && joined != nullptr) { cudaEventDestroy(joined); joined = nullptr; }
+    }
+    struct JoinedGuard { cudaEvent_t& e; ~JoinedGuard() { if (e != nullptr) cudaEventDestroy(e); } } joined_guard{joined};
     if ((e = cudaMemsetAsync(part, 0, 2 * part_n * sizeof(float), st)) != cudaSuccess) return e;
     // keys and values are independent given the log: one launch (blockIdx.z) when dk == dv, each into its own D table
     float* DnV = Dn + (size_t)p.B * p.H * p.T * p.N;
@@ -212,11 +231,12 @@ static cudaError_t bwd_run(const slotscan_params& p, const void* k, const void* 
         e = run_rows_bwd(p, p.DV, 1, av, av, gate, L.addr, L.tfirst, st);
     }
     if (e != cudaSuccess) return e;
+    if (vend_ready && (e = cudaStreamWaitEvent(st, joined, 0)) != cudaSuccess) return e;
     {
         ProfScope ps(K_ADDR_BWD, st);
         e = (p.in_dtype == SLOTSCAN_F32)
-                ? run_addr_bwd_f32(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st)
-                : run_addr_bwd_bf16(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, st);
+                ? run_addr_bwd_f32(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, vend_ready, st)
+                : run_addr_bwd_bf16(p, q ? q : k, k, gate, fr, temp, L, Dn, dq, dgate, dfr, part, vend, part_stride, vend_ready, st);
     }
     if (e != cudaSuccess) return e;
     ProfScope ps(K_FINISH, st);

@@ -24,12 +24,17 @@ cudaError_t run_addr_fwd_f32(const slotscan_params& p, const void* q, const void
                              const float* temp, const slotscan_log& L, const AddrFwdState& S0, cudaStream_t st);
 cudaError_t run_addr_fwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                               const float* temp, const slotscan_log& L, const AddrFwdState& S0, cudaStream_t st);
+// vend_ready: the next-write table (run_next_write) has been filled already, on a stream this one is ordered after
 cudaError_t run_addr_bwd_f32(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                              const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
-                             float* part, int* vend, int part_stride, cudaStream_t st);
+                             float* part, int* vend, int part_stride, bool vend_ready, cudaStream_t st);
 cudaError_t run_addr_bwd_bf16(const slotscan_params& p, const void* q, const void* k, const float* gate, const float* fr,
                               const float* temp, const slotscan_log& L, const float* Dn, void* dq, float* dgate, float* dfr,
-                              float* part, int* vend, int part_stride, cudaStream_t st);
+                              float* part, int* vend, int part_stride, bool vend_ready, cudaStream_t st);
+// the next-write table of the token-parallel address backward: it depends on the forward's log only, so it can run
+// beside the reverse row scan; true when the address backward of this shape uses it
+bool next_write_used(const slotscan_params& p);
+cudaError_t run_next_write(const slotscan_params& p, const slotscan_log& L, int* vend, cudaStream_t st);
 // tokens per CTA of the token-parallel address backward: the partial-sum table has one slot per such chunk (+ 1)
 constexpr int GATHER_CHUNK = 32;
 constexpr int GATHER_ROWS_MAX = 32;
